@@ -1,0 +1,286 @@
+// C ABI of libfkmoe (declarations and reference citations: include/fkmoe.h).
+
+#include <cstdio>
+#include <cstring>
+
+#include "common.cuh"
+#include "kernels.cuh"
+
+namespace fk {
+
+static thread_local char g_last_error[256] = "";
+
+void note_cuda_error(cudaError_t e, const char* where) {
+    snprintf(g_last_error, sizeof(g_last_error), "%s: %s", where, cudaGetErrorString(e));
+    (void)cudaGetLastError();   // clear the sticky-less error so later calls are not blamed for it
+}
+
+static bool dims_ok(const fk_moe_dims& d, bool need_routing) {
+    if (d.tokens < 0 || d.hidden < 1 || d.hidden > FK_MAX_HIDDEN) return false;
+    if (d.experts < 1 || d.experts > FK_MAX_EXPERTS) return false;
+    if (d.intermediate < 1 || d.intermediate > FK_MAX_INTERMEDIATE) return false;
+    if (d.top_k < (need_routing ? 1 : 0) || d.top_k > FK_MAX_TOP_K) return false;
+    if ((long long)d.tokens * (d.top_k > 0 ? d.top_k : 1) > (1 << 24)) return false;
+    return true;
+}
+
+static bool dtype_ok(int dt) { return dt == FK_F32 || dt == FK_BF16 || dt == FK_F16; }
+
+template <typename T>
+static T* at(void* base, size_t off) { return reinterpret_cast<T*>(reinterpret_cast<char*>(base) + off); }
+
+static int check_workspace(const fk_moe_call* c, Workspace& w) {
+    w = workspace_layout(c->dims);
+    if (c->workspace == nullptr || c->workspace_bytes < w.total) return FK_ERR_WORKSPACE;
+    if (reinterpret_cast<uintptr_t>(c->workspace) & 255) return FK_ERR_WORKSPACE;
+    return FK_OK;
+}
+
+// permutation + expert kernels + combine for routing already present in ids/weights
+static int run_experts(const fk_moe_call* c, const Workspace& w, const long long* ids, const float* weights,
+                       const float* shared_gate_sig, cudaStream_t stream) {
+    const fk_moe_dims& d = c->dims;
+    void* ws = c->workspace;
+    PermuteParams pp{};
+    pp.ids64 = ids;
+    pp.routes = d.tokens * d.top_k;
+    pp.E = d.experts;
+    pp.expert_base = c->expert_base;
+    pp.skip_foreign = (c->flags & FK_FLAG_SKIP_FOREIGN) ? 1 : 0;
+    pp.counts = at<int>(ws, w.counts);
+    pp.offsets = at<int>(ws, w.offsets);
+    pp.touched = at<int>(ws, w.touched);
+    pp.order = at<int>(ws, w.order);
+    pp.inv = at<int>(ws, w.inv);
+    pp.meta = at<int>(ws, w.meta);
+    int st = launch_permute(pp, stream);
+    if (st != FK_OK) return st;
+
+    ExpertParams ep{};
+    ep.hidden = c->hidden;
+    ep.hidden_dtype = c->hidden_dtype;
+    ep.gate_up = c->expert_gate_up;
+    ep.down = c->expert_down;
+    ep.shared_gate_up = c->shared_gate_up;
+    ep.shared_down = c->shared_gate_up ? c->shared_down : nullptr;
+    ep.T = d.tokens; ep.H = d.hidden; ep.E = d.experts; ep.I = d.intermediate; ep.top_k = d.top_k;
+    ep.routes = pp.routes;
+    ep.counts = pp.counts; ep.offsets = pp.offsets; ep.touched = pp.touched;
+    ep.order = pp.order; ep.inv = pp.inv; ep.meta = pp.meta;
+    ep.topk_weights = weights;
+    ep.shared_gate = shared_gate_sig;
+    ep.act = at<float>(ws, w.act);
+    ep.y = at<float>(ws, w.y);
+    ep.out = c->out;
+    ep.layer_hidden = c->layer_hidden;
+
+    const bool fast = !(c->flags & FK_FLAG_FORCE_GENERIC) && gemv_path_supported(ep, c->weight_dtype);
+    st = fast ? launch_experts_gemv(ep, stream) : launch_experts_generic(ep, c->weight_dtype, stream);
+    if (st != FK_OK) return st;
+    return launch_combine(ep, stream);
+}
+
+// sigmoid(g . x) per token for callers that skip the router (fk_moe_experts with a gate)
+__global__ void shared_gate_kernel(const void* hidden, int hidden_dtype, const void* g, int weight_dtype, float* out,
+                                   int T, int H) {
+    const int lane = threadIdx.x & 31;
+    const int t = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    if (t >= T) return;
+    float acc = 0.f;
+    for (int h = lane; h < H; h += 32)
+        acc = fmaf(load_any(g, weight_dtype, h), load_any(hidden, hidden_dtype, (size_t)t * H + h), acc);
+    acc = warp_sum(acc);
+    if (lane == 0) out[t] = sigmoidf_(acc);
+}
+
+}  // namespace fk
+
+using namespace fk;
+
+extern "C" {
+
+int fk_version(void) { return 100; }
+
+const char* fk_status_string(int status) {
+    switch (status) {
+        case FK_OK: return "ok";
+        case FK_ERR_ARG: return "invalid argument";
+        case FK_ERR_UNSUPPORTED: return "unsupported dtype or shape";
+        case FK_ERR_WORKSPACE: return "workspace too small or misaligned";
+        case FK_ERR_CUDA: return "CUDA error";
+        case FK_ERR_TIMEOUT: return "device-side wait timed out";
+        default: return "unknown status";
+    }
+}
+
+const char* fk_last_cuda_error(void) { return g_last_error; }
+
+size_t fk_moe_workspace_bytes(const fk_moe_dims* dims) {
+    if (dims == nullptr || !dims_ok(*dims, false)) return 0;
+    return workspace_layout(*dims).total;
+}
+
+int fk_moe_workspace_init(void* workspace, size_t bytes, void* stream) {
+    if (workspace == nullptr) return FK_ERR_ARG;
+    // only the self-resetting words need a defined start value; they sit at the front
+    Workspace w = workspace_layout(fk_moe_dims{0, 1, 1, 1, 0});
+    size_t head = w.ids32;
+    if (bytes < head) return FK_ERR_WORKSPACE;
+    FK_CUDA_OK(cudaMemsetAsync(workspace, 0, head, (cudaStream_t)stream), "workspace init");
+    return FK_OK;
+}
+
+int fk_moe_router(const fk_moe_call* c, void* stream) {
+    if (c == nullptr || !dims_ok(c->dims, true) || c->dims.top_k > c->dims.experts) return FK_ERR_ARG;
+    if (!dtype_ok(c->hidden_dtype) || !dtype_ok(c->weight_dtype)) return FK_ERR_UNSUPPORTED;
+    if (c->dims.tokens == 0) return FK_OK;
+    if (!c->hidden || !c->norm_weight || !c->router_weight || !c->logits || !c->topk_ids || !c->topk_weights) return FK_ERR_ARG;
+    Workspace w;
+    int st = check_workspace(c, w);
+    if (st != FK_OK) return st;
+    RouterParams rp{};
+    rp.hidden = c->hidden; rp.hidden_dtype = c->hidden_dtype;
+    rp.norm_weight = c->norm_weight; rp.router_weight = c->router_weight; rp.router_bias = c->router_bias;
+    rp.shared_gate_weight = nullptr; rp.shared_gate_out = nullptr;
+    rp.logits = c->logits; rp.topk_ids = reinterpret_cast<long long*>(c->topk_ids); rp.topk_weights = c->topk_weights;
+    rp.ids32 = nullptr;
+    rp.tickets = at<unsigned>(c->workspace, w.tickets);
+    rp.T = c->dims.tokens; rp.H = c->dims.hidden; rp.E = c->dims.experts; rp.top_k = c->dims.top_k;
+    rp.eps = c->eps; rp.norm_offset = c->norm_offset;
+    return launch_router(rp, c->weight_dtype, (cudaStream_t)stream);
+}
+
+int fk_moe_experts(const fk_moe_call* c, void* stream) {
+    if (c == nullptr || !dims_ok(c->dims, false)) return FK_ERR_ARG;
+    if (!dtype_ok(c->hidden_dtype) || !dtype_ok(c->weight_dtype)) return FK_ERR_UNSUPPORTED;
+    if (c->dims.tokens == 0) return FK_OK;
+    if (!c->hidden || !c->out) return FK_ERR_ARG;
+    if (c->dims.top_k > 0 && (!c->topk_ids_in || !c->topk_weights_in || !c->expert_gate_up || !c->expert_down)) return FK_ERR_ARG;
+    if ((c->shared_gate_up == nullptr) != (c->shared_down == nullptr)) return FK_ERR_ARG;
+    Workspace w;
+    int st = check_workspace(c, w);
+    if (st != FK_OK) return st;
+    cudaStream_t s = (cudaStream_t)stream;
+    const float* gate_sig = nullptr;
+    if (c->shared_gate_up && c->shared_gate) {
+        float* g = at<float>(c->workspace, w.shared_gate);
+        int warps_per_block = 8;
+        int blocks = (c->dims.tokens + warps_per_block - 1) / warps_per_block;
+        shared_gate_kernel<<<blocks, warps_per_block * 32, 0, s>>>(c->hidden, c->hidden_dtype, c->shared_gate, c->weight_dtype, g,
+                                                                  c->dims.tokens, c->dims.hidden);
+        FK_LAUNCH_OK("shared gate launch");
+        gate_sig = g;
+    }
+    return run_experts(c, w, reinterpret_cast<const long long*>(c->topk_ids_in), c->topk_weights_in, gate_sig, s);
+}
+
+int fk_moe_layer(const fk_moe_call* c, void* stream) {
+    if (c == nullptr || !dims_ok(c->dims, true) || c->dims.top_k > c->dims.experts) return FK_ERR_ARG;
+    if (!dtype_ok(c->hidden_dtype) || !dtype_ok(c->weight_dtype)) return FK_ERR_UNSUPPORTED;
+    if (c->dims.tokens == 0) return FK_OK;
+    if (!c->hidden || !c->norm_weight || !c->router_weight || !c->expert_gate_up || !c->expert_down || !c->out ||
+        !c->logits || !c->topk_ids || !c->topk_weights)
+        return FK_ERR_ARG;
+    if ((c->shared_gate_up == nullptr) != (c->shared_down == nullptr)) return FK_ERR_ARG;
+    Workspace w;
+    int st = check_workspace(c, w);
+    if (st != FK_OK) return st;
+    cudaStream_t s = (cudaStream_t)stream;
+    const bool gated = c->shared_gate_up && c->shared_gate;
+    RouterParams rp{};
+    rp.hidden = c->hidden; rp.hidden_dtype = c->hidden_dtype;
+    rp.norm_weight = c->norm_weight; rp.router_weight = c->router_weight; rp.router_bias = c->router_bias;
+    rp.shared_gate_weight = gated ? c->shared_gate : nullptr;
+    rp.shared_gate_out = gated ? at<float>(c->workspace, w.shared_gate) : nullptr;
+    rp.logits = c->logits; rp.topk_ids = reinterpret_cast<long long*>(c->topk_ids); rp.topk_weights = c->topk_weights;
+    rp.ids32 = nullptr;
+    rp.tickets = at<unsigned>(c->workspace, w.tickets);
+    rp.T = c->dims.tokens; rp.H = c->dims.hidden; rp.E = c->dims.experts; rp.top_k = c->dims.top_k;
+    rp.eps = c->eps; rp.norm_offset = c->norm_offset;
+    st = launch_router(rp, c->weight_dtype, s);
+    if (st != FK_OK) return st;
+    return run_experts(c, w, rp.topk_ids, c->topk_weights, rp.shared_gate_out, s);
+}
+
+size_t fk_moe_host_staging_bytes(const fk_moe_dims* d, int hidden_dtype) {
+    if (d == nullptr || !dims_ok(*d, true) || !dtype_ok(hidden_dtype)) return 0;
+    size_t T = d->tokens, H = d->hidden, E = d->experts, k = d->top_k;
+    size_t es = hidden_dtype == FK_F32 ? 4 : 2;
+    return align256(T * H * es) + 2 * align256(T * H * 4) + align256(T * E * 4) + align256(T * k * 8) + align256(T * k * 4);
+}
+
+int fk_moe_layer_host(const fk_moe_call* c, void* staging, size_t staging_bytes, void* stream) {
+    if (c == nullptr || staging == nullptr) return FK_ERR_ARG;
+    size_t need = fk_moe_host_staging_bytes(&c->dims, c->hidden_dtype);
+    if (need == 0) return FK_ERR_ARG;
+    if (staging_bytes < need || (reinterpret_cast<uintptr_t>(staging) & 255)) return FK_ERR_WORKSPACE;
+    if (c->dims.tokens == 0) return FK_OK;
+    if (!c->hidden || !c->out || !c->logits || !c->topk_ids || !c->topk_weights) return FK_ERR_ARG;
+    cudaStream_t s = (cudaStream_t)stream;
+    size_t T = c->dims.tokens, H = c->dims.hidden, E = c->dims.experts, k = c->dims.top_k;
+    size_t es = c->hidden_dtype == FK_F32 ? 4 : 2;
+    size_t o = 0;
+    auto take = [&](size_t bytes) { void* p = reinterpret_cast<char*>(staging) + o; o += align256(bytes); return p; };
+    void* d_hidden = take(T * H * es);
+    float* d_out = (float*)take(T * H * 4);
+    float* d_layer = (float*)take(T * H * 4);
+    float* d_logits = (float*)take(T * E * 4);
+    int64_t* d_ids = (int64_t*)take(T * k * 8);
+    float* d_w = (float*)take(T * k * 4);
+    FK_CUDA_OK(cudaMemcpyAsync(d_hidden, c->hidden, T * H * es, cudaMemcpyHostToDevice, s), "h2d hidden");
+    fk_moe_call dev = *c;
+    dev.hidden = d_hidden; dev.out = d_out; dev.layer_hidden = c->layer_hidden ? d_layer : nullptr;
+    dev.logits = d_logits; dev.topk_ids = d_ids; dev.topk_weights = d_w;
+    int st = fk_moe_layer(&dev, stream);
+    if (st != FK_OK) return st;
+    FK_CUDA_OK(cudaMemcpyAsync(c->out, d_out, T * H * 4, cudaMemcpyDeviceToHost, s), "d2h out");
+    if (c->layer_hidden) FK_CUDA_OK(cudaMemcpyAsync(c->layer_hidden, d_layer, T * H * 4, cudaMemcpyDeviceToHost, s), "d2h layer");
+    FK_CUDA_OK(cudaMemcpyAsync(c->logits, d_logits, T * E * 4, cudaMemcpyDeviceToHost, s), "d2h logits");
+    FK_CUDA_OK(cudaMemcpyAsync(c->topk_ids, d_ids, T * k * 8, cudaMemcpyDeviceToHost, s), "d2h ids");
+    FK_CUDA_OK(cudaMemcpyAsync(c->topk_weights, d_w, T * k * 4, cudaMemcpyDeviceToHost, s), "d2h weights");
+    return FK_OK;
+}
+
+int fk_single_expert_mlp(const void* hidden, int hidden_dtype, const void* gate_up, const void* down, int weight_dtype,
+                         float* out, int hidden_size, int intermediate, void* workspace, size_t workspace_bytes,
+                         void* stream) {
+    // one token through one expert == a layer with no routed experts whose "shared expert" is this expert
+    fk_moe_call c{};
+    c.dims = fk_moe_dims{1, hidden_size, 1, intermediate, 0};
+    c.hidden_dtype = hidden_dtype;
+    c.weight_dtype = weight_dtype;
+    c.hidden = hidden;
+    c.shared_gate_up = gate_up;
+    c.shared_down = down;
+    c.out = out;
+    c.workspace = workspace;
+    c.workspace_bytes = workspace_bytes;
+    if (!gate_up || !down) return FK_ERR_ARG;
+    return fk_moe_experts(&c, stream);
+}
+
+int fk_fused_swiglu(const void* gate_up, void* out, int dtype, int64_t rows, int intermediate, void* stream) {
+    if (!dtype_ok(dtype)) return FK_ERR_UNSUPPORTED;
+    if (rows > 0 && intermediate > 0 && (!gate_up || !out)) return FK_ERR_ARG;
+    return launch_swiglu(gate_up, out, dtype, rows, intermediate, (cudaStream_t)stream);
+}
+
+int fk_expert_histogram(const void* ids, int ids_are_int64, int64_t count, int num_experts, int32_t* counts, void* stream) {
+    if (!counts || (count > 0 && !ids)) return FK_ERR_ARG;
+    return launch_histogram(ids, ids_are_int64, count, num_experts, counts, (cudaStream_t)stream);
+}
+
+int fk_moe_permute(const int64_t* topk_ids, int tokens, int top_k, int num_experts, int32_t* counts, int32_t* offsets,
+                   int32_t* order, void* workspace, size_t workspace_bytes, void* stream) {
+    (void)workspace; (void)workspace_bytes;
+    if (!topk_ids || !counts || !offsets || !order || tokens < 0 || top_k < 1) return FK_ERR_ARG;
+    PermuteParams pp{};
+    pp.ids64 = reinterpret_cast<const long long*>(topk_ids);
+    pp.routes = tokens * top_k;
+    pp.E = num_experts;
+    pp.skip_foreign = 1;
+    pp.counts = counts; pp.offsets = offsets; pp.order = order;
+    return launch_permute(pp, (cudaStream_t)stream);
+}
+
+}  // extern "C"

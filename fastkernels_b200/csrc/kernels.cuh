@@ -1,0 +1,75 @@
+// Parameter blocks and host launchers of the individual kernels (internal to libfkmoe).
+#pragma once
+
+#include "common.cuh"
+
+namespace fk {
+
+struct RouterParams {
+    const void* hidden;
+    int hidden_dtype;
+    const void* norm_weight;
+    const void* router_weight;
+    const float* router_bias;          // optional
+    const void* shared_gate_weight;    // optional
+    float* logits;
+    long long* topk_ids;
+    float* topk_weights;
+    int* ids32;                        // optional int32 copy of the ids (workspace)
+    float* shared_gate_out;            // optional f32 [T]
+    unsigned* tickets;
+    int T, H, E, top_k;
+    float eps, norm_offset;
+};
+int launch_router(const RouterParams& p, int weight_dtype, cudaStream_t stream);
+
+struct PermuteParams {
+    const long long* ids64;   // one of ids64 / ids32 is set
+    const int* ids32;
+    int routes;               // T*k
+    int E;                    // local experts
+    int expert_base;          // ids are global; local id = id - expert_base
+    int skip_foreign;         // 1: ids outside the local range are dropped, 0: clamped into range
+    int* counts;              // [E]
+    int* offsets;             // [E+1]
+    int* touched;             // [E+1] (optional)
+    int* order;               // [routes]: packed row -> route (rows beyond offsets[E] are unused)
+    int* inv;                 // [routes]: route -> packed row, -1 if dropped (optional)
+    int* meta;                // [0] = number of experts with count>0 (optional)
+};
+int launch_permute(const PermuteParams& p, cudaStream_t stream);
+int launch_histogram(const void* ids, int ids_are_int64, long long count, int E, int* counts, cudaStream_t stream);
+
+struct ExpertParams {
+    const void* hidden;
+    int hidden_dtype;
+    const void* gate_up;          // [E,2I,H]
+    const void* down;             // [E,H,I]
+    const void* shared_gate_up;   // optional
+    const void* shared_down;
+    int T, H, E, I, top_k;
+    int routes;                   // T*k
+    const int* counts;
+    const int* offsets;
+    const int* touched;
+    const int* order;
+    const int* inv;
+    const int* meta;
+    const float* topk_weights;    // [T,k]
+    const float* shared_gate;     // optional f32 [T] (already sigmoid)
+    float* act;                   // [(routes+T), I]
+    float* y;                     // [(routes+T), H]
+    float* out;                   // [T,H]
+    float* layer_hidden;          // optional [T,H]
+};
+// shape-agnostic kernels (any dtype, any H/I)
+int launch_experts_generic(const ExpertParams& p, int weight_dtype, cudaStream_t stream);
+// bf16 weight-streaming grouped GEMV (H,I in {256,512,1024,2048})
+bool gemv_path_supported(const ExpertParams& p, int weight_dtype);
+int launch_experts_gemv(const ExpertParams& p, cudaStream_t stream);
+// ordered weighted combine of the per-row outputs (+ shared expert, + residual)
+int launch_combine(const ExpertParams& p, cudaStream_t stream);
+
+int launch_swiglu(const void* gate_up, void* out, int dtype, long long rows, int I, cudaStream_t stream);
+
+}  // namespace fk

@@ -1,0 +1,246 @@
+// Router: RMSNorm * (offset + w) -> GEMV over [E,H] -> (+bias) -> softmax -> top-k -> renormalise,
+// plus the shared-expert gate sigmoid(g . x).  One launch.
+//
+// Grid (expert tiles, token tiles).  A block holds its tokens' activations in shared memory as
+// fp32, computes one expert row per warp for all of them, and writes the logits.  The last block
+// to finish a token tile (a self-resetting ticket in the workspace) runs softmax + top-k for those
+// tokens, one warp per token, so no second launch and no spin-wait is needed.
+//
+// Reference semantics: src/fastkernels/reference/qwen36_real.py:23-28, :333-337; the Triton
+// kernels this replaces are src/fastkernels/kernels/triton/qwen36_router.py:113-187.
+// Tie rule: equal probabilities go to the LOWER expert index.
+
+#include "common.cuh"
+#include "kernels.cuh"
+
+namespace fk {
+
+constexpr int kRouterWarps = 8;
+
+template <typename WT, int VW>
+__device__ __forceinline__ void load_vec(const WT* p, float (&out)[VW]);
+
+template <>
+__device__ __forceinline__ void load_vec<float, 1>(const float* p, float (&o)[1]) { o[0] = *p; }
+template <>
+__device__ __forceinline__ void load_vec<__nv_bfloat16, 1>(const __nv_bfloat16* p, float (&o)[1]) { o[0] = __bfloat162float(*p); }
+template <>
+__device__ __forceinline__ void load_vec<__half, 1>(const __half* p, float (&o)[1]) { o[0] = __half2float(*p); }
+template <>
+__device__ __forceinline__ void load_vec<float, 4>(const float* p, float (&o)[4]) {
+    float4 v = *reinterpret_cast<const float4*>(p);
+    o[0] = v.x; o[1] = v.y; o[2] = v.z; o[3] = v.w;
+}
+template <>
+__device__ __forceinline__ void load_vec<__nv_bfloat16, 8>(const __nv_bfloat16* p, float (&o)[8]) {
+    uint4 v = *reinterpret_cast<const uint4*>(p);
+    o[0] = bf16lo(v.x); o[1] = bf16hi(v.x); o[2] = bf16lo(v.y); o[3] = bf16hi(v.y);
+    o[4] = bf16lo(v.z); o[5] = bf16hi(v.z); o[6] = bf16lo(v.w); o[7] = bf16hi(v.w);
+}
+template <>
+__device__ __forceinline__ void load_vec<__half, 8>(const __half* p, float (&o)[8]) {
+    uint4 v = *reinterpret_cast<const uint4*>(p);
+    const __half2* h = reinterpret_cast<const __half2*>(&v);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        float2 f = __half22float2(h[i]);
+        o[2 * i] = f.x; o[2 * i + 1] = f.y;
+    }
+}
+
+// softmax + top-k of one token's logits by one warp.  EPL = experts per lane (E <= 32*EPL).
+template <int EPL>
+__device__ void topk_warp(const float* __restrict__ logits_row, int E, int top_k, long long* ids_out,
+                          int* ids32_out, float* weights_out) {
+    const int lane = threadIdx.x & 31;
+    float v[EPL];
+    float m = -INFINITY;
+#pragma unroll
+    for (int j = 0; j < EPL; ++j) {
+        int e = j * 32 + lane;
+        v[j] = e < E ? __ldcg(logits_row + e) : -INFINITY;
+        m = fmaxf(m, v[j]);
+    }
+    m = warp_max(m);
+    float s = 0.f;
+#pragma unroll
+    for (int j = 0; j < EPL; ++j) {
+        int e = j * 32 + lane;
+        v[j] = e < E ? expf(v[j] - m) : 0.f;
+        s += v[j];
+    }
+    s = warp_sum(s);
+#pragma unroll
+    for (int j = 0; j < EPL; ++j) {
+        int e = j * 32 + lane;
+        v[j] = e < E ? v[j] / s : -1.f;      // probabilities; padding can never win
+    }
+    float sel_v[FK_MAX_TOP_K];
+    int sel_i[FK_MAX_TOP_K];
+    float total = 0.f;
+#pragma unroll
+    for (int r = 0; r < FK_MAX_TOP_K; ++r) {
+        sel_v[r] = 0.f;
+        sel_i[r] = 0;
+        if (r < top_k) {
+            float bv = -2.f;
+            int bi = 0x7fffffff;
+#pragma unroll
+            for (int j = 0; j < EPL; ++j) {
+                if (v[j] > bv) { bv = v[j]; bi = j * 32 + lane; }   // strict: lowest index within the lane
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                float ov = __shfl_xor_sync(kFull, bv, o);
+                int oi = __shfl_xor_sync(kFull, bi, o);
+                if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+            }
+#pragma unroll
+            for (int j = 0; j < EPL; ++j) {
+                if (j * 32 + lane == bi) v[j] = -1.f;
+            }
+            sel_v[r] = bv;
+            sel_i[r] = bi;
+            total += bv;
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < FK_MAX_TOP_K; ++r) {
+        if (r < top_k && lane == r) {
+            ids_out[r] = sel_i[r];
+            if (ids32_out) ids32_out[r] = sel_i[r];
+            weights_out[r] = sel_v[r] / total;
+        }
+    }
+}
+
+template <typename WT, int VW, int TPB>
+__global__ void __launch_bounds__(kRouterWarps * 32)
+router_kernel(RouterParams p) {
+    extern __shared__ float smem[];
+    float* xs = smem;                         // [TPB][H]
+    float* rstd = smem + (size_t)TPB * p.H;   // [TPB]
+    __shared__ int is_last;
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int tok0 = blockIdx.y * TPB;
+    const int H = p.H, E = p.E;
+    const WT* norm_w = reinterpret_cast<const WT*>(p.norm_weight);
+    const WT* router_w = reinterpret_cast<const WT*>(p.router_weight);
+
+    for (int i = tid; i < TPB * H; i += blockDim.x) {
+        int t = i / H, h = i - t * H;
+        int token = tok0 + t;
+        xs[i] = token < p.T ? load_any(p.hidden, p.hidden_dtype, (size_t)token * H + h) : 0.f;
+    }
+    __syncthreads();
+    // mean square per token (warps 0..TPB-1); shared-expert gate (remaining warps of expert tile 0)
+    for (int t = warp; t < TPB; t += kRouterWarps) {
+        float ss = 0.f;
+        for (int h = lane; h < H; h += 32) ss += xs[t * H + h] * xs[t * H + h];
+        ss = warp_sum(ss);
+        if (lane == 0) rstd[t] = rsqrtf(ss / (float)H + p.eps);
+    }
+    if (blockIdx.x == 0 && p.shared_gate_weight != nullptr && p.shared_gate_out != nullptr) {
+        const WT* g = reinterpret_cast<const WT*>(p.shared_gate_weight);
+        for (int t = warp; t < TPB; t += kRouterWarps) {
+            float acc = 0.f;
+            for (int h = lane; h < H; h += 32) acc += to_float(g[h]) * xs[t * H + h];
+            acc = warp_sum(acc);
+            if (lane == 0 && tok0 + t < p.T) p.shared_gate_out[tok0 + t] = sigmoidf_(acc);
+        }
+    }
+    __syncthreads();
+
+    const int e = blockIdx.x * kRouterWarps + warp;
+    if (e < E) {
+        float acc[TPB];
+#pragma unroll
+        for (int t = 0; t < TPB; ++t) acc[t] = 0.f;
+        const WT* wrow = router_w + (size_t)e * H;
+        for (int h = lane * VW; h < H; h += 32 * VW) {
+            float w[VW], nw[VW];
+            load_vec<WT, VW>(wrow + h, w);
+            load_vec<WT, VW>(norm_w + h, nw);
+#pragma unroll
+            for (int i = 0; i < VW; ++i) w[i] *= (p.norm_offset + nw[i]);
+#pragma unroll
+            for (int t = 0; t < TPB; ++t) {
+#pragma unroll
+                for (int i = 0; i < VW; ++i) acc[t] = fmaf(w[i], xs[t * H + h + i], acc[t]);
+            }
+        }
+#pragma unroll
+        for (int t = 0; t < TPB; ++t) {
+            float v = warp_sum(acc[t]);
+            if (lane == 0 && tok0 + t < p.T) {
+                float logit = v * rstd[t];
+                if (p.router_bias) logit += p.router_bias[e];
+                p.logits[(size_t)(tok0 + t) * E + e] = logit;
+            }
+        }
+    }
+
+    // ticket: the last expert-tile block of this token tile selects the top-k
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+        unsigned t = atomicAdd(p.tickets + blockIdx.y, 1u);
+        is_last = (t == gridDim.x - 1);
+        if (is_last) p.tickets[blockIdx.y] = 0u;    // re-arm for the next launch
+    }
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    for (int t = warp; t < TPB; t += kRouterWarps) {
+        int token = tok0 + t;
+        if (token >= p.T) continue;
+        const float* row = p.logits + (size_t)token * E;
+        long long* ids = p.topk_ids + (size_t)token * p.top_k;
+        int* ids32 = p.ids32 ? p.ids32 + (size_t)token * p.top_k : nullptr;
+        float* wts = p.topk_weights + (size_t)token * p.top_k;
+        if (E <= 256) topk_warp<8>(row, E, p.top_k, ids, ids32, wts);
+        else topk_warp<32>(row, E, p.top_k, ids, ids32, wts);
+    }
+}
+
+template <typename WT, int VW>
+static int launch_router_t(const RouterParams& p, cudaStream_t stream) {
+    dim3 block(kRouterWarps * 32);
+    if (p.T <= 64) {
+        constexpr int TPB = 4;
+        size_t smem = sizeof(float) * ((size_t)TPB * p.H + TPB);
+        dim3 grid((p.E + kRouterWarps - 1) / kRouterWarps, (p.T + TPB - 1) / TPB);
+        auto kern = router_kernel<WT, VW, TPB>;
+        FK_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), "router attr");
+        kern<<<grid, block, smem, stream>>>(p);
+    } else {
+        constexpr int TPB = 8;
+        size_t smem = sizeof(float) * ((size_t)TPB * p.H + TPB);
+        dim3 grid((p.E + kRouterWarps - 1) / kRouterWarps, (p.T + TPB - 1) / TPB);
+        auto kern = router_kernel<WT, VW, TPB>;
+        FK_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), "router attr");
+        kern<<<grid, block, smem, stream>>>(p);
+    }
+    FK_LAUNCH_OK("router launch");
+    return FK_OK;
+}
+
+int launch_router(const RouterParams& p, int weight_dtype, cudaStream_t stream) {
+    if (p.T <= 0) return FK_OK;
+    if ((p.T + 3) / 4 > kMaxTokenTiles) return FK_ERR_ARG;
+    const bool aligned = ((reinterpret_cast<uintptr_t>(p.router_weight) | reinterpret_cast<uintptr_t>(p.norm_weight)) & 15) == 0;
+    switch (weight_dtype) {
+        case FK_F32:
+            return (aligned && p.H % 4 == 0) ? launch_router_t<float, 4>(p, stream) : launch_router_t<float, 1>(p, stream);
+        case FK_BF16:
+            return (aligned && p.H % 8 == 0) ? launch_router_t<__nv_bfloat16, 8>(p, stream)
+                                             : launch_router_t<__nv_bfloat16, 1>(p, stream);
+        case FK_F16:
+            return (aligned && p.H % 8 == 0) ? launch_router_t<__half, 8>(p, stream) : launch_router_t<__half, 1>(p, stream);
+        default:
+            return FK_ERR_UNSUPPORTED;
+    }
+}
+
+}  // namespace fk

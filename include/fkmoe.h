@@ -1,0 +1,161 @@
+/* fkmoe.h -- C ABI of libfkmoe.so: the Qwen3.6 MoE decode layer on B200 (sm_100a).
+ *
+ * Every entry point takes raw DEVICE pointers (unless its name ends in _host),
+ * sizes, a dtype code and a CUDA stream (passed as void*; NULL = legacy default
+ * stream).  Entry points never allocate, never synchronise and never throw:
+ * they enqueue kernels on `stream` and return an fk_status.  Scratch memory is
+ * a caller-owned workspace of fk_moe_workspace_bytes() bytes that must have been
+ * cleared once with fk_moe_workspace_init() and must not be shared by calls
+ * that overlap on the GPU.
+ *
+ * Each declaration names the reference interface it replaces; paths are
+ * relative to the reference project's root (suryavanshi/fastkernels).
+ *
+ * Layouts (all row-major contiguous, weights in one dtype per call):
+ *   hidden [T,H]   norm_weight [H]   router_weight [E,H]
+ *   expert_gate_up [E,2I,H] (gate rows 0..I-1, up rows I..2I-1)   expert_down [E,H,I]
+ *   shared_gate_up [2I,H]   shared_down [H,I]   shared_gate [H]
+ *   logits f32 [T,E]   topk_ids i64 [T,k]   topk_weights f32 [T,k]   out f32 [T,H]
+ */
+#ifndef FKMOE_H
+#define FKMOE_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum fk_dtype { FK_F32 = 0, FK_BF16 = 1, FK_F16 = 2 };
+
+enum fk_status {
+    FK_OK = 0,
+    FK_ERR_ARG = 1,          /* null pointer, bad size, limit exceeded */
+    FK_ERR_UNSUPPORTED = 2,  /* dtype / shape combination not built */
+    FK_ERR_WORKSPACE = 3,    /* workspace too small or misaligned */
+    FK_ERR_CUDA = 4,         /* a CUDA runtime call failed (launch error) */
+    FK_ERR_TIMEOUT = 5       /* a bounded device-side wait gave up */
+};
+
+/* Limits carried over from the reference wrappers
+ * (src/fastkernels/kernels/triton/qwen36_router.py:280-288, qwen36_expert.py:850, :1137). */
+#define FK_MAX_TOP_K 8
+#define FK_MAX_HIDDEN 4096
+#define FK_MAX_EXPERTS 1024
+#define FK_MAX_INTERMEDIATE 1024
+
+typedef struct fk_moe_dims {
+    int32_t tokens;        /* T */
+    int32_t hidden;        /* H */
+    int32_t experts;       /* E (routed experts held by this call's weight tensors) */
+    int32_t intermediate;  /* I */
+    int32_t top_k;         /* k */
+} fk_moe_dims;
+
+/* flags for fk_moe_call.flags */
+#define FK_FLAG_FORCE_GENERIC 1u   /* use the shape-agnostic kernels even where a fast path exists */
+#define FK_FLAG_FORCE_GEMV 2u      /* never use the tensor-core grouped GEMM */
+#define FK_FLAG_FORCE_TENSOR 4u    /* use the tensor-core grouped GEMM whenever the shape allows */
+#define FK_FLAG_NO_FUSED_DECODE 8u /* T==1: run the staged kernels instead of the fused single-token kernel */
+#define FK_FLAG_SKIP_FOREIGN 16u   /* ids outside [expert_base, expert_base+E) are skipped instead of clamped */
+
+typedef struct fk_moe_call {
+    fk_moe_dims dims;
+    int32_t hidden_dtype;          /* fk_dtype of `hidden` */
+    int32_t weight_dtype;          /* fk_dtype of every weight tensor */
+    float eps;                     /* RMSNorm epsilon (reference default 1e-6) */
+    float norm_offset;             /* router norm gain is (norm_offset + norm_weight); reference default 1.0 */
+    uint32_t flags;
+    int32_t expert_base;           /* expert-parallel shard: ids in [expert_base, expert_base+E) are local,
+                                      others are skipped (0 for a whole layer) */
+    const void* hidden;
+    const void* norm_weight;
+    const void* router_weight;
+    const float* router_bias;      /* optional f32 [E] added to the logits, or NULL */
+    const void* expert_gate_up;
+    const void* expert_down;
+    const void* shared_gate_up;    /* NULL: no shared expert */
+    const void* shared_down;
+    const void* shared_gate;       /* NULL: shared expert is not gated */
+    const int64_t* topk_ids_in;    /* fk_moe_experts only: routing given by the caller */
+    const float* topk_weights_in;
+    float* out;                    /* f32 [T,H]: the MoE update */
+    float* layer_hidden;           /* optional f32 [T,H]: hidden + update, or NULL */
+    float* logits;                 /* f32 [T,E] */
+    int64_t* topk_ids;             /* i64 [T,k] */
+    float* topk_weights;           /* f32 [T,k] */
+    void* workspace;
+    size_t workspace_bytes;
+} fk_moe_call;
+
+/* Library identification and error text. */
+int fk_version(void);
+const char* fk_status_string(int status);
+/* Text of the last CUDA error seen by this thread inside the library ("" if none). */
+const char* fk_last_cuda_error(void);
+
+/* Scratch size for a call with these dims (0 on invalid dims); and the one-time clear. */
+size_t fk_moe_workspace_bytes(const fk_moe_dims* dims);
+int fk_moe_workspace_init(void* workspace, size_t bytes, void* stream);
+
+/* Router: RMSNorm * (norm_offset + w) -> GEMV [E,H] -> (+bias) -> softmax -> top-k (ties to the
+ * lower expert index) -> renormalise.  Uses call->{hidden,norm_weight,router_weight,router_bias,
+ * logits,topk_ids,topk_weights}.
+ * Replaces triton_qwen36_moe_router_decode / triton_qwen36_batched_moe_router_decode
+ * (src/fastkernels/kernels/triton/qwen36_router.py:193, :260); oracle
+ * src/fastkernels/reference/qwen36_real.py:333-337. */
+int fk_moe_router(const fk_moe_call* call, void* stream);
+
+/* Routed experts (+ optional shared expert, + optional sigmoid gate) for routing given in
+ * call->topk_ids_in / topk_weights_in; writes call->out (and layer_hidden if set).
+ * Replaces triton_qwen36_{,batched_}routed_experts_decode and
+ * triton_qwen36_{,batched_}routed_shared_experts_decode
+ * (src/fastkernels/kernels/triton/qwen36_expert.py:889, :969, :1096, :1181); oracle
+ * src/fastkernels/reference/qwen36_real.py:339-353.  Out-of-range expert ids are clamped
+ * as the reference kernels do (qwen36_expert.py:485) unless expert_base/E select a shard. */
+int fk_moe_experts(const fk_moe_call* call, void* stream);
+
+/* Whole layer: router -> routed + shared experts (-> residual).
+ * Replaces triton_qwen36_moe_decode / triton_qwen36_batched_moe_decode
+ * (qwen36_expert.py:1312, :1353) and triton_qwen36_batched_moe_layer_decode
+ * (src/fastkernels/kernels/triton/qwen36_layer.py:55); oracle qwen36_real_moe_update
+ * (src/fastkernels/reference/qwen36_real.py:329-354). */
+int fk_moe_layer(const fk_moe_call* call, void* stream);
+
+/* Same as fk_moe_layer, but hidden/out/layer_hidden/logits/topk_ids/topk_weights are HOST
+ * pointers (pinned memory recommended); weights and workspace stay device pointers.
+ * `staging` is a device buffer of fk_moe_host_staging_bytes(dims, hidden_dtype) bytes.  The copies are enqueued on
+ * `stream`; the caller synchronises the stream before reading the results. */
+size_t fk_moe_host_staging_bytes(const fk_moe_dims* dims, int hidden_dtype);
+int fk_moe_layer_host(const fk_moe_call* call, void* staging, size_t staging_bytes, void* stream);
+
+/* Single expert MLP for one token: out f32 [H] = Wd (silu(Wg x) * (Wu x)).
+ * Replaces triton_qwen36_single_expert_mlp_decode (qwen36_expert.py:817). */
+int fk_single_expert_mlp(const void* hidden, int hidden_dtype, const void* gate_up, const void* down,
+                         int weight_dtype, float* out, int hidden_size, int intermediate,
+                         void* workspace, size_t workspace_bytes, void* stream);
+
+/* out[n,c] = silu(gate_up[n,c]) * gate_up[n,I+c], fp32 math, stored in the input dtype.
+ * Replaces triton_fused_swiglu (src/fastkernels/kernels/triton/moe.py:67); oracle
+ * reference_fused_swiglu (src/fastkernels/reference/moe.py:16). */
+int fk_fused_swiglu(const void* gate_up, void* out, int dtype, int64_t rows, int intermediate, void* stream);
+
+/* counts[e] = number of ids equal to e (ids outside [0,E) are ignored); counts is int32 [E].
+ * Replaces triton_expert_histogram (src/fastkernels/kernels/triton/moe.py:87); oracle
+ * reference_expert_histogram (src/fastkernels/reference/moe.py:24). */
+int fk_expert_histogram(const void* ids, int ids_are_int64, int64_t count, int num_experts,
+                        int32_t* counts, void* stream);
+
+/* Histogram, exclusive offsets and the stable expert-major order of the T*k routes:
+ * order = argsort(ids.flatten(), stable).  counts i32 [E], offsets i32 [E+1], order i32 [T*k].
+ * The reference has no packing function (docs/QWEN36_MEGAKERNEL_PLAN.md:142-149 lists it as
+ * future work); this is the packing step its grouped-expert plan describes. */
+int fk_moe_permute(const int64_t* topk_ids, int tokens, int top_k, int num_experts,
+                   int32_t* counts, int32_t* offsets, int32_t* order,
+                   void* workspace, size_t workspace_bytes, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FKMOE_H */

@@ -1,0 +1,416 @@
+"""GPU parity: every stage of the MoE decode layer against the CPU oracle, through the C ABI.
+
+The stage list follows the reference's own CUDA tests (tests/test_triton_moe.py:57-681, :1112-1157):
+swiglu, histogram, router (single/batched, fp32/bf16), single expert, routed, routed+shared, shared
+gate, full MoE, layer residual, tiny fused block.  Inputs are seeded; real-shape cases use
+H=2048, E=256, I=512, k=8 like the reference.
+"""
+
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import moe_oracle as O
+from oracle.pin_against_reference import CASES, ROUTER_CASES
+from fastkernels_b200 import _lib
+from fastkernels_b200.kernels.triton import (
+    triton_expert_histogram,
+    triton_fused_swiglu,
+    triton_qwen36_batched_moe_decode,
+    triton_qwen36_batched_moe_layer_decode,
+    triton_qwen36_batched_moe_router_decode,
+    triton_qwen36_batched_routed_experts_decode,
+    triton_qwen36_batched_routed_shared_experts_decode,
+    triton_qwen36_moe_decode,
+    triton_qwen36_moe_router_decode,
+    triton_qwen36_routed_experts_decode,
+    triton_qwen36_routed_shared_experts_decode,
+    triton_qwen36_single_expert_mlp_decode,
+    triton_synthetic_qwen36_moe_decode,
+)
+from fastkernels_b200.moe import expert_permutation
+from fastkernels_b200.spec import MoESpec, MoEWeights
+from fastkernels_b200.workloads import HOT_EXPERT_IDS, make_hidden, make_moe_weights
+from tests.parity import check_output, check_routing, oracle_layer
+from tests.tolerances import default_tolerance
+
+pytestmark = pytest.mark.gpu
+GOLDEN = Path(__file__).parent / "golden"
+REAL = MoESpec()
+FIXED_IDS = list(HOT_EXPERT_IDS)
+
+
+@pytest.fixture(scope="module")
+def real_bf16():
+    return make_moe_weights(0, REAL, dtype=torch.bfloat16, device="cuda")
+
+
+@pytest.fixture(scope="module")
+def real_bf16_biased():
+    return make_moe_weights(1, REAL, dtype=torch.bfloat16, device="cuda", bias_std=0.5)
+
+
+def _randn(*shape, dtype, seed=0, scale=1.0):
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    return (scale * torch.randn(*shape, generator=g, device="cuda", dtype=torch.float32)).to(dtype)
+
+
+# ---------------------------------------------------------------- stand-alone ops
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32, torch.float16])
+def test_fused_swiglu_matches_oracle(dtype):
+    gate_up = _randn(128, 1024, dtype=dtype)
+    cand = triton_fused_swiglu(gate_up)
+    ref = O.fused_swiglu(gate_up.cpu().float()).to(dtype)
+    assert cand.dtype == dtype and cand.shape == (128, 512)
+    atol, rtol = default_tolerance(dtype)
+    torch.testing.assert_close(cand.cpu(), ref, atol=atol, rtol=rtol)
+
+
+@pytest.mark.parametrize("idtype", [torch.int32, torch.int64])
+def test_expert_histogram_bit_exact(idtype):
+    g = torch.Generator().manual_seed(0)
+    ids = torch.randint(0, 256, (64, 8), generator=g, dtype=idtype)
+    cand = triton_expert_histogram(ids.cuda(), 256)
+    assert cand.dtype == torch.int32
+    assert torch.equal(cand.cpu(), O.expert_histogram(ids, 256))
+
+
+@pytest.mark.parametrize("tokens,experts", [(1, 256), (7, 5), (64, 256), (256, 256), (2048, 32), (300, 1024)])
+def test_expert_permutation_bit_exact(tokens, experts):
+    g = torch.Generator().manual_seed(tokens)
+    ids = torch.randint(0, experts, (tokens, 8), generator=g)
+    if tokens == 256:
+        ids[:200, 0] = 17          # one hot expert
+    counts, offsets, order = expert_permutation(ids.cuda(), experts)
+    rc, ro, rord = O.expert_permutation(ids, experts)
+    assert torch.equal(counts.cpu(), rc) and torch.equal(offsets.cpu(), ro) and torch.equal(order.cpu(), rord)
+
+
+# ---------------------------------------------------------------- router
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_router_single_token_real_shape(dtype):
+    hidden = _randn(2048, dtype=dtype, seed=1)
+    norm_w = _randn(2048, dtype=dtype, seed=2, scale=0.02)
+    router_w = _randn(256, 2048, dtype=dtype, seed=3, scale=0.02)
+    logits, ids, weights = triton_qwen36_moe_router_decode(hidden, norm_w, router_w, top_k=8)
+    assert logits.shape == (256,) and ids.dtype == torch.int64 and weights.dtype == torch.float32
+    rl, rid, rw = O.router(hidden.cpu().unsqueeze(0), norm_w.cpu(), router_w.cpu(), top_k=8)
+    atol, rtol = default_tolerance(torch.float32)
+    torch.testing.assert_close(logits.cpu(), rl[0], atol=atol, rtol=rtol)
+    own_ids, own_w = O.route_from_logits(logits.cpu().unsqueeze(0), 8)
+    assert torch.equal(ids.cpu(), own_ids[0])
+    assert torch.equal(ids.cpu(), rid[0])
+    torch.testing.assert_close(weights.cpu(), rw[0], atol=1e-5, rtol=1e-4)
+
+
+@pytest.mark.parametrize("name", list(ROUTER_CASES))
+def test_router_matches_reference_golden(name):
+    tokens, dtype, seed = ROUTER_CASES[name]
+    gold = np.load(GOLDEN / f"{name}.npz")
+    g = torch.Generator().manual_seed(seed)
+    hidden = torch.randn(tokens, 2048, generator=g).to(dtype)
+    norm_w = (0.02 * torch.randn(2048, generator=g)).to(dtype)
+    router_w = (0.02 * torch.randn(256, 2048, generator=g)).to(dtype)
+    logits, ids, weights = triton_qwen36_batched_moe_router_decode(hidden.cuda(), norm_w.cuda(), router_w.cuda())
+    np.testing.assert_allclose(logits.cpu().numpy(), gold["logits"], atol=1e-4, rtol=1e-4)
+    clear = torch.from_numpy(gold["margin"]) > 2e-6
+    assert torch.equal(ids.cpu()[clear], torch.from_numpy(gold["topk_ids"])[clear])
+    np.testing.assert_allclose(weights.cpu().numpy()[clear.numpy()], gold["topk_weights"][clear.numpy()], atol=1e-5, rtol=1e-4)
+
+
+@pytest.mark.parametrize("tokens", [4, 33, 256])
+def test_router_batched_with_bias_and_offset(tokens):
+    dtype = torch.bfloat16
+    hidden = _randn(tokens, 2048, dtype=dtype, seed=4)
+    norm_w = _randn(2048, dtype=dtype, seed=5, scale=0.02)
+    router_w = _randn(256, 2048, dtype=dtype, seed=6, scale=0.02)
+    bias = _randn(256, dtype=torch.float32, seed=7, scale=0.5)
+    for off in (1.0, 0.0):
+        nw = norm_w if off == 1.0 else (norm_w + 1).to(dtype)
+        logits, ids, weights = triton_qwen36_batched_moe_router_decode(hidden, nw, router_w, norm_offset=off,
+                                                                       router_bias=bias)
+        rl, rid, rw = O.router(hidden.cpu(), nw.cpu(), router_w.cpu(), top_k=8, norm_offset=off, router_bias=bias.cpu())
+        torch.testing.assert_close(logits.cpu(), rl, atol=1e-4, rtol=1e-4)
+        own_ids, own_w = O.route_from_logits(logits.cpu(), 8)
+        assert torch.equal(ids.cpu(), own_ids)
+        torch.testing.assert_close(weights.cpu(), own_w, atol=1e-6, rtol=1e-5)
+
+
+@pytest.mark.parametrize("top_k", [1, 2, 5, 8])
+def test_router_exact_ties_go_to_lower_index(top_k):
+    # identical router rows give bit-identical logits: groups {0,1,2,3} and {100..103} tie exactly
+    dtype = torch.bfloat16
+    hidden = _randn(3, 2048, dtype=dtype, seed=8)
+    router_w = _randn(256, 2048, dtype=dtype, seed=9, scale=0.02)
+    router_w[1:4] = router_w[0]
+    router_w[101:104] = router_w[100]
+    norm_w = torch.zeros(2048, device="cuda", dtype=dtype)
+    bias = torch.zeros(256, device="cuda")
+    bias[0:4] = 4.0
+    bias[100:104] = 3.0
+    logits, ids, weights = triton_qwen36_batched_moe_router_decode(hidden, norm_w, router_w, top_k=top_k, router_bias=bias)
+    lc = logits.cpu()
+    assert torch.equal(lc[:, 0], lc[:, 1]) and torch.equal(lc[:, 100], lc[:, 103])
+    expect = [0, 1, 2, 3, 100, 101, 102, 103][:top_k]
+    assert ids.cpu().tolist() == [expect] * 3
+    own_ids, _ = O.route_from_logits(lc, top_k)
+    assert torch.equal(ids.cpu(), own_ids)
+    # all logits equal: the first k experts win
+    z = torch.zeros(256, 2048, device="cuda", dtype=dtype)
+    _, ids0, w0 = triton_qwen36_batched_moe_router_decode(hidden, norm_w, z, top_k=top_k)
+    assert ids0.cpu().tolist() == [list(range(top_k))] * 3
+    torch.testing.assert_close(w0.cpu(), torch.full((3, top_k), 1.0 / top_k))
+
+
+def test_router_odd_shapes_and_many_experts():
+    for (T, H, E, k, dtype) in [(3, 200, 24, 5, torch.float32), (2, 100, 1000, 8, torch.bfloat16), (5, 16, 4, 2, torch.float16)]:
+        hidden = _randn(T, H, dtype=dtype, seed=10)
+        norm_w = _randn(H, dtype=dtype, seed=11, scale=0.1)
+        router_w = _randn(E, H, dtype=dtype, seed=12, scale=0.1)
+        logits, ids, weights = triton_qwen36_batched_moe_router_decode(hidden, norm_w, router_w, top_k=k)
+        rl, rid, rw = O.router(hidden.cpu(), norm_w.cpu(), router_w.cpu(), top_k=k)
+        torch.testing.assert_close(logits.cpu(), rl, atol=1e-4, rtol=1e-4)
+        own_ids, own_w = O.route_from_logits(logits.cpu(), k)
+        assert torch.equal(ids.cpu(), own_ids)
+
+
+# ---------------------------------------------------------------- experts with fixed routing
+def _fixed_routing(tokens):
+    ids = torch.tensor([[(i + t) % 256 for i in FIXED_IDS] for t in range(tokens)], dtype=torch.int64)
+    ids[:, -1] = torch.arange(255, 255 - tokens, -1)
+    g = torch.Generator().manual_seed(3)
+    w = torch.rand(tokens, 8, generator=g) + 0.1
+    return ids.cuda(), (w / w.sum(-1, keepdim=True)).cuda()
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_single_expert_mlp(dtype):
+    hidden = _randn(2048, dtype=dtype, seed=1)
+    gu = _randn(1024, 2048, dtype=dtype, seed=2, scale=0.02)
+    dn = _randn(2048, 512, dtype=dtype, seed=3, scale=0.02)
+    out = triton_qwen36_single_expert_mlp_decode(hidden, gu, dn)
+    assert out.dtype == torch.float32 and out.shape == (2048,)
+    ref = O.expert_mlp(hidden.cpu().unsqueeze(0), gu.cpu(), dn.cpu())[0]
+    check_output(out, ref, dtype)
+
+
+@pytest.mark.parametrize("shared,gated", [(False, False), (True, False), (True, True)])
+def test_routed_experts_single_token_fixed_ids(real_bf16, shared, gated):
+    w = real_bf16
+    hidden = _randn(2048, dtype=torch.bfloat16, seed=5)
+    ids, wts = _fixed_routing(1)
+    if shared:
+        out = triton_qwen36_routed_shared_experts_decode(hidden, ids[0], wts[0], w.expert_gate_up_weight, w.expert_down_weight,
+                                                         w.shared_gate_up_weight, w.shared_down_weight,
+                                                         w.shared_expert_gate_weight if gated else None)
+    else:
+        out = triton_qwen36_routed_experts_decode(hidden, ids[0], wts[0], w.expert_gate_up_weight, w.expert_down_weight)
+    sel = ids[0].cpu()
+    ref = O.routed_experts(hidden.cpu().unsqueeze(0), torch.arange(8).unsqueeze(0), wts.cpu(),
+                           w.expert_gate_up_weight[sel.cuda()].cpu(), w.expert_down_weight[sel.cuda()].cpu())
+    if shared:
+        ref = ref + O.shared_expert(hidden.cpu().unsqueeze(0), w.shared_gate_up_weight.cpu(), w.shared_down_weight.cpu(),
+                                    w.shared_expert_gate_weight.cpu() if gated else None)
+    check_output(out, ref[0], torch.bfloat16)
+
+
+@pytest.mark.parametrize("tokens", [2, 4, 19])
+@pytest.mark.parametrize("shared,gated", [(False, False), (True, True)])
+def test_routed_experts_batched_fixed_ids(real_bf16, tokens, shared, gated):
+    w = real_bf16
+    hidden = _randn(tokens, 2048, dtype=torch.bfloat16, seed=6)
+    ids, wts = _fixed_routing(tokens)
+    if shared:
+        out = triton_qwen36_batched_routed_shared_experts_decode(hidden, ids, wts, w.expert_gate_up_weight, w.expert_down_weight,
+                                                                 w.shared_gate_up_weight, w.shared_down_weight,
+                                                                 w.shared_expert_gate_weight if gated else None)
+    else:
+        out = triton_qwen36_batched_routed_experts_decode(hidden, ids, wts, w.expert_gate_up_weight, w.expert_down_weight)
+    uniq, local = torch.unique(ids.cpu(), return_inverse=True)
+    ref = O.routed_experts(hidden.cpu(), local, wts.cpu(), w.expert_gate_up_weight[uniq.cuda()].cpu(),
+                           w.expert_down_weight[uniq.cuda()].cpu())
+    if shared:
+        ref = ref + O.shared_expert(hidden.cpu(), w.shared_gate_up_weight.cpu(), w.shared_down_weight.cpu(),
+                                    w.shared_expert_gate_weight.cpu() if gated else None)
+    check_output(out, ref, torch.bfloat16)
+
+
+def test_out_of_range_ids_are_clamped(real_bf16):
+    w = real_bf16
+    hidden = _randn(2, 2048, dtype=torch.bfloat16, seed=7)
+    ids, wts = _fixed_routing(2)
+    bad = ids.clone()
+    bad[0, 0] = 999
+    bad[1, 1] = -5
+    fixed = ids.clone()
+    fixed[0, 0] = 255
+    fixed[1, 1] = 0
+    a = triton_qwen36_batched_routed_experts_decode(hidden, bad, wts, w.expert_gate_up_weight, w.expert_down_weight)
+    b = triton_qwen36_batched_routed_experts_decode(hidden, fixed, wts, w.expert_gate_up_weight, w.expert_down_weight)
+    assert torch.equal(a, b)
+
+
+# ---------------------------------------------------------------- whole layer
+@pytest.mark.parametrize("tokens", [1, 4, 16, 32])
+def test_full_layer_bf16_real_shape(real_bf16_biased, tokens):
+    w = real_bf16_biased
+    hidden = make_hidden(100 + tokens, tokens, REAL, dtype=torch.bfloat16, device="cuda")
+    out, logits, ids, weights = triton_qwen36_batched_moe_decode(hidden, *w.tuple(), top_k=8, router_bias=w.router_bias)
+    ref = oracle_layer(hidden, w, 8)
+    check_routing(logits, ids, weights, ref, torch.bfloat16)
+    if torch.equal(ids.cpu(), ref.topk_ids):
+        check_output(out, ref.output, torch.bfloat16)
+    hist = triton_expert_histogram(ids, 256)
+    assert torch.equal(hist.cpu(), O.expert_histogram(ids.cpu(), 256))
+    # bitwise run-to-run determinism
+    out2, _, ids2, _ = triton_qwen36_batched_moe_decode(hidden, *w.tuple(), top_k=8, router_bias=w.router_bias)
+    assert torch.equal(out, out2) and torch.equal(ids, ids2)
+
+
+def test_full_layer_single_token_api(real_bf16):
+    w = real_bf16
+    hidden = make_hidden(7, 1, REAL, dtype=torch.bfloat16, device="cuda")[0]
+    out, logits, ids, weights = triton_qwen36_moe_decode(hidden, *w.tuple())
+    assert out.shape == (2048,) and logits.shape == (256,) and ids.shape == (8,)
+    ref = oracle_layer(hidden.unsqueeze(0), w, 8)
+    check_routing(logits.unsqueeze(0), ids.unsqueeze(0), weights.unsqueeze(0), ref, torch.bfloat16)
+    check_output(out, ref.output[0], torch.bfloat16)
+    # ungated shared expert
+    out_u, _, _, _ = triton_qwen36_moe_decode(hidden, *w.tuple()[:6], None)
+    w_u = MoEWeights(*w.tuple()[:6], None)
+    check_output(out_u, oracle_layer(hidden.unsqueeze(0), w_u, 8).output[0], torch.bfloat16)
+
+
+@pytest.mark.parametrize("flags", [_lib.FLAG_FORCE_GENERIC])
+def test_full_layer_generic_kernels_agree(real_bf16, flags):
+    w = real_bf16
+    hidden = make_hidden(9, 3, REAL, dtype=torch.bfloat16, device="cuda")
+    fast, _, ids_f, _ = triton_qwen36_batched_moe_decode(hidden, *w.tuple())
+    slow, _, ids_s, _ = triton_qwen36_batched_moe_decode(hidden, *w.tuple(), flags=flags)
+    assert torch.equal(ids_f, ids_s)
+    torch.testing.assert_close(fast, slow, atol=2e-5, rtol=1e-4)
+
+
+def test_full_layer_fp32_hidden_with_bf16_weights(real_bf16):
+    w = real_bf16
+    hidden = make_hidden(11, 4, REAL, dtype=torch.float32, device="cuda")
+    out, logits, ids, weights = triton_qwen36_batched_moe_decode(hidden, *w.tuple())
+    ref = oracle_layer(hidden, w, 8)
+    check_routing(logits, ids, weights, ref, torch.bfloat16)
+    check_output(out, ref.output, torch.bfloat16)
+
+
+def test_layer_residual(real_bf16):
+    w = real_bf16
+    hidden = make_hidden(13, 4, REAL, dtype=torch.bfloat16, device="cuda")
+    layer, update, logits, ids, weights = triton_qwen36_batched_moe_layer_decode(hidden, *w.tuple())
+    assert layer.dtype == torch.float32
+    torch.testing.assert_close(layer, hidden.float() + update, atol=0, rtol=0)
+    ref = oracle_layer(hidden, w, 8)
+    check_output(update, ref.output, torch.bfloat16)
+
+
+@pytest.mark.parametrize("name", list(CASES))
+def test_full_layer_matches_reference_golden(name):
+    spec, tokens, dtype, seed, bias_std = CASES[name]
+    gold = np.load(GOLDEN / f"moe_{name}.npz")
+    w = make_moe_weights(seed, spec, dtype=dtype, bias_std=bias_std).to("cuda")
+    hidden = make_hidden(seed, tokens, spec, dtype=dtype).cuda()
+    out, logits, ids, weights = triton_qwen36_batched_moe_decode(hidden, *w.tuple(), top_k=spec.num_routed_experts,
+                                                                 router_bias=w.router_bias)
+    np.testing.assert_allclose(logits.cpu().numpy(), gold["logits"], atol=1e-4, rtol=1e-4)
+    clear = torch.from_numpy(gold["margin"]) > 2e-6
+    assert torch.equal(ids.cpu()[clear], torch.from_numpy(gold["topk_ids"])[clear])
+    if bool(clear.all()):
+        assert torch.equal(triton_expert_histogram(ids, spec.num_experts).cpu(), torch.from_numpy(gold["histogram"]))
+        check_output(out, torch.from_numpy(gold["output"]), dtype)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("top_k", [1, 2, 4, 8])
+def test_synthetic_tiny_block(dtype, top_k):
+    spec = MoESpec(hidden_size=16, num_experts=8 if top_k > 4 else 4, num_routed_experts=top_k, expert_intermediate_size=8)
+    w = make_moe_weights(20 + top_k, spec, dtype=dtype, device="cuda", shared_gate=False, scale=0.2)
+    norm_w = torch.ones(16, device="cuda", dtype=dtype)
+    hidden = make_hidden(21, 1, spec, dtype=dtype, device="cuda")[0]
+    out = triton_synthetic_qwen36_moe_decode(hidden, norm_w, w.router_weight, w.expert_gate_up_weight, w.expert_down_weight,
+                                             w.shared_gate_up_weight, w.shared_down_weight, top_k=top_k)
+    assert out.dtype == dtype and out.shape == hidden.shape
+    ref = O.synthetic_moe_decode(hidden.cpu(), norm_w.cpu(), w.router_weight.cpu(), w.expert_gate_up_weight.cpu(),
+                                 w.expert_down_weight.cpu(), w.shared_gate_up_weight.cpu(), w.shared_down_weight.cpu(), top_k=top_k)
+    atol, rtol = default_tolerance(dtype)
+    torch.testing.assert_close(out.float().cpu(), ref, atol=atol, rtol=rtol)
+
+
+def test_synthetic_tiny_block_golden_and_256_experts():
+    g = np.load(GOLDEN / "synthetic_tiny.npz")
+    t = {k: torch.from_numpy(g[k]).cuda() for k in g.files}
+    out = triton_synthetic_qwen36_moe_decode(t["hidden"], t["norm_weight"], t["router_weight"], t["expert_gate_up_weight"],
+                                             t["expert_down_weight"], t["shared_gate_up_weight"], t["shared_down_weight"], top_k=2)
+    torch.testing.assert_close(out.cpu(), t["output"].cpu(), atol=1e-5, rtol=1e-4)
+    spec = MoESpec(hidden_size=16, num_experts=256, num_routed_experts=8, expert_intermediate_size=8)
+    w = make_moe_weights(30, spec, dtype=torch.float32, device="cuda", shared_gate=False, scale=0.2)
+    hidden = make_hidden(31, 1, spec, dtype=torch.float32, device="cuda")[0]
+    norm_w = torch.ones(16, device="cuda")
+    out = triton_synthetic_qwen36_moe_decode(hidden, norm_w, w.router_weight, w.expert_gate_up_weight, w.expert_down_weight,
+                                             w.shared_gate_up_weight, w.shared_down_weight, top_k=8)
+    ref = O.synthetic_moe_decode(hidden.cpu(), norm_w.cpu(), w.router_weight.cpu(), w.expert_gate_up_weight.cpu(),
+                                 w.expert_down_weight.cpu(), w.shared_gate_up_weight.cpu(), w.shared_down_weight.cpu(), top_k=8)
+    torch.testing.assert_close(out.cpu(), ref, atol=1e-4, rtol=1e-4)
+
+
+# ---------------------------------------------------------------- edge cases and full-size properties
+def test_empty_batch(real_bf16):
+    w = real_bf16
+    hidden = torch.empty(0, 2048, device="cuda", dtype=torch.bfloat16)
+    out, logits, ids, weights = triton_qwen36_batched_moe_decode(hidden, *w.tuple())
+    assert out.shape == (0, 2048) and logits.shape == (0, 256) and ids.shape == (0, 8)
+    assert triton_expert_histogram(ids, 256).sum().item() == 0
+
+
+def test_all_tokens_on_the_same_experts(real_bf16):
+    # ragged extreme: every token routes to the same 8 experts (one group of 24 rows each)
+    w = real_bf16
+    tokens = 24
+    hidden = _randn(tokens, 2048, dtype=torch.bfloat16, seed=40)
+    ids = torch.tensor([FIXED_IDS] * tokens, device="cuda")
+    wts = torch.full((tokens, 8), 0.125, device="cuda")
+    out = triton_qwen36_batched_routed_experts_decode(hidden, ids, wts, w.expert_gate_up_weight, w.expert_down_weight)
+    sel = torch.tensor(FIXED_IDS)
+    ref = O.routed_experts(hidden.cpu(), torch.arange(8).repeat(tokens, 1), wts.cpu(),
+                           w.expert_gate_up_weight[sel.cuda()].cpu(), w.expert_down_weight[sel.cuda()].cpu())
+    check_output(out, ref, torch.bfloat16)
+
+
+@pytest.mark.parametrize("tokens,hot", [(64, False), (256, False), (256, True)])
+def test_full_size_batches_properties(tokens, hot):
+    """Largest single-GPU batches: routing bit-exact on the kernel's own logits, histogram sums,
+    linearity in the routing weights, token-order independence, and oracle parity on a token sample."""
+    w = make_moe_weights(2, REAL, dtype=torch.bfloat16, device="cuda", hot_experts=HOT_EXPERT_IDS if hot else None)
+    hidden = make_hidden(200 + tokens, tokens, REAL, dtype=torch.bfloat16, device="cuda")
+    out, logits, ids, weights = triton_qwen36_batched_moe_decode(hidden, *w.tuple(), router_bias=w.router_bias)
+    own_ids, own_w = O.route_from_logits(logits.cpu(), 8)
+    assert torch.equal(ids.cpu(), own_ids)
+    hist = triton_expert_histogram(ids, 256)
+    assert int(hist.sum()) == tokens * 8
+    assert torch.equal(hist.cpu(), O.expert_histogram(ids.cpu(), 256))
+    if hot:
+        assert int(hist.cpu()[list(HOT_EXPERT_IDS)].sum()) > tokens * 8 // 4
+    # permuting the tokens permutes the outputs (bitwise: per-token math does not depend on batch order)
+    perm = torch.randperm(tokens, generator=torch.Generator().manual_seed(1)).cuda()
+    out_p, _, ids_p, _ = triton_qwen36_batched_moe_decode(hidden[perm], *w.tuple(), router_bias=w.router_bias)
+    assert torch.equal(ids_p, ids[perm])
+    torch.testing.assert_close(out_p, out[perm], atol=1e-5, rtol=1e-4)
+    # linearity of the routed part in the routing weights
+    r1 = triton_qwen36_batched_routed_experts_decode(hidden, ids, weights, w.expert_gate_up_weight, w.expert_down_weight)
+    r2 = triton_qwen36_batched_routed_experts_decode(hidden, ids, 2 * weights, w.expert_gate_up_weight, w.expert_down_weight)
+    torch.testing.assert_close(r2, 2 * r1, atol=1e-6, rtol=1e-5)
+    # oracle parity on a sample of tokens (the oracle needs only the experts those tokens use)
+    sample = torch.arange(0, tokens, max(1, tokens // 8))
+    ref = oracle_layer(hidden[sample.cuda()], w, 8)
+    clear = ref.margin > 2e-6
+    assert torch.equal(ids.cpu()[sample][clear], ref.topk_ids[clear])
+    if bool(clear.all()):
+        check_output(out[sample.cuda()], ref.output, torch.bfloat16)
