@@ -1,0 +1,357 @@
+#!/usr/bin/env python
+"""Benchmark of the Qwen3.6 MoE decode layer on B200 (one JSON line on stdout).
+
+    python bench.py --gpus N --steps K --warmup W [--batch B] [--impl reference]
+
+A step is one MoE layer call (router -> top-8 -> routed + shared experts) over one batch of
+synthetic decode tokens.  Shapes are the real layer (hidden 2048, 256 experts, top-8,
+intermediate 512, gated shared expert); weights ~ N(0, 0.02) bf16, hidden ~ N(0, 1) bf16, router
+logit bias ~ N(0, 0.5).  Consecutive steps use different layers' weights (a rotation of several
+resident copies, as a decoder stack does), so no step finds its weights in L2.
+
+value      tokens/s with the step's input already in HBM (CUDA events around the K steps).
+e2e        the same through the host-buffer entry point: every step copies its hidden batch from
+           pinned host memory, runs the layer and copies output, ids and weights back, then waits.
+roofline   the dominant kernel (gate_up GEMV + SwiGLU): its algorithmic bytes / its mean duration
+           (CUDA events between the stages of the same steps), against the measured copy bandwidth.
+cpu_baseline  the oracle port of the reference's PyTorch CPU path on this box's host cores.
+
+--impl reference times that CPU path alone (all host threads) on the same workload.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+METRIC = "moe_layer_decode_tokens_per_s"
+UNIT = "tokens/s"
+FALLBACK_HBM_GBS = 6650.0
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=60)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--impl", default="own", choices=["own", "reference"])
+    ap.add_argument("--batch", type=int, default=32, help="decode tokens per GPU per step")
+    ap.add_argument("--layers", type=int, default=6, help="resident weight copies rotated between steps")
+    ap.add_argument("--no-sweep", action="store_true", help="skip the per-batch sweep (1..256 tokens)")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--flags", type=int, default=0)
+    return ap.parse_args()
+
+
+def measured_peak():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        try:
+            return float(json.loads(p.read_text())["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return FALLBACK_HBM_GBS, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clock/throttle samples while a timed region runs (read-only queries)."""
+
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.proc = None
+        self.lines: list[str] = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                                          "-i", str(self.index), "-lms", "100"], stdout=subprocess.PIPE, text=True)
+            threading.Thread(target=self._pump, daemon=True).start()
+        except Exception:
+            self.proc = None
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        sm, smax, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 9:
+                continue
+            try:
+                sm.append(float(parts[1]))
+                smax.append(float(parts[2]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[5:9]):
+                if val.lower() == "active":
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(smax) if smax else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+# --------------------------------------------------------------------------------------------- CPU arm
+def cpu_weights(seed: int, bias_std: float):
+    import torch
+    from fastkernels_b200.spec import MoESpec
+    from fastkernels_b200.workloads import make_moe_weights
+    dev = "cuda" if torch.cuda.is_available() else "cpu"
+    w = make_moe_weights(seed, MoESpec(), dtype=torch.bfloat16, device=dev, bias_std=bias_std)
+    return w.to("cpu") if dev == "cuda" else w
+
+
+def time_cpu_port(weights, hidden_cpu, *, budget_s: float = 20.0, min_reps: int = 2):
+    """Seconds per call of the oracle's token-loop port on `hidden_cpu` (all host threads)."""
+    import torch
+    from oracle import moe_oracle as O
+    threads = os.cpu_count() or 1
+    torch.set_num_threads(threads)
+    args = weights.tuple()
+    O.moe_update_token_loop(hidden_cpu[:1], *args, top_k=8, router_bias=weights.router_bias)   # warm-up
+    times = []
+    t_end = time.perf_counter() + budget_s
+    while len(times) < min_reps or (time.perf_counter() < t_end and len(times) < 8):
+        t0 = time.perf_counter()
+        O.moe_update_token_loop(hidden_cpu, *args, top_k=8, router_bias=weights.router_bias)
+        times.append(time.perf_counter() - t0)
+    return statistics.median(times), threads, len(times)
+
+
+def cpu_sample_tokens(batch: int) -> int:
+    return min(batch, 32)
+
+
+def run_reference(args):
+    """The reference's CPU implementation of the path (oracle port), timed on the host cores."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    import torch
+    from fastkernels_b200.spec import MoESpec
+    from fastkernels_b200.workloads import make_hidden
+    spec = MoESpec()
+    batch = args.batch
+    sample = cpu_sample_tokens(batch)
+    w = cpu_weights(0, 0.5)
+    from oracle import moe_oracle as O
+    threads = os.cpu_count() or 1
+    torch.set_num_threads(threads)
+    steps = max(1, min(args.steps, 12))
+    warm = max(1, min(args.warmup, 2))
+    hs = [make_hidden(1000 + i, sample, spec, dtype=torch.bfloat16) for i in range(4)]
+    for i in range(warm):
+        O.moe_update_token_loop(hs[i % 4], *w.tuple(), top_k=8, router_bias=w.router_bias)
+    t0 = time.perf_counter()
+    for i in range(steps):
+        O.moe_update_token_loop(hs[i % 4], *w.tuple(), top_k=8, router_bias=w.router_bias)
+    dt = (time.perf_counter() - t0) / steps
+    # a step of the full workload is `batch * n_gpus` tokens; the token loop is linear in tokens
+    tokens_per_s = sample / dt
+    total = batch * args.gpus
+    line = {
+        "impl": "reference", "metric": METRIC, "value": tokens_per_s, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": steps, "warmup": warm, "ms_per_step": dt * 1e3 * total / sample, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": workload_config(batch, args.gpus, args.layers),
+        "cpu_baseline": {"value": tokens_per_s, "unit": UNIT, "cores": threads, "kind": "port",
+                         "sample": f"{sample} of {total} tokens per step, {steps} steps; token x route loop is linear in tokens"},
+        "e2e": {"value": tokens_per_s, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(batch: int, gpus: int, layers: int) -> dict:
+    which = "configs[1]" if batch <= 32 else "configs[2]"
+    if gpus > 1:
+        which = "configs[3]-style expert parallel"
+    return {"workload": f"Qwen3.6 MoE layer decode, bf16, {batch} tokens per GPU ({which})", "hidden": 2048,
+            "experts": 256, "top_k": 8, "intermediate": 512, "tokens_per_gpu": batch, "global_tokens": batch * gpus,
+            "router_bias_std": 0.5, "parallelism": "single GPU" if gpus == 1 else f"ep{gpus}",
+            "l2": f"weights rotate over {layers} resident layer copies per GPU; a step's weights were last touched "
+                  f"{layers} steps earlier, more than L2 apart"}
+
+
+# --------------------------------------------------------------------------------------------- own arm
+def distinct_experts(ids) -> int:
+    import torch
+    return int(torch.unique(ids).numel())
+
+
+def time_steps(plans, hiddens, steps: int, warmup: int):
+    """CUDA-event time of `steps` layer calls rotating over plans/hidden batches; returns ms per step."""
+    import torch
+    n, m = len(plans), len(hiddens)
+    for i, p in enumerate(plans):          # inputs are resident before the timed region starts
+        p.hidden.copy_(hiddens[i % m])
+    for i in range(warmup):
+        plans[i % n].run()
+    torch.cuda.synchronize()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for i in range(steps):
+        plans[i % n].run()
+    stop.record()
+    torch.cuda.synchronize()
+    return start.elapsed_time(stop) / steps
+
+
+def run_single(args):
+    import torch
+    from fastkernels_b200 import _lib
+    from fastkernels_b200.plan import MoEDecodePlan
+    from fastkernels_b200.spec import MoESpec
+    from fastkernels_b200.workloads import algorithmic_bytes, make_hidden, make_moe_weights
+
+    lib = _lib.load()                      # fails loudly if the CUDA library is missing
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py needs a CUDA device; there is no CPU path in the product")
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    spec = MoESpec()
+    peak, peak_src = measured_peak()
+    B, K, W, L = args.batch, args.steps, max(args.warmup, 3), args.layers
+
+    weights = [make_moe_weights(layer, spec, dtype=torch.bfloat16, device=dev, bias_std=0.5) for layer in range(L)]
+    pool = 8
+    hid_host = [make_hidden(1000 + i, B, spec, dtype=torch.bfloat16).pin_memory() for i in range(pool)]
+    hid_dev = [h.to(dev) for h in hid_host]
+
+    def plans_for(tokens):
+        ps = [MoEDecodePlan(w, tokens, flags=args.flags) for w in weights]
+        for p in ps:
+            p.capture()
+        return ps
+
+    plans = plans_for(B)
+    sampler = ClockSampler(local)
+    sampler.start()
+    ms = time_steps(plans, hid_dev, K, W)
+    # the timed steps replay CUDA graphs, which bypass the library's launch counter: count the
+    # kernels one direct call enqueues (the graph holds exactly these) and multiply by the steps
+    c0 = lib.fk_launch_count()
+    plans[0].launch()
+    per_call = lib.fk_launch_count() - c0
+    torch.cuda.synchronize()
+    launches = per_call * K
+
+    # per-stage durations of the same steps (events between the kernels), for the roofline
+    stage_sum = None
+    for i in range(W):
+        plans[i % L].timed()
+    ucount = []
+    for i in range(K):
+        p = plans[i % L]
+        st = p.timed()
+        stage_sum = st if stage_sum is None else [a + b for a, b in zip(stage_sum, st)]
+        if i < L * pool:
+            ucount.append(distinct_experts(p.topk_ids))
+    clocks = sampler.stop()
+    stage_ms = [s / K for s in stage_sum]
+    stage_names = ["router", "permute", "gate_up", "down", "combine"][:len(stage_ms)]
+    U = statistics.mean(ucount)
+    layer_bytes = algorithmic_bytes(spec, B, 0) + U * spec.expert_bytes_bf16
+    H, I = spec.hidden_size, spec.expert_intermediate_size
+    gate_up_bytes = (U + 1) * 2 * I * H * 2 + B * H * 2
+    dom = stage_names.index("gate_up") if "gate_up" in stage_names else 0
+    dom_ms = stage_ms[dom]
+    achieved = gate_up_bytes / (dom_ms * 1e-3) / 1e9
+    roofline = {"bound": "hbm", "kernel": "gate_up_gemv_kernel (gate_up GEMV + SwiGLU)", "achieved": achieved,
+                "peak": peak, "peak_source": peak_src, "unit": "GB/s", "frac": achieved / peak,
+                "algorithmic_bytes_per_launch": gate_up_bytes, "ms_per_launch": dom_ms, "traffic": None,
+                "stages_ms": dict(zip(stage_names, stage_ms)),
+                "layer": {"algorithmic_bytes": layer_bytes, "achieved": layer_bytes / (ms * 1e-3) / 1e9,
+                          "frac": layer_bytes / (ms * 1e-3) / 1e9 / peak, "distinct_experts": U}}
+
+    # end to end through the host-buffer entry point
+    out_host = torch.empty(B, H, dtype=torch.float32).pin_memory()
+    ids_host = torch.empty(B, 8, dtype=torch.int64).pin_memory()
+    w_host = torch.empty(B, 8, dtype=torch.float32).pin_memory()
+    for i in range(W):
+        plans[i % L].run_host(hid_host[i % pool], out_host, ids_host, w_host)
+        torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(K):
+        plans[i % L].run_host(hid_host[i % pool], out_host, ids_host, w_host)
+        torch.cuda.current_stream().synchronize()
+    e1.record()
+    torch.cuda.synchronize()
+    e2e_ms = e0.elapsed_time(e1) / K
+    wall_ms = (time.perf_counter() - t0) * 1e3 / K
+    e2e = {"value": B / (max(e2e_ms, wall_ms) * 1e-3), "unit": UNIT, "ms_per_step": max(e2e_ms, wall_ms),
+           "h2d_bytes_per_step": B * H * 2, "d2h_bytes_per_step": B * H * 4 + B * 8 * 12}
+
+    sweep = []
+    if not args.no_sweep:
+        for b in (1, 4, 16, 32, 64, 128, 256):
+            ps = plans if b == B else plans_for(b)
+            hs = [make_hidden(2000 + i, b, spec, dtype=torch.bfloat16, device=dev) for i in range(pool)]
+            t = time_steps(ps, hs, max(20, K // 2), W)
+            us = []
+            for i in range(min(L, 2)):
+                ps[i].run(hs[i])
+                torch.cuda.synchronize()
+                us.append(distinct_experts(ps[i].topk_ids))
+            u = statistics.mean(us)
+            by = algorithmic_bytes(spec, b, 0) + u * spec.expert_bytes_bf16
+            sweep.append({"batch": b, "us_per_step": t * 1e3, "tokens_per_s": b / (t * 1e-3), "distinct_experts": u,
+                          "algorithmic_bytes": by, "achieved_gbs": by / (t * 1e-3) / 1e9,
+                          "frac_of_hbm_peak": by / (t * 1e-3) / 1e9 / peak})
+            if b != B:
+                del ps
+
+    cpu = None
+    if not args.no_cpu:
+        sample = cpu_sample_tokens(B)
+        wc = weights[0].to("cpu")
+        sec, threads, reps = time_cpu_port(wc, hid_host[0][:sample].clone(), budget_s=15.0)
+        cpu = {"value": sample / sec, "unit": UNIT, "cores": threads, "kind": "port",
+               "sample": f"{sample} of {B} tokens of one step, median of {reps} calls of the token x route loop "
+                         f"(fp32 PyTorch on the host cores)", "ms_per_call": sec * 1e3}
+
+    line = {
+        "metric": METRIC, "value": B / (ms * 1e-3), "unit": UNIT, "n_gpus": 1, "steps": K, "warmup": W,
+        "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic", "config": workload_config(B, 1, L), "roofline": roofline, "cpu_baseline": cpu,
+        "e2e": e2e, "gpu_launches": int(launches), "launches_per_step": int(per_call), "clocks": clocks,
+        "sweep": sweep,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    args = parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+        return
+    if args.gpus > 1 or int(os.environ.get("WORLD_SIZE", "1")) > 1:
+        from fastkernels_b200.ep_bench import run_ep
+        run_ep(args, workload_config, measured_peak, ClockSampler, METRIC, UNIT)
+        return
+    run_single(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -47,6 +47,8 @@ SIGNATURES = {
     "fk_version": (C.c_int, []),
     "fk_status_string": (C.c_char_p, [C.c_int]),
     "fk_last_cuda_error": (C.c_char_p, []),
+    "fk_launch_count": (C.c_uint64, []),
+    "fk_moe_layer_timed": (C.c_int, [C.POINTER(Call), C.c_void_p, C.POINTER(C.c_float), C.POINTER(C.c_int)]),
     "fk_moe_workspace_bytes": (C.c_size_t, [C.POINTER(Dims)]),
     "fk_moe_workspace_init": (C.c_int, [C.c_void_p, C.c_size_t, C.c_void_p]),
     "fk_moe_router": (C.c_int, [C.POINTER(Call), C.c_void_p]),

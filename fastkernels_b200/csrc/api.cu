@@ -9,6 +9,10 @@
 namespace fk {
 
 static thread_local char g_last_error[256] = "";
+static unsigned long long g_launches = 0;
+thread_local StageTimer* g_stage_timer = nullptr;
+
+void note_launch() { __atomic_fetch_add(&g_launches, 1ull, __ATOMIC_RELAXED); }
 
 void note_cuda_error(cudaError_t e, const char* where) {
     snprintf(g_last_error, sizeof(g_last_error), "%s: %s", where, cudaGetErrorString(e));
@@ -55,6 +59,7 @@ static int run_experts(const fk_moe_call* c, const Workspace& w, const long long
     pp.meta = at<int>(ws, w.meta);
     int st = launch_permute(pp, stream);
     if (st != FK_OK) return st;
+    stage_mark();   // end of permute
 
     ExpertParams ep{};
     ep.hidden = c->hidden;
@@ -77,7 +82,9 @@ static int run_experts(const fk_moe_call* c, const Workspace& w, const long long
     const bool fast = !(c->flags & FK_FLAG_FORCE_GENERIC) && gemv_path_supported(ep, c->weight_dtype);
     st = fast ? launch_experts_gemv(ep, stream) : launch_experts_generic(ep, c->weight_dtype, stream);
     if (st != FK_OK) return st;
-    return launch_combine(ep, stream);
+    st = launch_combine(ep, stream);
+    stage_mark();   // end of combine
+    return st;
 }
 
 // sigmoid(g . x) per token for callers that skip the router (fk_moe_experts with a gate)
@@ -114,6 +121,26 @@ const char* fk_status_string(int status) {
 }
 
 const char* fk_last_cuda_error(void) { return g_last_error; }
+
+uint64_t fk_launch_count(void) { return __atomic_load_n(&g_launches, __ATOMIC_RELAXED); }
+
+int fk_moe_layer_timed(const fk_moe_call* c, void* stream, float* stage_ms, int* stages) {
+    if (!stage_ms || !stages) return FK_ERR_ARG;
+    StageTimer t{};
+    t.stream = (cudaStream_t)stream;
+    for (int i = 0; i < 12; ++i) FK_CUDA_OK(cudaEventCreate(&t.ev[i]), "event create");
+    g_stage_timer = &t;
+    int st = fk_moe_layer(c, stream);
+    g_stage_timer = nullptr;
+    *stages = 0;
+    if (st == FK_OK && t.used >= 2) {
+        FK_CUDA_OK(cudaEventSynchronize(t.ev[t.used - 1]), "event sync");
+        for (int i = 1; i < t.used; ++i) cudaEventElapsedTime(&stage_ms[i - 1], t.ev[i - 1], t.ev[i]);
+        *stages = t.used - 1;
+    }
+    for (int i = 0; i < 12; ++i) cudaEventDestroy(t.ev[i]);
+    return st;
+}
 
 size_t fk_moe_workspace_bytes(const fk_moe_dims* dims) {
     if (dims == nullptr || !dims_ok(*dims, false)) return 0;
@@ -197,8 +224,10 @@ int fk_moe_layer(const fk_moe_call* c, void* stream) {
     rp.tickets = at<unsigned>(c->workspace, w.tickets);
     rp.T = c->dims.tokens; rp.H = c->dims.hidden; rp.E = c->dims.experts; rp.top_k = c->dims.top_k;
     rp.eps = c->eps; rp.norm_offset = c->norm_offset;
+    stage_mark();   // start
     st = launch_router(rp, c->weight_dtype, s);
     if (st != FK_OK) return st;
+    stage_mark();   // end of router
     return run_experts(c, w, rp.topk_ids, c->topk_weights, rp.shared_gate_out, s);
 }
 
@@ -215,7 +244,7 @@ int fk_moe_layer_host(const fk_moe_call* c, void* staging, size_t staging_bytes,
     if (need == 0) return FK_ERR_ARG;
     if (staging_bytes < need || (reinterpret_cast<uintptr_t>(staging) & 255)) return FK_ERR_WORKSPACE;
     if (c->dims.tokens == 0) return FK_OK;
-    if (!c->hidden || !c->out || !c->logits || !c->topk_ids || !c->topk_weights) return FK_ERR_ARG;
+    if (!c->hidden || !c->out) return FK_ERR_ARG;
     cudaStream_t s = (cudaStream_t)stream;
     size_t T = c->dims.tokens, H = c->dims.hidden, E = c->dims.experts, k = c->dims.top_k;
     size_t es = c->hidden_dtype == FK_F32 ? 4 : 2;
@@ -235,9 +264,9 @@ int fk_moe_layer_host(const fk_moe_call* c, void* staging, size_t staging_bytes,
     if (st != FK_OK) return st;
     FK_CUDA_OK(cudaMemcpyAsync(c->out, d_out, T * H * 4, cudaMemcpyDeviceToHost, s), "d2h out");
     if (c->layer_hidden) FK_CUDA_OK(cudaMemcpyAsync(c->layer_hidden, d_layer, T * H * 4, cudaMemcpyDeviceToHost, s), "d2h layer");
-    FK_CUDA_OK(cudaMemcpyAsync(c->logits, d_logits, T * E * 4, cudaMemcpyDeviceToHost, s), "d2h logits");
-    FK_CUDA_OK(cudaMemcpyAsync(c->topk_ids, d_ids, T * k * 8, cudaMemcpyDeviceToHost, s), "d2h ids");
-    FK_CUDA_OK(cudaMemcpyAsync(c->topk_weights, d_w, T * k * 4, cudaMemcpyDeviceToHost, s), "d2h weights");
+    if (c->logits) FK_CUDA_OK(cudaMemcpyAsync(c->logits, d_logits, T * E * 4, cudaMemcpyDeviceToHost, s), "d2h logits");
+    if (c->topk_ids) FK_CUDA_OK(cudaMemcpyAsync(c->topk_ids, d_ids, T * k * 8, cudaMemcpyDeviceToHost, s), "d2h ids");
+    if (c->topk_weights) FK_CUDA_OK(cudaMemcpyAsync(c->topk_weights, d_w, T * k * 4, cudaMemcpyDeviceToHost, s), "d2h weights");
     return FK_OK;
 }
 

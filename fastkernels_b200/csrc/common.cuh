@@ -119,6 +119,20 @@ __device__ __forceinline__ float sigmoidf_(float x) { return 1.0f / (1.0f + expf
 // ---------------------------------------------------------------------------------------------
 namespace fk {
 void note_cuda_error(cudaError_t e, const char* where);
+void note_launch();
+// Optional per-stage timing hook: when set, stage_mark(i) records event i on the stream.
+struct StageTimer {
+    cudaEvent_t ev[12];
+    int used;
+    cudaStream_t stream;
+};
+extern thread_local StageTimer* g_stage_timer;
+inline void stage_mark() {
+    if (g_stage_timer && g_stage_timer->used < 12) {
+        cudaEventRecord(g_stage_timer->ev[g_stage_timer->used], g_stage_timer->stream);
+        g_stage_timer->used++;
+    }
+}
 }
 #define FK_CUDA_OK(expr, where)                          \
     do {                                                 \
@@ -128,4 +142,8 @@ void note_cuda_error(cudaError_t e, const char* where);
             return FK_ERR_CUDA;                          \
         }                                                \
     } while (0)
-#define FK_LAUNCH_OK(where) FK_CUDA_OK(cudaPeekAtLastError(), where)
+#define FK_LAUNCH_OK(where)                              \
+    do {                                                 \
+        fk::note_launch();                               \
+        FK_CUDA_OK(cudaPeekAtLastError(), where);        \
+    } while (0)

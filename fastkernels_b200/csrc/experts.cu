@@ -100,20 +100,27 @@ int launch_experts_generic(const ExpertParams& p, int weight_dtype, cudaStream_t
     switch (weight_dtype) {
         case FK_F32:
             gate_up_generic_kernel<float><<<blocks(gu_warps), 256, 0, stream>>>(p);
+            FK_LAUNCH_OK("generic gate_up launch");
+            stage_mark();
             down_generic_kernel<float><<<blocks(dn_warps), 256, 0, stream>>>(p);
             break;
         case FK_BF16:
             gate_up_generic_kernel<__nv_bfloat16><<<blocks(gu_warps), 256, 0, stream>>>(p);
+            FK_LAUNCH_OK("generic gate_up launch");
+            stage_mark();
             down_generic_kernel<__nv_bfloat16><<<blocks(dn_warps), 256, 0, stream>>>(p);
             break;
         case FK_F16:
             gate_up_generic_kernel<__half><<<blocks(gu_warps), 256, 0, stream>>>(p);
+            FK_LAUNCH_OK("generic gate_up launch");
+            stage_mark();
             down_generic_kernel<__half><<<blocks(dn_warps), 256, 0, stream>>>(p);
             break;
         default:
             return FK_ERR_UNSUPPORTED;
     }
-    FK_LAUNCH_OK("generic experts launch");
+    FK_LAUNCH_OK("generic down launch");
+    stage_mark();
     return FK_OK;
 }
 
@@ -432,6 +439,7 @@ int launch_experts_gemv(const ExpertParams& p, cudaStream_t stream) {
         default: return FK_ERR_UNSUPPORTED;
     }
     FK_LAUNCH_OK("gate_up gemv launch");
+    stage_mark();   // end of gate_up
     switch (p.I / 256) {
         case 1: down_gemv_kernel<1><<<grid, kGemvThreads, 0, stream>>>(p); break;
         case 2: down_gemv_kernel<2><<<grid, kGemvThreads, 0, stream>>>(p); break;
@@ -440,6 +448,7 @@ int launch_experts_gemv(const ExpertParams& p, cudaStream_t stream) {
         default: return FK_ERR_UNSUPPORTED;
     }
     FK_LAUNCH_OK("down gemv launch");
+    stage_mark();   // end of down
     return FK_OK;
 }
 

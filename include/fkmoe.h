@@ -95,6 +95,16 @@ const char* fk_status_string(int status);
 /* Text of the last CUDA error seen by this thread inside the library ("" if none). */
 const char* fk_last_cuda_error(void);
 
+/* Number of kernels this library has launched in this process (all threads, all entry points). */
+uint64_t fk_launch_count(void);
+
+/* Profiling aid, not a hot path: runs fk_moe_layer with CUDA events recorded on `stream`
+ * between its stages, WAITS for the last one, and writes the stage durations in milliseconds
+ * to stage_ms (room for 11) and their number to *stages.  Staged path: router, permute,
+ * gate_up, down, combine.  No counterpart in the reference (it times with a host clock around
+ * a Python loop, e.g. bench/qwen36_real_moe_microbench.py:101-119). */
+int fk_moe_layer_timed(const fk_moe_call* call, void* stream, float* stage_ms, int* stages);
+
 /* Scratch size for a call with these dims (0 on invalid dims); and the one-time clear. */
 size_t fk_moe_workspace_bytes(const fk_moe_dims* dims);
 int fk_moe_workspace_init(void* workspace, size_t bytes, void* stream);
@@ -125,6 +135,7 @@ int fk_moe_layer(const fk_moe_call* call, void* stream);
 
 /* Same as fk_moe_layer, but hidden/out/layer_hidden/logits/topk_ids/topk_weights are HOST
  * pointers (pinned memory recommended); weights and workspace stay device pointers.
+ * layer_hidden, logits, topk_ids and topk_weights may be NULL: that result is then not copied back.
  * `staging` is a device buffer of fk_moe_host_staging_bytes(dims, hidden_dtype) bytes.  The copies are enqueued on
  * `stream`; the caller synchronises the stream before reading the results. */
 size_t fk_moe_host_staging_bytes(const fk_moe_dims* dims, int hidden_dtype);

@@ -197,6 +197,35 @@ def moe_update(hidden, norm_weight, router_weight, expert_gate_up_weight, expert
     return MoEResult(out, logits, ids, weights, expert_histogram(ids, num_experts), margin)
 
 
+def moe_update_token_loop(hidden, norm_weight, router_weight, expert_gate_up_weight, expert_down_weight,
+                          shared_gate_up_weight, shared_down_weight, shared_expert_gate_weight=None, *,
+                          top_k: int = 8, eps: float = 1e-6, router_bias=None) -> torch.Tensor:
+    """The same block with the reference's exact loop structure: token by token, route by route, one
+    matrix-vector product at a time with the weights upcast per use (qwen36_real.py:339-353).
+
+    Numerically it equals `moe_update`; it exists so that the CPU baseline is timed on the
+    reference's own control flow, not on a batched rewrite of it.
+    """
+    x = hidden.float()
+    logits = rms_norm(x, norm_weight, eps) @ router_weight.float().t()
+    if router_bias is not None:
+        logits = logits + router_bias.float()
+    ids, weights = route_from_logits(logits, top_k)
+    out = torch.zeros_like(x)
+    for t in range(x.shape[0]):
+        token = x[t]
+        for r in range(top_k):
+            e = int(ids[t, r].item())
+            gate, up = torch.chunk(expert_gate_up_weight[e].float() @ token, 2, dim=0)
+            out[t] += weights[t, r] * (expert_down_weight[e].float() @ (F.silu(gate) * up))
+        gate, up = torch.chunk(shared_gate_up_weight.float() @ token, 2, dim=0)
+        shared = shared_down_weight.float() @ (F.silu(gate) * up)
+        if shared_expert_gate_weight is not None:
+            shared = shared * torch.sigmoid((shared_expert_gate_weight.float().reshape(-1, x.shape[-1]) @ token)[0])
+        out[t] += shared
+    return out
+
+
 def moe_layer(hidden, *args, **kwargs):
     """`hidden + moe_update(hidden)` in fp32 (src/fastkernels/kernels/triton/qwen36_layer.py:94-105)."""
     res = moe_update(hidden, *args, **kwargs)

@@ -148,8 +148,8 @@ def test_router_exact_ties_go_to_lower_index(top_k):
     router_w[101:104] = router_w[100]
     norm_w = torch.zeros(2048, device="cuda", dtype=dtype)
     bias = torch.zeros(256, device="cuda")
-    bias[0:4] = 4.0
-    bias[100:104] = 3.0
+    bias[0:4] = 40.0
+    bias[100:104] = 30.0
     logits, ids, weights = triton_qwen36_batched_moe_router_decode(hidden, norm_w, router_w, top_k=top_k, router_bias=bias)
     lc = logits.cpu()
     assert torch.equal(lc[:, 0], lc[:, 1]) and torch.equal(lc[:, 100], lc[:, 103])
