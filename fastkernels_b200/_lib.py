@@ -18,6 +18,7 @@ FLAG_FORCE_GEMV = 2
 FLAG_FORCE_TENSOR = 4
 FLAG_NO_FUSED_DECODE = 8
 FLAG_SKIP_FOREIGN = 16
+FLAG_REGISTER_GEMV = 32
 
 
 class Dims(C.Structure):

@@ -57,6 +57,8 @@ static int run_experts(const fk_moe_call* c, const Workspace& w, const long long
     pp.order = at<int>(ws, w.order);
     pp.inv = at<int>(ws, w.inv);
     pp.meta = at<int>(ws, w.meta);
+    pp.passes = at<int4>(ws, w.passes);
+    pp.shared_tokens = c->shared_gate_up ? d.tokens : 0;
     int st = launch_permute(pp, stream);
     if (st != FK_OK) return st;
     stage_mark();   // end of permute
@@ -71,7 +73,7 @@ static int run_experts(const fk_moe_call* c, const Workspace& w, const long long
     ep.T = d.tokens; ep.H = d.hidden; ep.E = d.experts; ep.I = d.intermediate; ep.top_k = d.top_k;
     ep.routes = pp.routes;
     ep.counts = pp.counts; ep.offsets = pp.offsets; ep.touched = pp.touched;
-    ep.order = pp.order; ep.inv = pp.inv; ep.meta = pp.meta;
+    ep.order = pp.order; ep.inv = pp.inv; ep.meta = pp.meta; ep.passes = pp.passes;
     ep.topk_weights = weights;
     ep.shared_gate = shared_gate_sig;
     ep.act = at<float>(ws, w.act);
@@ -79,8 +81,14 @@ static int run_experts(const fk_moe_call* c, const Workspace& w, const long long
     ep.out = c->out;
     ep.layer_hidden = c->layer_hidden;
 
-    const bool fast = !(c->flags & FK_FLAG_FORCE_GENERIC) && gemv_path_supported(ep, c->weight_dtype);
-    st = fast ? launch_experts_gemv(ep, stream) : launch_experts_generic(ep, c->weight_dtype, stream);
+    ep.error_word = at<int>(ws, w.meta) + 2;
+    const bool generic = (c->flags & FK_FLAG_FORCE_GENERIC) != 0;
+    if (!generic && !(c->flags & FK_FLAG_REGISTER_GEMV) && stream_path_supported(ep, c->weight_dtype))
+        st = launch_experts_stream(ep, stream);
+    else if (!generic && gemv_path_supported(ep, c->weight_dtype))
+        st = launch_experts_gemv(ep, stream);
+    else
+        st = launch_experts_generic(ep, c->weight_dtype, stream);
     if (st != FK_OK) return st;
     st = launch_combine(ep, stream);
     stage_mark();   // end of combine

@@ -20,7 +20,7 @@ constexpr int kMaxTokenTiles = 4096;   // ticket slots in the workspace
 struct Workspace {
     size_t tickets;      // u32 [kMaxTokenTiles]   router "last block" tickets (self-resetting)
     size_t counters;     // u32 [64]               misc. counters / barrier words (self-resetting)
-    size_t meta;         // i32 [16]               [0]=U distinct experts hit, [1]=tile count, [2]=error word
+    size_t meta;         // i32 [16]               [0]=U distinct experts hit, [1]=GEMV pass count, [2]=error word
     size_t ids32;        // i32 [R]
     size_t counts;       // i32 [E]
     size_t offsets;      // i32 [E+1]
@@ -28,6 +28,7 @@ struct Workspace {
     size_t order;        // i32 [R]     packed row -> route (token*k+slot)
     size_t inv;          // i32 [R]     route -> packed row
     size_t tiles;        // i32 [4*maxTiles]  tensor-core tile table (expert, row0, rows, pad)
+    size_t passes;       // int4 [R+T+1]  GEMV pass list: (expert or -1 for shared, first packed row, rows<=4, first token)
     size_t shared_gate;  // f32 [T]
     size_t act;          // f32 [(R+T), I]  SwiGLU activations per packed row (+ shared rows)
     size_t y;            // f32 [(R+T), H]  un-weighted expert outputs per packed row
@@ -62,6 +63,7 @@ __host__ inline Workspace workspace_layout(const fk_moe_dims& d) {
     w.order = take(sizeof(int32_t) * R);
     w.inv = take(sizeof(int32_t) * R);
     w.tiles = take(sizeof(int32_t) * 4 * (rpad / 16 + 1));
+    w.passes = take(sizeof(int32_t) * 4 * (R + T + 1));
     w.shared_gate = take(sizeof(float) * T);
     w.act = take(sizeof(float) * rows * I);
     w.y = take(sizeof(float) * rows * H);

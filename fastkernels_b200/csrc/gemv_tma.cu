@@ -1,0 +1,394 @@
+// bf16 weight-streaming grouped GEMV fed by bulk (TMA) copies through shared-memory rings.
+//
+// Work unit = (pass, tile): a pass is up to 4 packed rows (tokens) of one expert (the pass list is
+// written by the permute kernel), a tile is 16 gate/up pairs (gate_up) or 64 output rows (down).
+// Units are dealt round-robin to one persistent block per SM, so a hot expert spreads over many
+// blocks; its weights cross HBM once and the other passes find them in L2.
+//
+// Block = 16 consumer warps (two groups of 8 that take alternate weight stages) + a weight
+// producer warp + an activation producer warp.  The weight producer issues 32 KB bulk copies of
+// weight rows into a 4-stage ring; the activation producer looks up the pass, writes a small
+// header (first row, row count) and bulk-copies the pass's activation rows into a 2-slot ring.
+// Consumers never touch global memory except to store results: they wait on mbarriers, read
+// 16-byte shared-memory vectors (lane = 8 consecutive columns of a 256-column slice), keep the
+// activations in registers, fold partial sums with a transposing shuffle reduction and meet the
+// other slices of the row in shared memory behind a named barrier of their group.
+// A stage is released only after the values read from it have been used (the arrive carries a data
+// dependence on the sums), so a refill cannot overtake a pending shared-memory read.
+//
+// GU = true : gate_up rows + SwiGLU -> act[row, i]     (a stage holds 4*RG gate rows + 4*RG up rows)
+// GU = false: down rows             -> y[row, h]       (a stage holds 8*RG rows)
+// with K = KCH*256 columns per row, RG = 8/KCH row groups per stage, 32 KB per stage either way.
+//
+// Reference math: src/fastkernels/reference/qwen36_real.py:343-347.
+
+#include "common.cuh"
+#include "kernels.cuh"
+#include "tma.cuh"
+
+namespace fk {
+
+constexpr int kStageBytes = 32768;
+constexpr int kStages = 4;
+constexpr int kXSlots = 2;
+constexpr int kXSlotBytes = 32768;          // 4 rows x 2048 columns x 4 bytes at most
+constexpr int kGroupWarps = 8;
+constexpr int kGroups = 2;
+constexpr int kConsumerWarps = kGroups * kGroupWarps;
+constexpr int kStreamThreads = (kConsumerWarps + 2) * 32;
+constexpr int kDownTile = 64;
+
+struct StreamSmem {
+    unsigned char stage[kStages][kStageBytes];
+    unsigned char xslot[kXSlots][kXSlotBytes];
+    float partial[kGroups][2][kGroupWarps][32];
+    int4 header[kXSlots];                    // (expert or -1, first packed row, rows, first token)
+    uint64_t full[kStages];
+    uint64_t empty[kStages];
+    uint64_t xfull[kXSlots];
+    uint64_t xempty[kXSlots];
+    int abort_flag;
+};
+
+template <int V> struct Lg2 { static constexpr int value = 1 + Lg2<V / 2>::value; };
+template <> struct Lg2<1> { static constexpr int value = 0; };
+
+// After the call, v[0] of lane L holds the warp-wide sum of the value with index L >> (5 - log2 V).
+template <int V>
+__device__ __forceinline__ void transpose_reduce(float (&v)[V], int lane) {
+    constexpr int L = Lg2<V>::value;
+#pragma unroll
+    for (int s = 0; s < L; ++s) {
+        const int half = V >> (s + 1);
+        const int off = 16 >> s;
+        const bool upper = (lane & off) != 0;
+#pragma unroll
+        for (int i = 0; i < half; ++i) {
+            float send = upper ? v[i] : v[i + half];
+            float keep = upper ? v[i + half] : v[i];
+            v[i] = keep + __shfl_xor_sync(kFull, send, off);
+        }
+    }
+#pragma unroll
+    for (int off = 16 >> L; off > 0; off >>= 1) v[0] += __shfl_xor_sync(kFull, v[0], off);
+}
+
+__device__ __forceinline__ void unpack_bf16x8(const uint4& w, float (&f)[8]) {
+    f[0] = bf16lo(w.x); f[1] = bf16hi(w.x); f[2] = bf16lo(w.y); f[3] = bf16hi(w.y);
+    f[4] = bf16lo(w.z); f[5] = bf16hi(w.z); f[6] = bf16lo(w.w); f[7] = bf16hi(w.w);
+}
+
+// mbarrier arrive that cannot be scheduled before `dep` has been computed.
+__device__ __forceinline__ void mbar_arrive_after(uint64_t* bar, float dep) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)), "f"(dep) : "memory");
+}
+
+// pairs (gate_up) or rows (down) per unit: at least two stages, so that both groups see every unit
+__host__ __device__ constexpr int stream_tile(int kch, bool gu) {
+    return gu ? ((8 / kch) * 8 > 16 ? (8 / kch) * 8 : 16) : ((8 / kch) * 16 > kDownTile ? (8 / kch) * 16 : kDownTile);
+}
+
+__host__ __device__ constexpr int elem_bytes(int dtype) { return dtype == FK_F32 ? 4 : 2; }
+
+// 8 consecutive activation values (columns col0..col0+7 of row t) from an activation slot.
+__device__ __forceinline__ void load8_slot(const unsigned char* row, int dtype, int col0, float (&o)[8]) {
+    if (dtype == FK_F32) {
+        uint4 a = lds128(row + (size_t)col0 * 4), b = lds128(row + (size_t)col0 * 4 + 16);
+        o[0] = __uint_as_float(a.x); o[1] = __uint_as_float(a.y); o[2] = __uint_as_float(a.z); o[3] = __uint_as_float(a.w);
+        o[4] = __uint_as_float(b.x); o[5] = __uint_as_float(b.y); o[6] = __uint_as_float(b.z); o[7] = __uint_as_float(b.w);
+    } else if (dtype == FK_BF16) {
+        uint4 v = lds128(row + (size_t)col0 * 2);
+        unpack_bf16x8(v, o);
+    } else {
+        uint4 v = lds128(row + (size_t)col0 * 2);
+        const __half2* h = reinterpret_cast<const __half2*>(&v);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            float2 f = __half22float2(h[i]);
+            o[2 * i] = f.x; o[2 * i + 1] = f.y;
+        }
+    }
+}
+
+// The weight stages of one unit for consumer group `g`, NT activation rows in registers.
+template <int NT, int KCH, bool GU>
+__device__ __forceinline__ void consume_unit(const ExpertParams& p, StreamSmem& s, const unsigned char* xrows, int xdtype,
+                                             int row_pos, int nvalid, int tile, uint32_t& it, int& pbuf,
+                                             uint64_t* xempty, int g, int w8, int lane, int gtid) {
+    constexpr int RG = 8 / KCH;
+    constexpr int K = KCH * 256;
+    constexpr int TILE = stream_tile(KCH, GU);
+    constexpr int PER_STAGE = GU ? 4 * RG : 8 * RG;
+    constexpr int STEPS = TILE / PER_STAGE;
+    constexpr int RC = NT == 4 ? 4 : 8;                 // rows per reduction chunk
+    constexpr int V = RC * NT;
+    constexpr int SH = 5 - Lg2<V>::value;
+    const int kw = w8 % KCH, rg = w8 / KCH;
+    const int col0 = kw * 256 + lane * 8;
+
+    float x[NT][8];
+#pragma unroll
+    for (int t = 0; t < NT; ++t) {
+        if (t < nvalid) {
+            load8_slot(xrows + (size_t)t * K * elem_bytes(xdtype), xdtype, col0, x[t]);
+        } else {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) x[t][i] = 0.f;
+        }
+    }
+    bool x_released = false;
+
+#pragma unroll 1
+    for (int step = 0; step < STEPS; ++step, ++it) {
+        if ((int)(it & 1u) != g) continue;
+        const int stage = it % kStages;
+        const uint32_t par = (it / kStages) & 1u;
+        mbar_wait(&s.full[stage], par, &s.abort_flag);
+        const unsigned char* base = s.stage[stage];
+        uint4 w[8];
+        if (GU) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                w[q] = lds128(base + ((size_t)(rg * 4 + q) * K + col0) * 2);
+                w[4 + q] = lds128(base + kStageBytes / 2 + ((size_t)(rg * 4 + q) * K + col0) * 2);
+            }
+        } else {
+#pragma unroll
+            for (int r = 0; r < 8; ++r) w[r] = lds128(base + ((size_t)(rg * 8 + r) * K + col0) * 2);
+        }
+
+        float* part = s.partial[g][pbuf][w8];
+        float dep = 0.f;
+#pragma unroll
+        for (int c = 0; c < 8 / RC; ++c) {
+            float acc[V];
+#pragma unroll
+            for (int r = 0; r < RC; ++r) {
+                float wf[8];
+                unpack_bf16x8(w[c * RC + r], wf);
+#pragma unroll
+                for (int t = 0; t < NT; ++t) {
+                    float a = 0.f;
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) a = fmaf(wf[i], x[t][i], a);
+                    acc[r * NT + t] = a;
+                }
+            }
+            transpose_reduce<V>(acc, lane);
+            if ((lane & ((1 << SH) - 1)) == 0) part[c * V + (lane >> SH)] = acc[0];
+            dep += acc[0];
+        }
+        // every value read from the stage (and from the activation slot) has been consumed by now
+        dep = __shfl_sync(kFull, dep, 0) + dep;
+        if (lane == 0) {
+            mbar_arrive_after(&s.empty[stage], dep);
+            if (!x_released) mbar_arrive_after(xempty, dep);
+        }
+        x_released = true;
+
+        named_bar_sync(1 + g, kGroupWarps * 32);
+        if (gtid < PER_STAGE * NT) {
+            const int t = gtid % NT;
+            const int o = gtid / NT;              // output index inside the stage
+            if (GU) {
+                const int rg2 = o / 4, q = o - rg2 * 4;
+                float gsum = 0.f, usum = 0.f;
+#pragma unroll
+                for (int k2 = 0; k2 < KCH; ++k2) {
+                    gsum += s.partial[g][pbuf][rg2 * KCH + k2][q * NT + t];
+                    usum += s.partial[g][pbuf][rg2 * KCH + k2][(4 + q) * NT + t];
+                }
+                if (t < nvalid) {
+                    const int col = tile * TILE + step * PER_STAGE + o;
+                    p.act[(size_t)(row_pos + t) * p.I + col] = silu_mul(gsum, usum);
+                }
+            } else {
+                const int rg2 = o / 8, r = o - rg2 * 8;
+                float sum = 0.f;
+#pragma unroll
+                for (int k2 = 0; k2 < KCH; ++k2) sum += s.partial[g][pbuf][rg2 * KCH + k2][r * NT + t];
+                if (t < nvalid) {
+                    const int h = tile * TILE + step * PER_STAGE + o;
+                    p.y[(size_t)(row_pos + t) * p.H + h] = sum;
+                }
+            }
+        }
+        pbuf ^= 1;
+    }
+}
+
+template <int KCH, bool GU>
+__global__ void __launch_bounds__(kStreamThreads, 1) stream_gemv_kernel(ExpertParams p) {
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    StreamSmem& s = *reinterpret_cast<StreamSmem*>(smem_raw);
+    constexpr int RG = 8 / KCH;
+    constexpr int K = KCH * 256;
+    constexpr int TILE = stream_tile(KCH, GU);
+    constexpr int PER_STAGE = GU ? 4 * RG : 8 * RG;
+    constexpr int STEPS = TILE / PER_STAGE;
+    static_assert(STEPS % 2 == 0, "both consumer groups must see every unit");
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+
+    if (tid == 0) {
+        for (int i = 0; i < kStages; ++i) {
+            mbar_init(&s.full[i], 1);
+            mbar_init(&s.empty[i], kGroupWarps);
+        }
+        for (int i = 0; i < kXSlots; ++i) {
+            mbar_init(&s.xfull[i], 1);
+            mbar_init(&s.xempty[i], kConsumerWarps);
+        }
+        s.abort_flag = 0;
+        mbar_init_fence();
+    }
+    __syncthreads();
+
+    const int tiles = (GU ? p.I : p.H) / TILE;
+    const int units = p.meta[1] * tiles;
+    const int xdtype = GU ? p.hidden_dtype : FK_F32;
+    const int xrow_bytes = K * elem_bytes(xdtype);
+
+    if (warp == kConsumerWarps) {
+        // ---------------------------------------------------------------- weight producer
+        if (lane == 0) {
+            uint32_t it = 0;
+            int unit = blockIdx.x;
+            int4 next = unit < units ? p.passes[unit / tiles] : make_int4(0, 0, 0, 0);
+            for (; unit < units; unit += gridDim.x) {
+                const int4 pass = next;
+                const int tile = unit % tiles;
+                const int nu = unit + gridDim.x;
+                if (nu < units) next = p.passes[nu / tiles];
+                const __nv_bfloat16* W;
+                if (pass.x < 0) {
+                    W = reinterpret_cast<const __nv_bfloat16*>(GU ? p.shared_gate_up : p.shared_down);
+                } else {
+                    const size_t per_expert = GU ? (size_t)2 * p.I * p.H : (size_t)p.H * p.I;
+                    W = reinterpret_cast<const __nv_bfloat16*>(GU ? p.gate_up : p.down) + (size_t)pass.x * per_expert;
+                }
+                for (int step = 0; step < STEPS; ++step, ++it) {
+                    const int stage = it % kStages;
+                    const uint32_t par = (it / kStages) & 1u;
+                    mbar_wait(&s.empty[stage], par ^ 1u, &s.abort_flag);
+                    mbar_expect_tx(&s.full[stage], kStageBytes);
+                    const size_t first = (size_t)tile * TILE + (size_t)step * PER_STAGE;
+                    if (GU) {
+                        bulk_load(s.stage[stage], W + first * K, kStageBytes / 2, &s.full[stage]);
+                        bulk_load(s.stage[stage] + kStageBytes / 2, W + ((size_t)p.I + first) * K, kStageBytes / 2, &s.full[stage]);
+                    } else {
+                        bulk_load(s.stage[stage], W + first * K, kStageBytes, &s.full[stage]);
+                    }
+                }
+            }
+        }
+    } else if (warp == kConsumerWarps + 1) {
+        // ---------------------------------------------------------------- activation producer
+        uint32_t ui = 0;
+        int unit = blockIdx.x;
+        int4 next = unit < units ? p.passes[unit / tiles] : make_int4(0, 0, 0, 0);
+        for (; unit < units; unit += gridDim.x, ++ui) {
+            const int4 pass = next;
+            const int nu = unit + gridDim.x;
+            if (nu < units) next = p.passes[nu / tiles];
+            const int slot = ui % kXSlots;
+            const uint32_t par = (ui / kXSlots) & 1u;
+            const void* src = nullptr;
+            if (GU) {
+                if (lane < pass.z) {
+                    const int token = pass.x < 0 ? (pass.w + lane) : (p.order[pass.y + lane] / p.top_k);
+                    src = reinterpret_cast<const unsigned char*>(p.hidden) + (size_t)token * xrow_bytes;
+                }
+            } else if (lane == 0) {
+                src = p.act + (size_t)pass.y * K;      // the rows of a pass are consecutive in act
+            }
+            if (lane == 0) {
+                mbar_wait(&s.xempty[slot], par ^ 1u, &s.abort_flag);
+                s.header[slot] = pass;
+                mbar_expect_tx(&s.xfull[slot], (uint32_t)(pass.z * xrow_bytes));
+            }
+            __syncwarp();
+            if (GU) {
+                if (lane < pass.z) bulk_load(s.xslot[slot] + (size_t)lane * xrow_bytes, src, xrow_bytes, &s.xfull[slot]);
+            } else if (lane == 0) {
+                bulk_load(s.xslot[slot], src, (uint32_t)(pass.z * xrow_bytes), &s.xfull[slot]);
+            }
+        }
+    } else {
+        // ---------------------------------------------------------------- consumers
+        const int g = warp / kGroupWarps, w8 = warp % kGroupWarps, gtid = tid - g * kGroupWarps * 32;
+        int pbuf = 0;
+        uint32_t it = 0, ui = 0;
+        for (int unit = blockIdx.x; unit < units; unit += gridDim.x, ++ui) {
+            const int tile = unit % tiles;
+            const int slot = ui % kXSlots;
+            const uint32_t par = (ui / kXSlots) & 1u;
+            mbar_wait(&s.xfull[slot], par, &s.abort_flag);
+            const int4 pass = s.header[slot];
+            const unsigned char* xrows = s.xslot[slot];
+            if (pass.z == 1) consume_unit<1, KCH, GU>(p, s, xrows, xdtype, pass.y, 1, tile, it, pbuf, &s.xempty[slot], g, w8, lane, gtid);
+            else if (pass.z == 2) consume_unit<2, KCH, GU>(p, s, xrows, xdtype, pass.y, 2, tile, it, pbuf, &s.xempty[slot], g, w8, lane, gtid);
+            else consume_unit<4, KCH, GU>(p, s, xrows, xdtype, pass.y, pass.z, tile, it, pbuf, &s.xempty[slot], g, w8, lane, gtid);
+        }
+        if (s.abort_flag && lane == 0 && p.error_word) atomicExch(p.error_word, 1);
+    }
+}
+
+static bool kch_supported(int k) { return k == 256 || k == 512 || k == 1024 || k == 2048; }
+
+bool stream_path_supported(const ExpertParams& p, int weight_dtype) {
+    if (weight_dtype != FK_BF16) return false;
+    if (!kch_supported(p.H) || !kch_supported(p.I)) return false;
+    if (p.I % stream_tile(p.H / 256, true) != 0 || p.H % stream_tile(p.I / 256, false) != 0) return false;
+    uintptr_t bits = reinterpret_cast<uintptr_t>(p.hidden) | reinterpret_cast<uintptr_t>(p.gate_up) |
+                     reinterpret_cast<uintptr_t>(p.down) | reinterpret_cast<uintptr_t>(p.shared_gate_up) |
+                     reinterpret_cast<uintptr_t>(p.shared_down);
+    return (bits & 15) == 0;
+}
+
+int sm_count() {
+    static int cached[64] = {0};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+    if (cached[dev] == 0) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+        cached[dev] = n;
+    }
+    return cached[dev];
+}
+
+template <int KCH, bool GU>
+static int launch_stream_t(const ExpertParams& p, cudaStream_t stream) {
+    auto kern = stream_gemv_kernel<KCH, GU>;
+    const int smem = (int)sizeof(StreamSmem) + 128;
+    FK_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem), "stream gemv attr");
+    kern<<<sm_count(), kStreamThreads, smem, stream>>>(p);
+    FK_LAUNCH_OK(GU ? "gate_up stream launch" : "down stream launch");
+    return FK_OK;
+}
+
+int launch_experts_stream(const ExpertParams& p, cudaStream_t stream) {
+    if (p.T <= 0) return FK_OK;
+    int st;
+    switch (p.H / 256) {
+        case 1: st = launch_stream_t<1, true>(p, stream); break;
+        case 2: st = launch_stream_t<2, true>(p, stream); break;
+        case 4: st = launch_stream_t<4, true>(p, stream); break;
+        case 8: st = launch_stream_t<8, true>(p, stream); break;
+        default: return FK_ERR_UNSUPPORTED;
+    }
+    if (st != FK_OK) return st;
+    stage_mark();   // end of gate_up
+    switch (p.I / 256) {
+        case 1: st = launch_stream_t<1, false>(p, stream); break;
+        case 2: st = launch_stream_t<2, false>(p, stream); break;
+        case 4: st = launch_stream_t<4, false>(p, stream); break;
+        case 8: st = launch_stream_t<8, false>(p, stream); break;
+        default: return FK_ERR_UNSUPPORTED;
+    }
+    if (st != FK_OK) return st;
+    stage_mark();   // end of down
+    return FK_OK;
+}
+
+}  // namespace fk

@@ -35,7 +35,9 @@ struct PermuteParams {
     int* touched;             // [E+1] (optional)
     int* order;               // [routes]: packed row -> route (rows beyond offsets[E] are unused)
     int* inv;                 // [routes]: route -> packed row, -1 if dropped (optional)
-    int* meta;                // [0] = number of experts with count>0 (optional)
+    int* meta;                // [0] = number of experts with count>0, [1] = number of passes (optional)
+    int4* passes;             // optional GEMV pass list: routed experts ascending, then the shared expert
+    int shared_tokens;        // tokens the shared expert sees (0: no shared expert)
 };
 int launch_permute(const PermuteParams& p, cudaStream_t stream);
 int launch_histogram(const void* ids, int ids_are_int64, long long count, int E, int* counts, cudaStream_t stream);
@@ -55,18 +57,23 @@ struct ExpertParams {
     const int* order;
     const int* inv;
     const int* meta;
+    const int4* passes;
     const float* topk_weights;    // [T,k]
     const float* shared_gate;     // optional f32 [T] (already sigmoid)
     float* act;                   // [(routes+T), I]
     float* y;                     // [(routes+T), H]
     float* out;                   // [T,H]
     float* layer_hidden;          // optional [T,H]
+    int* error_word;              // optional: set to non-zero when a bounded device-side wait gave up
 };
 // shape-agnostic kernels (any dtype, any H/I)
 int launch_experts_generic(const ExpertParams& p, int weight_dtype, cudaStream_t stream);
 // bf16 weight-streaming grouped GEMV (H,I in {256,512,1024,2048})
 bool gemv_path_supported(const ExpertParams& p, int weight_dtype);
 int launch_experts_gemv(const ExpertParams& p, cudaStream_t stream);
+// bf16 grouped GEMV fed by bulk copies through a shared-memory ring (same shapes as the GEMV path)
+bool stream_path_supported(const ExpertParams& p, int weight_dtype);
+int launch_experts_stream(const ExpertParams& p, cudaStream_t stream);
 // ordered weighted combine of the per-row outputs (+ shared expert, + residual)
 int launch_combine(const ExpertParams& p, cudaStream_t stream);
 

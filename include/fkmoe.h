@@ -58,6 +58,7 @@ typedef struct fk_moe_dims {
 #define FK_FLAG_FORCE_GEMV 2u      /* never use the tensor-core grouped GEMM */
 #define FK_FLAG_FORCE_TENSOR 4u    /* use the tensor-core grouped GEMM whenever the shape allows */
 #define FK_FLAG_NO_FUSED_DECODE 8u /* T==1: run the staged kernels instead of the fused single-token kernel */
+#define FK_FLAG_REGISTER_GEMV 32u  /* grouped GEMV with direct global->register loads instead of the bulk-copy ring */
 #define FK_FLAG_SKIP_FOREIGN 16u   /* ids outside [expert_base, expert_base+E) are skipped instead of clamped */
 
 typedef struct fk_moe_call {

@@ -283,7 +283,7 @@ def test_full_layer_single_token_api(real_bf16):
     check_output(out_u, oracle_layer(hidden.unsqueeze(0), w_u, 8).output[0], torch.bfloat16)
 
 
-@pytest.mark.parametrize("flags", [_lib.FLAG_FORCE_GENERIC])
+@pytest.mark.parametrize("flags", [_lib.FLAG_FORCE_GENERIC, _lib.FLAG_REGISTER_GEMV])
 def test_full_layer_generic_kernels_agree(real_bf16, flags):
     w = real_bf16
     hidden = make_hidden(9, 3, REAL, dtype=torch.bfloat16, device="cuda")
