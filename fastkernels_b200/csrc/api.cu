@@ -150,6 +150,11 @@ int fk_moe_layer_timed(const fk_moe_call* c, void* stream, float* stage_ms, int*
     return st;
 }
 
+size_t fk_moe_trace_offset(const fk_moe_dims* dims) {
+    if (dims == nullptr || !dims_ok(*dims, false)) return 0;
+    return workspace_layout(*dims).y;
+}
+
 size_t fk_moe_workspace_bytes(const fk_moe_dims* dims) {
     if (dims == nullptr || !dims_ok(*dims, false)) return 0;
     return workspace_layout(*dims).total;
@@ -233,6 +238,29 @@ int fk_moe_layer(const fk_moe_call* c, void* stream) {
     rp.T = c->dims.tokens; rp.H = c->dims.hidden; rp.E = c->dims.experts; rp.top_k = c->dims.top_k;
     rp.eps = c->eps; rp.norm_offset = c->norm_offset;
     stage_mark();   // start
+    if (c->dims.tokens == 1 && !(c->flags & (FK_FLAG_NO_FUSED_DECODE | FK_FLAG_FORCE_GENERIC | FK_FLAG_REGISTER_GEMV))) {
+        DecodeParams dp{};
+        dp.hidden = c->hidden; dp.hidden_dtype = c->hidden_dtype;
+        dp.norm_weight = c->norm_weight; dp.router_weight = c->router_weight; dp.router_bias = c->router_bias;
+        dp.gate_up = c->expert_gate_up; dp.down = c->expert_down;
+        dp.shared_gate_up = c->shared_gate_up; dp.shared_down = c->shared_gate_up ? c->shared_down : nullptr;
+        dp.shared_gate = gated ? c->shared_gate : nullptr;
+        dp.logits = c->logits; dp.topk_ids = reinterpret_cast<long long*>(c->topk_ids); dp.topk_weights = c->topk_weights;
+        dp.out = c->out; dp.layer_hidden = c->layer_hidden;
+        dp.ract = at<float>(c->workspace, w.act);
+        dp.sact = dp.ract + (size_t)c->dims.top_k * c->dims.intermediate;
+        dp.sgate = at<float>(c->workspace, w.shared_gate);
+        dp.bar = at<unsigned>(c->workspace, w.counters);
+        dp.error_word = at<int>(c->workspace, w.meta) + 2;
+        dp.trace = (c->flags & FK_FLAG_TRACE) ? at<unsigned long long>(c->workspace, w.y) : nullptr;
+        dp.H = c->dims.hidden; dp.E = c->dims.experts; dp.I = c->dims.intermediate; dp.top_k = c->dims.top_k;
+        dp.eps = c->eps; dp.norm_offset = c->norm_offset;
+        if (decode1_supported(dp, c->weight_dtype)) {
+            st = launch_decode1(dp, s);
+            stage_mark();   // end of the fused kernel
+            return st;
+        }
+    }
     st = launch_router(rp, c->weight_dtype, s);
     if (st != FK_OK) return st;
     stage_mark();   // end of router

@@ -77,6 +77,36 @@ int launch_experts_stream(const ExpertParams& p, cudaStream_t stream);
 // ordered weighted combine of the per-row outputs (+ shared expert, + residual)
 int launch_combine(const ExpertParams& p, cudaStream_t stream);
 
+// one token, whole layer, one cooperative launch (bf16 weights)
+struct DecodeParams {
+    const void* hidden;
+    int hidden_dtype;
+    const void* norm_weight;
+    const void* router_weight;
+    const float* router_bias;
+    const void* gate_up;
+    const void* down;
+    const void* shared_gate_up;   // optional
+    const void* shared_down;
+    const void* shared_gate;      // optional
+    float* logits;                // [E]
+    long long* topk_ids;          // [k]
+    float* topk_weights;          // [k]
+    float* out;                   // [H]
+    float* layer_hidden;          // optional [H]
+    float* ract;                  // workspace [k, I]
+    float* sact;                  // workspace [I]
+    float* sgate;                 // workspace [1]
+    unsigned* bar;                // workspace [3]: arrive 1, arrive 2, depart (all zero between launches)
+    int* error_word;
+    unsigned long long* trace;    // optional [blocks][8] nanosecond timestamps of the phase boundaries
+    int H, E, I, top_k;
+    float eps, norm_offset;
+};
+bool decode1_supported(const DecodeParams& p, int weight_dtype);
+int launch_decode1(const DecodeParams& p, cudaStream_t stream);
+int sm_count();
+
 int launch_swiglu(const void* gate_up, void* out, int dtype, long long rows, int I, cudaStream_t stream);
 
 }  // namespace fk

@@ -12,6 +12,7 @@
 
 #include "common.cuh"
 #include "kernels.cuh"
+#include "topk.cuh"
 
 namespace fk {
 
@@ -48,72 +49,6 @@ __device__ __forceinline__ void load_vec<__half, 8>(const __half* p, float (&o)[
     }
 }
 
-// softmax + top-k of one token's logits by one warp.  EPL = experts per lane (E <= 32*EPL).
-template <int EPL>
-__device__ void topk_warp(const float* __restrict__ logits_row, int E, int top_k, long long* ids_out,
-                          int* ids32_out, float* weights_out) {
-    const int lane = threadIdx.x & 31;
-    float v[EPL];
-    float m = -INFINITY;
-#pragma unroll
-    for (int j = 0; j < EPL; ++j) {
-        int e = j * 32 + lane;
-        v[j] = e < E ? __ldcg(logits_row + e) : -INFINITY;
-        m = fmaxf(m, v[j]);
-    }
-    m = warp_max(m);
-    float s = 0.f;
-#pragma unroll
-    for (int j = 0; j < EPL; ++j) {
-        int e = j * 32 + lane;
-        v[j] = e < E ? expf(v[j] - m) : 0.f;
-        s += v[j];
-    }
-    s = warp_sum(s);
-#pragma unroll
-    for (int j = 0; j < EPL; ++j) {
-        int e = j * 32 + lane;
-        v[j] = e < E ? v[j] / s : -1.f;      // probabilities; padding can never win
-    }
-    float sel_v[FK_MAX_TOP_K];
-    int sel_i[FK_MAX_TOP_K];
-    float total = 0.f;
-#pragma unroll
-    for (int r = 0; r < FK_MAX_TOP_K; ++r) {
-        sel_v[r] = 0.f;
-        sel_i[r] = 0;
-        if (r < top_k) {
-            float bv = -2.f;
-            int bi = 0x7fffffff;
-#pragma unroll
-            for (int j = 0; j < EPL; ++j) {
-                if (v[j] > bv) { bv = v[j]; bi = j * 32 + lane; }   // strict: lowest index within the lane
-            }
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) {
-                float ov = __shfl_xor_sync(kFull, bv, o);
-                int oi = __shfl_xor_sync(kFull, bi, o);
-                if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
-            }
-#pragma unroll
-            for (int j = 0; j < EPL; ++j) {
-                if (j * 32 + lane == bi) v[j] = -1.f;
-            }
-            sel_v[r] = bv;
-            sel_i[r] = bi;
-            total += bv;
-        }
-    }
-#pragma unroll
-    for (int r = 0; r < FK_MAX_TOP_K; ++r) {
-        if (r < top_k && lane == r) {
-            ids_out[r] = sel_i[r];
-            if (ids32_out) ids32_out[r] = sel_i[r];
-            weights_out[r] = sel_v[r] / total;
-        }
-    }
-}
-
 template <typename WT, int VW, int TPB>
 __global__ void __launch_bounds__(kRouterWarps * 32)
 router_kernel(RouterParams p) {
@@ -128,55 +63,122 @@ router_kernel(RouterParams p) {
     const WT* norm_w = reinterpret_cast<const WT*>(p.norm_weight);
     const WT* router_w = reinterpret_cast<const WT*>(p.router_weight);
 
-    for (int i = tid; i < TPB * H; i += blockDim.x) {
-        int t = i / H, h = i - t * H;
-        int token = tok0 + t;
-        xs[i] = token < p.T ? load_any(p.hidden, p.hidden_dtype, (size_t)token * H + h) : 0.f;
+    // The weight row of this warp does not depend on the activations: start its loads first.
+    // Row E (when present) is the shared-expert gate vector: no norm scaling, sigmoid instead of a logit.
+    const bool has_gate = p.shared_gate_weight != nullptr && p.shared_gate_out != nullptr;
+    const int e = blockIdx.x * kRouterWarps + warp;
+    const bool is_gate = has_gate && e == E;
+    const bool active = e < E || is_gate;
+    const WT* wrow = is_gate ? reinterpret_cast<const WT*>(p.shared_gate_weight) : router_w + (size_t)(active ? e : 0) * H;
+    constexpr int PF = 4;                       // chunks of the row in flight per lane
+    float wpre[PF][VW];
+#pragma unroll
+    for (int j = 0; j < PF; ++j) {
+        const int h = (lane + j * 32) * VW;
+        if (active && h < H) load_vec<WT, VW>(wrow + h, wpre[j]);
+        else {
+#pragma unroll
+            for (int i = 0; i < VW; ++i) wpre[j][i] = 0.f;
+        }
+    }
+
+    // activations -> shared memory as fp32 (vectorised when the layout allows), norm gains next to them
+    float* gain = rstd + TPB;                   // [H]  (norm_offset + norm_weight)
+    const bool vec_x = (VW > 1) && (H % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.hidden) & 15) == 0) && p.hidden_dtype != FK_F32;
+    if (vec_x) {
+        const int chunks = H / 8;
+        for (int i = tid; i < TPB * chunks; i += blockDim.x) {
+            const int t = i / chunks, c = i - t * chunks;
+            const int token = tok0 + t;
+            float v[8];
+            if (token < p.T) {
+                uint4 raw = *reinterpret_cast<const uint4*>(reinterpret_cast<const unsigned short*>(p.hidden) + (size_t)token * H + c * 8);
+                if (p.hidden_dtype == FK_BF16) {
+                    v[0] = bf16lo(raw.x); v[1] = bf16hi(raw.x); v[2] = bf16lo(raw.y); v[3] = bf16hi(raw.y);
+                    v[4] = bf16lo(raw.z); v[5] = bf16hi(raw.z); v[6] = bf16lo(raw.w); v[7] = bf16hi(raw.w);
+                } else {
+                    const __half2* hh = reinterpret_cast<const __half2*>(&raw);
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) { float2 f = __half22float2(hh[q]); v[2 * q] = f.x; v[2 * q + 1] = f.y; }
+                }
+            } else {
+#pragma unroll
+                for (int q = 0; q < 8; ++q) v[q] = 0.f;
+            }
+            float4* dst = reinterpret_cast<float4*>(xs + (size_t)t * H + c * 8);
+            dst[0] = make_float4(v[0], v[1], v[2], v[3]);
+            dst[1] = make_float4(v[4], v[5], v[6], v[7]);
+        }
+    } else {
+        for (int i = tid; i < TPB * H; i += blockDim.x) {
+            int t = i / H, h = i - t * H;
+            int token = tok0 + t;
+            xs[i] = token < p.T ? load_any(p.hidden, p.hidden_dtype, (size_t)token * H + h) : 0.f;
+        }
+    }
+    for (int h = tid * VW; h < H; h += blockDim.x * VW) {
+        float nw[VW];
+        load_vec<WT, VW>(norm_w + h, nw);
+#pragma unroll
+        for (int i = 0; i < VW; ++i) gain[h + i] = p.norm_offset + nw[i];
     }
     __syncthreads();
-    // mean square per token (warps 0..TPB-1); shared-expert gate (remaining warps of expert tile 0)
+    // mean square per token
     for (int t = warp; t < TPB; t += kRouterWarps) {
         float ss = 0.f;
+#pragma unroll 8
         for (int h = lane; h < H; h += 32) ss += xs[t * H + h] * xs[t * H + h];
         ss = warp_sum(ss);
         if (lane == 0) rstd[t] = rsqrtf(ss / (float)H + p.eps);
     }
-    if (blockIdx.x == 0 && p.shared_gate_weight != nullptr && p.shared_gate_out != nullptr) {
-        const WT* g = reinterpret_cast<const WT*>(p.shared_gate_weight);
-        for (int t = warp; t < TPB; t += kRouterWarps) {
-            float acc = 0.f;
-            for (int h = lane; h < H; h += 32) acc += to_float(g[h]) * xs[t * H + h];
-            acc = warp_sum(acc);
-            if (lane == 0 && tok0 + t < p.T) p.shared_gate_out[tok0 + t] = sigmoidf_(acc);
-        }
-    }
     __syncthreads();
 
-    const int e = blockIdx.x * kRouterWarps + warp;
-    if (e < E) {
+    if (active) {
         float acc[TPB];
 #pragma unroll
         for (int t = 0; t < TPB; ++t) acc[t] = 0.f;
-        const WT* wrow = router_w + (size_t)e * H;
-        for (int h = lane * VW; h < H; h += 32 * VW) {
-            float w[VW], nw[VW];
-            load_vec<WT, VW>(wrow + h, w);
-            load_vec<WT, VW>(norm_w + h, nw);
+        for (int h0 = lane * VW; h0 < H; h0 += PF * 32 * VW) {
+            float wnext[PF][VW];
 #pragma unroll
-            for (int i = 0; i < VW; ++i) w[i] *= (p.norm_offset + nw[i]);
+            for (int j = 0; j < PF; ++j) {          // next group of chunks in flight while this one is used
+                const int h = h0 + (PF + j) * 32 * VW;
+                if (h < H) load_vec<WT, VW>(wrow + h, wnext[j]);
+                else {
 #pragma unroll
-            for (int t = 0; t < TPB; ++t) {
+                    for (int i = 0; i < VW; ++i) wnext[j][i] = 0.f;
+                }
+            }
 #pragma unroll
-                for (int i = 0; i < VW; ++i) acc[t] = fmaf(w[i], xs[t * H + h + i], acc[t]);
+            for (int j = 0; j < PF; ++j) {
+                const int h = h0 + j * 32 * VW;
+                if (h < H) {
+                    float w[VW];
+#pragma unroll
+                    for (int i = 0; i < VW; ++i) w[i] = is_gate ? wpre[j][i] : wpre[j][i] * gain[h + i];
+#pragma unroll
+                    for (int t = 0; t < TPB; ++t) {
+#pragma unroll
+                        for (int i = 0; i < VW; ++i) acc[t] = fmaf(w[i], xs[t * H + h + i], acc[t]);
+                    }
+                }
+            }
+#pragma unroll
+            for (int j = 0; j < PF; ++j) {
+#pragma unroll
+                for (int i = 0; i < VW; ++i) wpre[j][i] = wnext[j][i];
             }
         }
 #pragma unroll
         for (int t = 0; t < TPB; ++t) {
             float v = warp_sum(acc[t]);
             if (lane == 0 && tok0 + t < p.T) {
-                float logit = v * rstd[t];
-                if (p.router_bias) logit += p.router_bias[e];
-                p.logits[(size_t)(tok0 + t) * E + e] = logit;
+                if (is_gate) {
+                    p.shared_gate_out[tok0 + t] = sigmoidf_(v);
+                } else {
+                    float logit = v * rstd[t];
+                    if (p.router_bias) logit += p.router_bias[e];
+                    p.logits[(size_t)(tok0 + t) * E + e] = logit;
+                }
             }
         }
     }
@@ -209,15 +211,15 @@ static int launch_router_t(const RouterParams& p, cudaStream_t stream) {
     dim3 block(kRouterWarps * 32);
     if (p.T <= 64) {
         constexpr int TPB = 4;
-        size_t smem = sizeof(float) * ((size_t)TPB * p.H + TPB);
-        dim3 grid((p.E + kRouterWarps - 1) / kRouterWarps, (p.T + TPB - 1) / TPB);
+        size_t smem = sizeof(float) * ((size_t)TPB * p.H + TPB + p.H);
+        dim3 grid((p.E + (p.shared_gate_weight && p.shared_gate_out ? 1 : 0) + kRouterWarps - 1) / kRouterWarps, (p.T + TPB - 1) / TPB);
         auto kern = router_kernel<WT, VW, TPB>;
         FK_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), "router attr");
         kern<<<grid, block, smem, stream>>>(p);
     } else {
         constexpr int TPB = 8;
-        size_t smem = sizeof(float) * ((size_t)TPB * p.H + TPB);
-        dim3 grid((p.E + kRouterWarps - 1) / kRouterWarps, (p.T + TPB - 1) / TPB);
+        size_t smem = sizeof(float) * ((size_t)TPB * p.H + TPB + p.H);
+        dim3 grid((p.E + (p.shared_gate_weight && p.shared_gate_out ? 1 : 0) + kRouterWarps - 1) / kRouterWarps, (p.T + TPB - 1) / TPB);
         auto kern = router_kernel<WT, VW, TPB>;
         FK_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), "router attr");
         kern<<<grid, block, smem, stream>>>(p);

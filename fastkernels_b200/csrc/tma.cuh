@@ -40,11 +40,16 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 }
 
 // Returns false on time-out (and raises *abort_flag, a shared-memory word of the block).
+// Waiting threads back off with nanosleep: a tight poll of a shared-memory barrier by whole warps
+// competes with the shared-memory loads and shuffles of the warps that have work.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
     if (mbar_try_wait(bar, parity)) return true;
     const long long limit = *abort_flag ? kWaitCyclesAfterAbort : kWaitCycles;
     const long long t0 = clock64();
+    unsigned ns = 32;
     while (!mbar_try_wait(bar, parity)) {
+        __nanosleep(ns);
+        if (ns < 256) ns += ns;
         if (clock64() - t0 > limit) {
             *abort_flag = 1;
             return false;

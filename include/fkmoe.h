@@ -59,6 +59,8 @@ typedef struct fk_moe_dims {
 #define FK_FLAG_FORCE_TENSOR 4u    /* use the tensor-core grouped GEMM whenever the shape allows */
 #define FK_FLAG_NO_FUSED_DECODE 8u /* T==1: run the staged kernels instead of the fused single-token kernel */
 #define FK_FLAG_REGISTER_GEMV 32u  /* grouped GEMV with direct global->register loads instead of the bulk-copy ring */
+#define FK_FLAG_TRACE 64u          /* T==1 fused kernel: write per-block phase timestamps (ns) at the start of the
+                                      workspace's y region: u64 [blocks][8]; fk_moe_trace_offset() gives the offset */
 #define FK_FLAG_SKIP_FOREIGN 16u   /* ids outside [expert_base, expert_base+E) are skipped instead of clamped */
 
 typedef struct fk_moe_call {
@@ -105,6 +107,9 @@ uint64_t fk_launch_count(void);
  * gate_up, down, combine.  No counterpart in the reference (it times with a host clock around
  * a Python loop, e.g. bench/qwen36_real_moe_microbench.py:101-119). */
 int fk_moe_layer_timed(const fk_moe_call* call, void* stream, float* stage_ms, int* stages);
+
+/* Byte offset inside the workspace of the FK_FLAG_TRACE record for these dims. */
+size_t fk_moe_trace_offset(const fk_moe_dims* dims);
 
 /* Scratch size for a call with these dims (0 on invalid dims); and the one-time clear. */
 size_t fk_moe_workspace_bytes(const fk_moe_dims* dims);

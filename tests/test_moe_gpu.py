@@ -293,6 +293,40 @@ def test_full_layer_generic_kernels_agree(real_bf16, flags):
     torch.testing.assert_close(fast, slow, atol=2e-5, rtol=1e-4)
 
 
+@pytest.mark.parametrize("gated,bias", [(True, True), (False, False)])
+def test_single_token_fused_kernel_matches_staged_path_and_oracle(real_bf16_biased, gated, bias):
+    w = real_bf16_biased
+    args = list(w.tuple())
+    if not gated:
+        args[6] = None
+    rb = w.router_bias if bias else None
+    for seed in range(4):
+        hidden = make_hidden(300 + seed, 1, REAL, dtype=torch.bfloat16, device="cuda")
+        fused = triton_qwen36_batched_moe_layer_decode(hidden, *args, router_bias=rb)
+        staged = triton_qwen36_batched_moe_layer_decode(hidden, *args, router_bias=rb, flags=_lib.FLAG_NO_FUSED_DECODE)
+        assert torch.equal(fused[3], staged[3])                       # ids
+        torch.testing.assert_close(fused[2], staged[2], atol=1e-5, rtol=1e-5)   # logits
+        torch.testing.assert_close(fused[4], staged[4], atol=1e-6, rtol=1e-5)   # weights
+        torch.testing.assert_close(fused[1], staged[1], atol=2e-5, rtol=1e-4)   # update
+        torch.testing.assert_close(fused[0], hidden.float() + fused[1], atol=0, rtol=0)
+        ref = oracle_layer(hidden, MoEWeights(*args, rb), 8)
+        check_routing(fused[2], fused[3], fused[4], ref, torch.bfloat16)
+        check_output(fused[1], ref.output, torch.bfloat16)
+        again = triton_qwen36_batched_moe_layer_decode(hidden, *args, router_bias=rb)
+        assert torch.equal(again[1], fused[1])                        # bitwise repeatable
+
+
+def test_single_token_fused_kernel_fp32_hidden_and_many_calls(real_bf16):
+    w = real_bf16
+    hidden = make_hidden(5, 1, REAL, dtype=torch.float32, device="cuda")
+    out = None
+    for _ in range(50):                                               # the barrier words re-arm themselves
+        out, logits, ids, weights = triton_qwen36_batched_moe_decode(hidden, *w.tuple())
+    ref = oracle_layer(hidden, w, 8)
+    check_routing(logits, ids, weights, ref, torch.bfloat16)
+    check_output(out, ref.output, torch.bfloat16)
+
+
 def test_full_layer_fp32_hidden_with_bf16_weights(real_bf16):
     w = real_bf16
     hidden = make_hidden(11, 4, REAL, dtype=torch.float32, device="cuda")
