@@ -1,0 +1,152 @@
+"""Expert-parallel MoE layer over one node: experts block-sharded over the ranks of a process group.
+
+The reference has no distributed code at all (no torch.distributed, NCCL or MPI call site
+anywhere in suryavanshi/fastkernels); its plan lists expert-parallel dispatch as future work
+(docs/QWEN35_KERNEL_PLAN.md:83).  The single-device semantics this module must reproduce are
+those of `qwen36_real_moe_update` (src/fastkernels/reference/qwen36_real.py:329-354) applied
+to the concatenation of all ranks' tokens.
+
+Layout: rank r owns experts [r*E/G, (r+1)*E/G) (slices of expert_gate_up_weight / expert_down_weight
+along dim 0).  Norm, router, shared expert and shared gate are replicated.  Every rank routes its
+own T tokens.
+
+One layer call, per rank (all shapes fixed, so the sequence can be captured in a CUDA graph and
+needs no host synchronisation):
+  1. router on the local tokens -> ids, weights                      (fk_moe_router)
+  2. dispatch: all-gather of hidden rows, ids and weights             (NCCL)
+     A token goes to every rank that owns one of its 8 experts (5.3 of 8 ranks on average), so
+     the fixed-shape gather moves 1.5x the rows a routed all-to-all would, and in exchange
+     needs no split-size exchange.
+  3. local experts on all G*T tokens, foreign ids skipped, routing weights applied, slots in order
+                                                                      (fk_moe_experts, FK_FLAG_SKIP_FOREIGN)
+  4. combine: all-to-all of the per-rank partial rows back to the tokens' home ranks   (NCCL)
+  5. home rank: partials summed in rank order + gated shared expert (+ residual)
+Results do not depend on scheduling: every sum has a fixed order.
+
+The exchange code is backend-agnostic (gloo on CPU in the tests); the compute steps default to
+the CUDA library and can be replaced by callables for those tests.  There is no silent fallback:
+without CUDA tensors and without explicit callables the call raises.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Callable, Optional
+
+import torch
+import torch.distributed as dist
+
+from . import _lib
+from .spec import MoEWeights
+
+
+@dataclass
+class EPShard:
+    """This rank's slice of one layer: `weights.expert_*` hold only the local experts."""
+
+    weights: MoEWeights
+    rank: int
+    world: int
+    num_experts: int            # global E
+
+    @property
+    def local_experts(self) -> int:
+        return self.num_experts // self.world
+
+    @property
+    def expert_base(self) -> int:
+        return self.rank * self.local_experts
+
+
+def shard_weights(full: MoEWeights, rank: int, world: int) -> EPShard:
+    """Slice a full layer's routed experts for `rank` (views, no copy); everything else is shared."""
+    E = full.expert_gate_up_weight.shape[0]
+    if E % world:
+        raise ValueError("number of experts must be divisible by the number of ranks")
+    lo, hi = rank * (E // world), (rank + 1) * (E // world)
+    w = MoEWeights(full.norm_weight, full.router_weight, full.expert_gate_up_weight[lo:hi], full.expert_down_weight[lo:hi],
+                   full.shared_gate_up_weight, full.shared_down_weight, full.shared_expert_gate_weight, full.router_bias)
+    return EPShard(w, rank, world, E)
+
+
+# --------------------------------------------------------------------------- default compute steps
+def _cuda_router(hidden, w: MoEWeights, top_k, eps):
+    from .moe import qwen36_batched_moe_router_decode
+    return qwen36_batched_moe_router_decode(hidden, w.norm_weight, w.router_weight, top_k=top_k, eps=eps,
+                                            router_bias=w.router_bias)
+
+
+def _cuda_local_experts(hidden_all, ids_all, weights_all, shard: EPShard):
+    from .moe import qwen36_batched_routed_experts_decode
+    w = shard.weights
+    return qwen36_batched_routed_experts_decode(hidden_all, ids_all, weights_all, w.expert_gate_up_weight,
+                                                w.expert_down_weight, flags=_lib.FLAG_SKIP_FOREIGN,
+                                                expert_base=shard.expert_base)
+
+
+def _cuda_shared_expert(hidden, w: MoEWeights):
+    from .moe import _experts
+    T = hidden.shape[0]
+    ids = torch.empty((T, 0), dtype=torch.int64, device=hidden.device)
+    wts = torch.empty((T, 0), dtype=torch.float32, device=hidden.device)
+    # a layer with no routed slots: only the (gated) shared expert contributes
+    return _experts(hidden, ids, wts, w.expert_gate_up_weight[:1], w.expert_down_weight[:1], w.shared_gate_up_weight,
+                    w.shared_down_weight, w.shared_expert_gate_weight)
+
+
+# --------------------------------------------------------------------------- the layer
+def ep_moe_layer(hidden: torch.Tensor, shard: EPShard, *, top_k: int = 8, eps: float = 1e-6,
+                 group: Optional[dist.ProcessGroup] = None, residual: bool = False,
+                 router_fn: Optional[Callable] = None, local_experts_fn: Optional[Callable] = None,
+                 shared_expert_fn: Optional[Callable] = None):
+    """One expert-parallel layer call for this rank's `hidden [T,H]`.
+
+    Returns `(output [T,H] f32, logits [T,E] f32, topk_ids [T,k] i64, topk_weights [T,k] f32)`;
+    `output` includes the residual when `residual=True`.
+    """
+    if hidden.ndim != 2:
+        raise ValueError("hidden must have shape [tokens, hidden_size]")
+    world = dist.get_world_size(group)
+    if world != shard.world:
+        raise ValueError("shard was built for a different world size")
+    if not hidden.is_cuda and (router_fn is None or local_experts_fn is None or shared_expert_fn is None):
+        raise RuntimeError("expert-parallel MoE needs CUDA tensors: there is no CPU path in the product")
+    router_fn = router_fn or _cuda_router
+    local_experts_fn = local_experts_fn or _cuda_local_experts
+    shared_expert_fn = shared_expert_fn or _cuda_shared_expert
+    w = shard.weights
+    T, H = hidden.shape
+
+    logits, ids, weights = router_fn(hidden, w, top_k, eps)
+
+    # dispatch (fixed shape): every rank sees every token and its routing
+    hidden_all = torch.empty((world * T, H), dtype=hidden.dtype, device=hidden.device)
+    ids_all = torch.empty((world * T, top_k), dtype=ids.dtype, device=hidden.device)
+    weights_all = torch.empty((world * T, top_k), dtype=weights.dtype, device=hidden.device)
+    dist.all_gather_into_tensor(hidden_all, hidden.contiguous(), group=group)
+    dist.all_gather_into_tensor(ids_all, ids.contiguous(), group=group)
+    dist.all_gather_into_tensor(weights_all, weights.contiguous(), group=group)
+
+    partial = local_experts_fn(hidden_all, ids_all, weights_all, shard)          # [world*T, H] f32
+    shared = shared_expert_fn(hidden, w) if w.shared_gate_up_weight is not None else None
+
+    # combine: rows go back to their home rank; chunk g of `recv` is rank g's partial for our tokens
+    recv = torch.empty_like(partial)
+    dist.all_to_all_single(recv, partial.contiguous(), group=group)
+    out = recv.view(world, T, H)[0].clone()
+    for g in range(1, world):                                                     # fixed rank order
+        out += recv.view(world, T, H)[g]
+    if shared is not None:
+        out += shared
+    if residual:
+        out += hidden.float()
+    return out, logits, ids, weights
+
+
+def ep_payload_bytes(tokens: int, hidden_size: int, top_k: int, world: int, hidden_bytes: int = 2) -> dict:
+    """Bytes one rank sends per layer call (what crosses NVLink), for the roofline of the exchange."""
+    remote = world - 1
+    return {
+        "dispatch": remote * tokens * (hidden_size * hidden_bytes + top_k * 12),
+        "combine": remote * tokens * hidden_size * 4,
+    }

@@ -1,0 +1,122 @@
+"""Expert-parallel leg of bench.py (N > 1): one process per GPU, NCCL over NVLink.
+
+Weak scaling in tokens: every rank brings `--batch` tokens per step; the 256 experts are split
+evenly, so each rank streams 1/N of the routed weights plus the replicated router and shared
+expert.  Timing: barrier + synchronize on both sides of the K steps, CUDA events, maximum over ranks.
+"""
+
+from __future__ import annotations
+
+import json
+import os
+import statistics
+import time
+
+import torch
+import torch.distributed as dist
+
+
+def run_ep(args, workload_config, measured_peak, ClockSampler, METRIC, UNIT):
+    from . import _lib
+    from .ep import ep_moe_layer, ep_payload_bytes, EPShard
+    from .spec import MoESpec
+    from .workloads import make_hidden, make_moe_weights
+
+    lib = _lib.load()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", str(args.gpus)))
+    local = int(os.environ.get("LOCAL_RANK", str(rank)))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if not dist.is_initialized():
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", "29500")
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    spec = MoESpec()
+    peak, peak_src = measured_peak()
+    B, K, W, L = args.batch, args.steps, max(args.warmup, 3), args.layers
+    E, H, I = spec.num_experts, spec.hidden_size, spec.expert_intermediate_size
+    per = E // world
+    shards = []
+    for layer in range(L):
+        w = make_moe_weights(layer, spec, dtype=torch.bfloat16, device=dev, bias_std=0.5,
+                             expert_range=(rank * per, (rank + 1) * per))
+        shards.append(EPShard(w, rank, world, E))
+    pool = 8
+    hid_host = [make_hidden(1000 + i * world + rank, B, spec, dtype=torch.bfloat16).pin_memory() for i in range(pool)]
+    hid_dev = [h.to(dev) for h in hid_host]
+
+    def step(i, hidden):
+        return ep_moe_layer(hidden, shards[i % L], top_k=8)
+
+    def timed(fn, steps):
+        dist.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(steps):
+            fn(i)
+        e1.record()
+        torch.cuda.synchronize()
+        dist.barrier()
+        t = torch.tensor([e0.elapsed_time(e1) / steps], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    for i in range(W):
+        step(i, hid_dev[i % pool])
+    sampler = ClockSampler(local) if rank == 0 else None
+    if sampler:
+        sampler.start()
+    c0 = lib.fk_launch_count()
+    ms = timed(lambda i: step(i, hid_dev[i % pool]), K)
+    launches = lib.fk_launch_count() - c0
+
+    # end to end: pinned host hidden in, output back to pinned host memory, every step
+    out_host = torch.empty(B, H, dtype=torch.float32).pin_memory()
+    stage = torch.empty(B, H, dtype=torch.bfloat16, device=dev)
+
+    def e2e_step(i):
+        stage.copy_(hid_host[i % pool], non_blocking=True)
+        out, _, _, _ = step(i, stage)
+        out_host.copy_(out, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    for i in range(W):
+        e2e_step(i)
+    t0 = time.perf_counter()
+    e2e_ms = timed(e2e_step, K)
+    clocks = sampler.stop() if sampler else None
+
+    # distinct local experts hit per step (for the per-rank algorithmic bytes)
+    us = []
+    for i in range(min(L, 3)):
+        _, _, ids, _ = step(i, hid_dev[i % pool])
+        ids_all = torch.empty((world * B, 8), dtype=ids.dtype, device=dev)
+        dist.all_gather_into_tensor(ids_all, ids)
+        mine = ids_all[(ids_all >= rank * per) & (ids_all < (rank + 1) * per)]
+        us.append(int(torch.unique(mine).numel()))
+    u_local = statistics.mean(us)
+    per_expert = 3 * H * I * 2
+    rank_bytes = (u_local + 1) * per_expert + E * H * 2 + 2 * H * 2 + B * H * 2 + B * H * 4 + B * E * 4 + B * 8 * 12
+    payload = ep_payload_bytes(B, H, 8, world)
+    if rank == 0:
+        achieved = rank_bytes / (ms * 1e-3) / 1e9
+        line = {
+            "metric": METRIC, "value": world * B / (ms * 1e-3), "unit": UNIT, "n_gpus": world, "steps": K, "warmup": W,
+            "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+            "data": "synthetic", "config": workload_config(B, world, L),
+            "roofline": {"bound": "hbm", "kernel": "per-rank layer call (router, local experts of all ranks' tokens, shared expert)",
+                         "achieved": achieved, "peak": peak, "peak_source": peak_src, "unit": "GB/s", "frac": achieved / peak,
+                         "algorithmic_bytes_per_launch": rank_bytes, "ms_per_launch": ms, "traffic": None,
+                         "distinct_local_experts": u_local,
+                         "nvlink_bytes_per_rank_per_step": payload,
+                         "nvlink_floor_us": (max(payload["dispatch"], 0) + payload["combine"]) / 770e9 * 1e6},
+            "cpu_baseline": None,
+            "e2e": {"value": world * B / (e2e_ms * 1e-3), "unit": UNIT, "ms_per_step": e2e_ms,
+                    "h2d_bytes_per_step": world * B * H * 2, "d2h_bytes_per_step": world * B * H * 4},
+            "gpu_launches": int(launches) * world, "clocks": clocks,
+        }
+        print(json.dumps(line), flush=True)
+    dist.barrier()
+    dist.destroy_process_group()

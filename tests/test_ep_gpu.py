@@ -1,0 +1,66 @@
+"""GPU, 2 ranks over NCCL (skipped with fewer than 2 devices): the expert-parallel layer with the CUDA
+kernels matches the single-device oracle on the gathered batch, and the single-GPU layer bitwise in routing."""
+
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+pytestmark = pytest.mark.gpu
+
+
+def _worker(rank, world, port, tokens, failures):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        from oracle import moe_oracle as O
+        from fastkernels_b200.ep import ep_moe_layer, shard_weights
+        from fastkernels_b200.moe import qwen36_batched_moe_decode
+        from fastkernels_b200.spec import MoESpec
+        from fastkernels_b200.workloads import make_hidden, make_moe_weights
+        spec = MoESpec()
+        full = make_moe_weights(4, spec, dtype=torch.bfloat16, device="cuda", bias_std=0.5)
+        shard = shard_weights(full, rank, world)
+        hidden = make_hidden(70 + rank, tokens, spec, dtype=torch.bfloat16, device="cuda")
+        out, logits, ids, weights = ep_moe_layer(hidden, shard, top_k=8)
+        out2, _, ids2, _ = ep_moe_layer(hidden, shard, top_k=8)
+        assert torch.equal(out, out2) and torch.equal(ids, ids2), "not repeatable"
+        single, _, ids1, _ = qwen36_batched_moe_decode(hidden, *full.tuple(), router_bias=full.router_bias)
+        assert torch.equal(ids, ids1), "routing differs between one GPU and expert parallel"
+        torch.testing.assert_close(out, single, atol=2e-5, rtol=1e-4)
+        cpu = [None if t is None else t.cpu() for t in full.tuple()]
+        ref = O.moe_update(hidden.cpu(), *cpu, top_k=8, router_bias=full.router_bias.cpu())
+        clear = ref.margin > 2e-6
+        assert torch.equal(ids.cpu()[clear], ref.topk_ids[clear])
+        if bool(clear.all()):
+            ma, rl = O.max_abs(out.cpu(), ref.output), O.rel_l2(out.cpu(), ref.output)
+            assert ma <= 2e-2 and rl <= 5e-3, (ma, rl)
+    except Exception as exc:  # noqa: BLE001
+        failures.put(f"rank {rank}: {exc!r}")
+    finally:
+        dist.destroy_process_group()
+
+
+def test_ep_two_gpus_matches_oracle_and_single_gpu():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    ctx = mp.get_context("spawn")
+    failures = ctx.Queue()
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, 6, failures)) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(300)
+    msgs = []
+    while not failures.empty():
+        msgs.append(failures.get())
+    assert not msgs, msgs
+    assert all(p.exitcode == 0 for p in procs)
