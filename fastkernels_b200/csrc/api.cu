@@ -59,9 +59,6 @@ static int run_experts(const fk_moe_call* c, const Workspace& w, const long long
     pp.meta = at<int>(ws, w.meta);
     pp.passes = at<int4>(ws, w.passes);
     pp.shared_tokens = c->shared_gate_up ? d.tokens : 0;
-    int st = launch_permute(pp, stream);
-    if (st != FK_OK) return st;
-    stage_mark();   // end of permute
 
     ExpertParams ep{};
     ep.hidden = c->hidden;
@@ -72,6 +69,16 @@ static int run_experts(const fk_moe_call* c, const Workspace& w, const long long
     ep.shared_down = c->shared_gate_up ? c->shared_down : nullptr;
     ep.T = d.tokens; ep.H = d.hidden; ep.E = d.experts; ep.I = d.intermediate; ep.top_k = d.top_k;
     ep.routes = pp.routes;
+    // path choice: tensor cores from 64 tokens up (or when forced), bulk-copy GEMV below
+    const bool generic = (c->flags & FK_FLAG_FORCE_GENERIC) != 0;
+    const bool want_tc = !generic && !(c->flags & (FK_FLAG_FORCE_GEMV | FK_FLAG_REGISTER_GEMV)) &&
+                         ((c->flags & FK_FLAG_FORCE_TENSOR) || d.tokens >= 64);
+    const bool use_tc = want_tc && tc_path_supported(ep, c->weight_dtype);
+    pp.pass_rows = use_tc ? 64 : 4;
+    int st = launch_permute(pp, stream);
+    if (st != FK_OK) return st;
+    stage_mark();   // end of permute
+
     ep.counts = pp.counts; ep.offsets = pp.offsets; ep.touched = pp.touched;
     ep.order = pp.order; ep.inv = pp.inv; ep.meta = pp.meta; ep.passes = pp.passes;
     ep.topk_weights = weights;
@@ -82,8 +89,9 @@ static int run_experts(const fk_moe_call* c, const Workspace& w, const long long
     ep.layer_hidden = c->layer_hidden;
 
     ep.error_word = at<int>(ws, w.meta) + 2;
-    const bool generic = (c->flags & FK_FLAG_FORCE_GENERIC) != 0;
-    if (!generic && !(c->flags & FK_FLAG_REGISTER_GEMV) && stream_path_supported(ep, c->weight_dtype))
+    if (use_tc)
+        st = launch_experts_tc(ep, at<__nv_bfloat16>(ws, w.xg), at<__nv_bfloat16>(ws, w.actb), stream);
+    else if (!generic && !(c->flags & FK_FLAG_REGISTER_GEMV) && stream_path_supported(ep, c->weight_dtype))
         st = launch_experts_stream(ep, stream);
     else if (!generic && gemv_path_supported(ep, c->weight_dtype))
         st = launch_experts_gemv(ep, stream);

@@ -38,6 +38,7 @@ struct PermuteParams {
     int* meta;                // [0] = number of experts with count>0, [1] = number of passes (optional)
     int4* passes;             // optional GEMV pass list: routed experts ascending, then the shared expert
     int shared_tokens;        // tokens the shared expert sees (0: no shared expert)
+    int pass_rows;            // rows per pass: 4 for the GEMV kernels, 64 for the tensor-core GEMM
 };
 int launch_permute(const PermuteParams& p, cudaStream_t stream);
 int launch_histogram(const void* ids, int ids_are_int64, long long count, int E, int* counts, cudaStream_t stream);
@@ -74,6 +75,9 @@ int launch_experts_gemv(const ExpertParams& p, cudaStream_t stream);
 // bf16 grouped GEMV fed by bulk copies through a shared-memory ring (same shapes as the GEMV path)
 bool stream_path_supported(const ExpertParams& p, int weight_dtype);
 int launch_experts_stream(const ExpertParams& p, cudaStream_t stream);
+// tcgen05 grouped GEMM (bf16, H and I multiples of 128); needs a pass list of <= 64-row passes
+bool tc_path_supported(const ExpertParams& p, int weight_dtype);
+int launch_experts_tc(const ExpertParams& p, __nv_bfloat16* xg, __nv_bfloat16* actb, cudaStream_t stream);
 // ordered weighted combine of the per-row outputs (+ shared expert, + residual)
 int launch_combine(const ExpertParams& p, cudaStream_t stream);
 

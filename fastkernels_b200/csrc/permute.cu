@@ -79,10 +79,11 @@ __global__ void __launch_bounds__(kPermWarps * 32) permute_kernel(PermuteParams 
             if (p.meta) p.meta[0] = excl_f + f;
             if (p.touched) p.touched[excl_f + f] = -1;
         }
-        // GEMV pass list: an expert with c rows is visited in ceil(c/4) passes of up to 4 rows
+        // pass list: an expert with c rows is visited in ceil(c/PR) passes of up to PR rows
         if (p.passes) {
             __syncthreads();                   // warp_cnt is reused for the pass-count scan
-            const int np = (c + 3) >> 2;
+            const int PR = p.pass_rows > 0 ? p.pass_rows : 4;
+            const int np = (c + PR - 1) / PR;
             int ip = np;
 #pragma unroll
             for (int o = 1; o < 32; o <<= 1) {
@@ -94,13 +95,13 @@ __global__ void __launch_bounds__(kPermWarps * 32) permute_kernel(PermuteParams 
             int pre = 0;
             for (int w = 0; w < warp; ++w) pre += warp_cnt[w];
             const int first = pre + ip - np;
-            for (int j = 0; j < np; ++j) p.passes[first + j] = make_int4(e, excl_c + 4 * j, min(4, c - 4 * j), 0);
+            for (int j = 0; j < np; ++j) p.passes[first + j] = make_int4(e, excl_c + PR * j, min(PR, c - PR * j), 0);
             __shared__ int routed_passes;
             if (tid == blockDim.x - 1) routed_passes = first + np;
             __syncthreads();
-            const int sp = (p.shared_tokens + 3) >> 2;
+            const int sp = (p.shared_tokens + PR - 1) / PR;
             for (int j = tid; j < sp; j += blockDim.x)
-                p.passes[routed_passes + j] = make_int4(-1, p.routes + 4 * j, min(4, p.shared_tokens - 4 * j), 4 * j);
+                p.passes[routed_passes + j] = make_int4(-1, p.routes + PR * j, min(PR, p.shared_tokens - PR * j), PR * j);
             if (tid == 0 && p.meta) p.meta[1] = routed_passes + sp;
         }
     }

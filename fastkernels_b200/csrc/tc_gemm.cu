@@ -1,0 +1,321 @@
+// Grouped expert GEMM on the Blackwell tensor cores (tcgen05 + tensor memory), for expert groups
+// that are too tall for the CUDA-core GEMV (>= 64 tokens in the batch).
+//
+// Swap-AB: the weight rows are the MMA's M dimension (128 rows per tile, K-major in shared memory,
+// 128-byte swizzle, loaded by tiled TMA), the tokens of one pass are its N dimension (up to 64,
+// rounded up to 16), K runs over the reduction dimension in chunks of 64.  gate_up keeps two fp32
+// accumulators in tensor memory, gate rows and up rows of the same 128 pairs, so the epilogue thread
+// that owns pair p reads gate[p, t] and up[p, t] from its own lane and applies SwiGLU without any
+// exchange; the bf16 result goes to the packed activation buffer that the down GEMM reads back
+// through TMA.  Two accumulator buffers: the MMAs of the next unit run while the epilogue drains
+// the previous one.
+//
+// Block = 6 warps: warp 0 issues TMA (one lane), warp 1 owns tensor memory and issues the MMAs (one
+// lane), warps 2..5 are the epilogue (one TMEM lane quarter each).  One persistent block per SM,
+// units (pass x 128-row tile) dealt round-robin.  Every wait is bounded.
+//
+// Reference math: src/fastkernels/reference/qwen36_real.py:343-347.
+
+#include <mutex>
+#include <unordered_map>
+
+#include "common.cuh"
+#include "kernels.cuh"
+#include "tcgen05.cuh"
+
+namespace fk {
+
+constexpr int kTcStages = 4;
+constexpr int kTcN = 64;                 // tokens per pass (MMA N, rounded up to 16)
+constexpr int kTcThreads = 192;
+constexpr int kTcTileBytes = 128 * 64 * 2;          // one 128-row x 64-column bf16 operand tile
+constexpr int kTcBBytes = kTcN * 64 * 2;
+constexpr int kTcTmemCols = 256;         // 2 buffers x (gate 64 + up 64) columns
+
+struct TcBarriers {
+    uint64_t full[kTcStages];
+    uint64_t empty[kTcStages];
+    uint64_t tfull[2];
+    uint64_t tempty[2];
+    uint32_t tmem_base;
+    int abort_flag;
+};
+
+struct TcParams {
+    const int4* passes;        // (expert or -1, first packed row, rows <= 64, first token)
+    const int* meta;           // [1] = number of passes
+    __nv_bfloat16* actb;       // GU: output [rows, I] bf16
+    float* y;                  // down: output [rows, H] f32
+    int* error_word;
+    int H, I;
+};
+
+template <bool GU>
+__global__ void __launch_bounds__(kTcThreads, 1)
+tc_grouped_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ CUtensorMap smap,
+                  const __grid_constant__ CUtensorMap amap, TcParams p) {
+    extern __shared__ unsigned char smem_dyn[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~uintptr_t(1023));
+    constexpr int kStageBytes = (GU ? 2 : 1) * kTcTileBytes + kTcBBytes;
+    TcBarriers& bar = *reinterpret_cast<TcBarriers*>(smem + kTcStages * kStageBytes);
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int K = GU ? p.H : p.I;
+    const int chunks = K / 64;
+    const int tiles = (GU ? p.I : p.H) / 128;
+    const int rows_per_expert = GU ? 2 * p.I : p.H;
+    const int units = p.meta[1] * tiles;
+
+    if (tid == 0) {
+        for (int i = 0; i < kTcStages; ++i) { mbar_init(&bar.full[i], 1); mbar_init(&bar.empty[i], 1); }
+        for (int i = 0; i < 2; ++i) { mbar_init(&bar.tfull[i], 1); mbar_init(&bar.tempty[i], 4); }
+        bar.abort_flag = 0;
+        mbar_init_fence();
+        prefetch_tensormap(&wmap);
+        prefetch_tensormap(&smap);
+        prefetch_tensormap(&amap);
+    }
+    if (warp == 1) tmem_alloc(&bar.tmem_base, kTcTmemCols);
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = bar.tmem_base;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            uint32_t it = 0;
+            for (int unit = blockIdx.x; unit < units; unit += gridDim.x) {
+                const int4 pass = p.passes[unit / tiles];
+                const int mt = unit % tiles;
+                const int npad = (pass.z + 15) & ~15;
+                const CUtensorMap* wm = pass.x < 0 ? &smap : &wmap;
+                const int wrow = (pass.x < 0 ? 0 : pass.x * rows_per_expert) + mt * 128;
+                for (int c = 0; c < chunks; ++c, ++it) {
+                    const int stage = it % kTcStages;
+                    const uint32_t par = (it / kTcStages) & 1u;
+                    mbar_wait(&bar.empty[stage], par ^ 1u, &bar.abort_flag);
+                    unsigned char* st = smem + stage * kStageBytes;
+                    mbar_expect_tx(&bar.full[stage], (GU ? 2 : 1) * kTcTileBytes + npad * 128);
+                    tma_load_2d(st, wm, c * 64, wrow, &bar.full[stage]);
+                    if (GU) tma_load_2d(st + kTcTileBytes, wm, c * 64, wrow + p.I, &bar.full[stage]);
+                    unsigned char* bt = st + (GU ? 2 : 1) * kTcTileBytes;
+                    for (int j = 0; j < npad / 16; ++j)
+                        tma_load_2d(bt + j * 16 * 128, &amap, c * 64, pass.y + j * 16, &bar.full[stage]);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            uint32_t it = 0, ui = 0;
+            for (int unit = blockIdx.x; unit < units; unit += gridDim.x, ++ui) {
+                const int4 pass = p.passes[unit / tiles];
+                const uint32_t npad = (uint32_t)((pass.z + 15) & ~15);
+                const uint32_t idesc = umma_idesc_bf16(npad);
+                const uint32_t acc = ui & 1u;
+                mbar_wait(&bar.tempty[acc], ((ui >> 1) & 1u) ^ 1u, &bar.abort_flag);
+                tc_fence_after_sync();
+                const uint32_t d0 = tmem_base + acc * 128u;
+                for (int c = 0; c < chunks; ++c, ++it) {
+                    const int stage = it % kTcStages;
+                    const uint32_t par = (it / kTcStages) & 1u;
+                    mbar_wait(&bar.full[stage], par, &bar.abort_flag);
+                    tc_fence_after_sync();
+                    const unsigned char* st = smem + stage * kStageBytes;
+                    const unsigned char* bt = st + (GU ? 2 : 1) * kTcTileBytes;
+#pragma unroll
+                    for (int kk = 0; kk < 4; ++kk) {
+                        const uint64_t b_desc = umma_smem_desc(bt + kk * 32);
+                        const uint32_t accum = (c > 0 || kk > 0) ? 1u : 0u;
+                        umma_bf16(d0, umma_smem_desc(st + kk * 32), b_desc, idesc, accum);
+                        if (GU) umma_bf16(d0 + 64u, umma_smem_desc(st + kTcTileBytes + kk * 32), b_desc, idesc, accum);
+                    }
+                    umma_commit(&bar.empty[stage]);      // the stage is free once these MMAs have read it
+                }
+                umma_commit(&bar.tfull[acc]);            // the accumulators are complete
+            }
+        }
+    } else {
+        // ------------------------------------------------------------------ epilogue warps
+        const int q = warp & 3;                          // TMEM lane quarter this warp may read
+        const int r = q * 32 + lane;                     // row of the 128-row tile
+        uint32_t ui = 0;
+        for (int unit = blockIdx.x; unit < units; unit += gridDim.x, ++ui) {
+            const int4 pass = p.passes[unit / tiles];
+            const int mt = unit % tiles;
+            const int n = pass.z, npad = (n + 15) & ~15;
+            const uint32_t acc = ui & 1u;
+            mbar_wait(&bar.tfull[acc], (ui >> 1) & 1u, &bar.abort_flag);
+            tc_fence_after_sync();
+            const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + acc * 128u;
+            for (int c16 = 0; c16 < npad / 16; ++c16) {
+                float g[16];
+                tmem_ld16(taddr + c16 * 16, g);
+                if (GU) {
+                    float u[16];
+                    tmem_ld16(taddr + 64u + c16 * 16, u);
+#pragma unroll
+                    for (int t = 0; t < 16; ++t) {
+                        const int tok = c16 * 16 + t;
+                        if (tok < n) p.actb[(size_t)(pass.y + tok) * p.I + mt * 128 + r] = __float2bfloat16_rn(silu_mul(g[t], u[t]));
+                    }
+                } else {
+#pragma unroll
+                    for (int t = 0; t < 16; ++t) {
+                        const int tok = c16 * 16 + t;
+                        if (tok < n) p.y[(size_t)(pass.y + tok) * p.H + mt * 128 + r] = g[t];
+                    }
+                }
+            }
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&bar.tempty[acc]);
+        }
+    }
+
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after_sync();
+        tmem_dealloc(tmem_base, kTcTmemCols);
+    }
+    if (tid == 0 && bar.abort_flag && p.error_word) atomicExch(p.error_word, 3);
+}
+
+// packed bf16 activations: xg[pos] = hidden[token of packed row pos]; the shared expert's rows follow
+__global__ void gather_rows_kernel(ExpertParams p, __nv_bfloat16* xg) {
+    const int routed = p.offsets[p.E];
+    const int shared_rows = p.shared_gate_up ? p.T : 0;
+    const int chunks = p.H / 8;
+    const long long total = (long long)(p.routes + shared_rows) * chunks;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const int pos = (int)(i / chunks), c = (int)(i - (long long)pos * chunks);
+        int token;
+        if (pos >= p.routes) token = pos - p.routes;
+        else if (pos < routed) token = p.order[pos] / p.top_k;
+        else continue;
+        const size_t src = (size_t)token * p.H + c * 8;
+        uint4 out;
+        if (p.hidden_dtype == FK_BF16) {
+            out = *reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(p.hidden) + src);
+        } else {
+            __nv_bfloat162 h2[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k)
+                h2[k] = __floats2bfloat162_rn(load_any(p.hidden, p.hidden_dtype, src + 2 * k), load_any(p.hidden, p.hidden_dtype, src + 2 * k + 1));
+            out = *reinterpret_cast<uint4*>(h2);
+        }
+        *reinterpret_cast<uint4*>(xg + (size_t)pos * p.H + c * 8) = out;
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Host side: tensor maps (encoded through the driver entry point, cached) and launches
+// ---------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(ptr);
+    });
+    return fn;
+}
+
+struct MapKey {
+    const void* base; uint64_t rows, cols; uint32_t box_rows;
+    bool operator==(const MapKey& o) const { return base == o.base && rows == o.rows && cols == o.cols && box_rows == o.box_rows; }
+};
+struct MapKeyHash {
+    size_t operator()(const MapKey& k) const {
+        return std::hash<const void*>()(k.base) ^ (k.rows * 1000003ull) ^ (k.cols * 10007ull) ^ k.box_rows;
+    }
+};
+
+// 2-D bf16 tensor [rows, cols] row-major, box = [box_rows, 64 columns], 128-byte swizzle, zero fill outside
+static bool tensor_map(const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows, CUtensorMap* out) {
+    static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
+    static std::mutex mu;
+    MapKey key{base, rows, cols, box_rows};
+    std::lock_guard<std::mutex> lock(mu);
+    auto it = cache.find(key);
+    if (it != cache.end()) { *out = it->second; return true; }
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return false;
+    cuuint64_t dims[2] = {cols, rows};
+    cuuint64_t strides[1] = {cols * 2};
+    cuuint32_t box[2] = {64, box_rows};
+    cuuint32_t elem[2] = {1, 1};
+    CUtensorMap m;
+    CUresult r = fn(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return false;
+    if (cache.size() > 4096) cache.clear();
+    cache.emplace(key, m);
+    *out = m;
+    return true;
+}
+
+bool tc_path_supported(const ExpertParams& p, int weight_dtype) {
+    if (weight_dtype != FK_BF16) return false;
+    if (p.H % 128 != 0 || p.I % 128 != 0 || p.H < 128 || p.I < 128) return false;
+    uintptr_t bits = reinterpret_cast<uintptr_t>(p.hidden) | reinterpret_cast<uintptr_t>(p.gate_up) |
+                     reinterpret_cast<uintptr_t>(p.down) | reinterpret_cast<uintptr_t>(p.shared_gate_up) |
+                     reinterpret_cast<uintptr_t>(p.shared_down);
+    if (bits & 15) return false;
+    return encode_fn() != nullptr;
+}
+
+// gather -> gate_up GEMM (+SwiGLU) -> down GEMM; the pass list in p.passes must hold passes of <= 64 rows
+int launch_experts_tc(const ExpertParams& p, __nv_bfloat16* xg, __nv_bfloat16* actb, cudaStream_t stream) {
+    if (p.T <= 0) return FK_OK;
+    const uint64_t rows = (uint64_t)p.routes + (p.shared_gate_up ? p.T : 0);
+    CUtensorMap w_gu, s_gu, a_x, w_dn, s_dn, a_act;
+    const void* dummy_gu = p.gate_up ? p.gate_up : p.shared_gate_up;
+    const void* dummy_dn = p.down ? p.down : p.shared_down;
+    const uint64_t e_rows = p.gate_up ? (uint64_t)p.E : 0;
+    bool ok = tensor_map(dummy_gu, p.gate_up ? e_rows * 2 * p.I : 2 * p.I, p.H, 128, &w_gu) &&
+              tensor_map(p.shared_gate_up ? p.shared_gate_up : dummy_gu, 2 * (uint64_t)p.I, p.H, 128, &s_gu) &&
+              tensor_map(xg, rows, p.H, 16, &a_x) &&
+              tensor_map(dummy_dn, p.down ? e_rows * p.H : p.H, p.I, 128, &w_dn) &&
+              tensor_map(p.shared_down ? p.shared_down : dummy_dn, (uint64_t)p.H, p.I, 128, &s_dn) &&
+              tensor_map(actb, rows, p.I, 16, &a_act);
+    if (!ok) return FK_ERR_UNSUPPORTED;
+
+    {
+        long long total = (long long)rows * (p.H / 8);
+        int blocks = (int)((total + 255) / 256);
+        if (blocks > sm_count() * 8) blocks = sm_count() * 8;
+        gather_rows_kernel<<<blocks, 256, 0, stream>>>(p, xg);
+        FK_LAUNCH_OK("gather rows launch");
+    }
+    TcParams tp{};
+    tp.passes = p.passes; tp.meta = p.meta; tp.actb = actb; tp.y = p.y; tp.error_word = p.error_word; tp.H = p.H; tp.I = p.I;
+    {
+        auto kern = tc_grouped_kernel<true>;
+        const int smem = kTcStages * (2 * kTcTileBytes + kTcBBytes) + (int)sizeof(TcBarriers) + 1024;
+        FK_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem), "tc gate_up attr");
+        kern<<<sm_count(), kTcThreads, smem, stream>>>(w_gu, s_gu, a_x, tp);
+        FK_LAUNCH_OK("tc gate_up launch");
+    }
+    stage_mark();   // end of gate_up
+    {
+        auto kern = tc_grouped_kernel<false>;
+        const int smem = kTcStages * (kTcTileBytes + kTcBBytes) + (int)sizeof(TcBarriers) + 1024;
+        FK_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem), "tc down attr");
+        kern<<<sm_count(), kTcThreads, smem, stream>>>(w_dn, s_dn, a_act, tp);
+        FK_LAUNCH_OK("tc down launch");
+    }
+    stage_mark();   // end of down
+    return FK_OK;
+}
+
+}  // namespace fk

@@ -327,6 +327,41 @@ def test_single_token_fused_kernel_fp32_hidden_and_many_calls(real_bf16):
     check_output(out, ref.output, torch.bfloat16)
 
 
+@pytest.mark.parametrize("tokens", [1, 5, 17, 64, 130])
+def test_tensor_core_grouped_gemm_matches_gemv_path_and_oracle(real_bf16_biased, tokens):
+    """tcgen05 grouped GEMM (forced at any batch) against the CUDA-core GEMV path and the oracle.
+    The tensor path rounds the SwiGLU activations to bf16 before the down projection, so it is
+    compared with the bf16 output bounds, not bitwise."""
+    w = real_bf16_biased
+    hidden = make_hidden(400 + tokens, tokens, REAL, dtype=torch.bfloat16, device="cuda")
+    gemv = triton_qwen36_batched_moe_decode(hidden, *w.tuple(), router_bias=w.router_bias,
+                                            flags=_lib.FLAG_FORCE_GEMV | _lib.FLAG_NO_FUSED_DECODE)
+    tc = triton_qwen36_batched_moe_decode(hidden, *w.tuple(), router_bias=w.router_bias,
+                                          flags=_lib.FLAG_FORCE_TENSOR | _lib.FLAG_NO_FUSED_DECODE)
+    tc2 = triton_qwen36_batched_moe_decode(hidden, *w.tuple(), router_bias=w.router_bias,
+                                           flags=_lib.FLAG_FORCE_TENSOR | _lib.FLAG_NO_FUSED_DECODE)
+    assert torch.equal(tc[2], gemv[2]) and torch.equal(tc[0], tc2[0])
+    check_output(tc[0], gemv[0].cpu(), torch.bfloat16)
+    sample = torch.arange(0, tokens, max(1, tokens // 6))
+    ref = oracle_layer(hidden[sample.cuda()], w, 8)
+    if torch.equal(tc[2].cpu()[sample], ref.topk_ids):
+        check_output(tc[0][sample.cuda()], ref.output, torch.bfloat16)
+
+
+def test_tensor_core_path_hot_experts_and_fp32_hidden():
+    """Groups taller than one 64-row pass (hot experts), and fp32 activations converted on the way in."""
+    w = make_moe_weights(2, REAL, dtype=torch.bfloat16, device="cuda", hot_experts=HOT_EXPERT_IDS, hot_boost=6.0)
+    hidden = make_hidden(77, 192, REAL, dtype=torch.float32, device="cuda")
+    out, logits, ids, weights = triton_qwen36_batched_moe_decode(hidden, *w.tuple(), router_bias=w.router_bias)
+    hist = triton_expert_histogram(ids, 256).cpu()
+    assert int(hist.max()) > 64                       # at least one group needs several passes
+    sample = torch.arange(0, 192, 24)
+    ref = oracle_layer(hidden[sample.cuda()], w, 8)
+    assert torch.equal(ids.cpu()[sample][ref.margin > 2e-6], ref.topk_ids[ref.margin > 2e-6])
+    if torch.equal(ids.cpu()[sample], ref.topk_ids):
+        check_output(out[sample.cuda()], ref.output, torch.bfloat16)
+
+
 def test_full_layer_fp32_hidden_with_bf16_weights(real_bf16):
     w = real_bf16
     hidden = make_hidden(11, 4, REAL, dtype=torch.float32, device="cuda")
