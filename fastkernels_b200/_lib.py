@@ -55,6 +55,7 @@ SIGNATURES = {
     "fk_moe_workspace_bytes": (C.c_size_t, [C.POINTER(Dims)]),
     "fk_moe_workspace_init": (C.c_int, [C.c_void_p, C.c_size_t, C.c_void_p]),
     "fk_moe_router": (C.c_int, [C.POINTER(Call), C.c_void_p]),
+    "fk_moe_router_noalloc": (C.c_int, [C.POINTER(Call), C.c_void_p]),
     "fk_moe_experts": (C.c_int, [C.POINTER(Call), C.c_void_p]),
     "fk_moe_layer": (C.c_int, [C.POINTER(Call), C.c_void_p]),
     "fk_moe_host_staging_bytes": (C.c_size_t, [C.POINTER(Dims), C.c_int]),

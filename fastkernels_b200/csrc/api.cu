@@ -198,6 +198,25 @@ int fk_moe_router(const fk_moe_call* c, void* stream) {
     return launch_router(rp, c->weight_dtype, (cudaStream_t)stream);
 }
 
+int fk_moe_router_noalloc(const fk_moe_call* c, void* stream) {
+    if (c == nullptr || !dims_ok(c->dims, true) || c->dims.top_k > c->dims.experts) return FK_ERR_ARG;
+    if (!dtype_ok(c->hidden_dtype) || !dtype_ok(c->weight_dtype)) return FK_ERR_UNSUPPORTED;
+    if (c->dims.tokens > FK_NOALLOC_MAX_TOKENS) {
+        snprintf(g_last_error, sizeof(g_last_error), "fk_moe_router_noalloc: %d tokens exceed the built-in scratch (max %d)",
+                 c->dims.tokens, FK_NOALLOC_MAX_TOKENS);
+        return FK_ERR_ARG;
+    }
+    if (c->dims.tokens == 0) return FK_OK;
+    if (!c->hidden || !c->norm_weight || !c->router_weight || !c->logits || !c->topk_ids || !c->topk_weights) return FK_ERR_ARG;
+    RouterParams rp{};
+    rp.hidden = c->hidden; rp.hidden_dtype = c->hidden_dtype;
+    rp.norm_weight = c->norm_weight; rp.router_weight = c->router_weight; rp.router_bias = c->router_bias;
+    rp.logits = c->logits; rp.topk_ids = reinterpret_cast<long long*>(c->topk_ids); rp.topk_weights = c->topk_weights;
+    rp.T = c->dims.tokens; rp.H = c->dims.hidden; rp.E = c->dims.experts; rp.top_k = c->dims.top_k;
+    rp.eps = c->eps; rp.norm_offset = c->norm_offset;
+    return launch_router_noalloc(rp, c->weight_dtype, (cudaStream_t)stream);
+}
+
 int fk_moe_experts(const fk_moe_call* c, void* stream) {
     if (c == nullptr || !dims_ok(c->dims, false)) return FK_ERR_ARG;
     if (!dtype_ok(c->hidden_dtype) || !dtype_ok(c->weight_dtype)) return FK_ERR_UNSUPPORTED;

@@ -22,6 +22,7 @@ struct RouterParams {
     float eps, norm_offset;
 };
 int launch_router(const RouterParams& p, int weight_dtype, cudaStream_t stream);
+int launch_router_noalloc(RouterParams p, int weight_dtype, cudaStream_t stream);   // tickets in a static device array
 
 struct PermuteParams {
     const long long* ids64;   // one of ids64 / ids32 is set

@@ -246,3 +246,45 @@ int launch_router(const RouterParams& p, int weight_dtype, cudaStream_t stream) 
 }
 
 }  // namespace fk
+
+// ---------------------------------------------------------------------------------------------
+// Router without caller-provided scratch (fk_moe_router_noalloc)
+// ---------------------------------------------------------------------------------------------
+// The router's only scratch is its "last block" tickets.  Here they live in a fixed array inside the
+// library image instead of the caller's workspace, so a caller that cannot allocate device memory
+// (and therefore has no workspace to hand over) can still route tokens.
+namespace fk {
+
+constexpr int kNoAllocTicketSlots = 1024;      // 4 KB per device; one slot per token tile
+static __device__ __align__(256) unsigned g_noalloc_tickets[kNoAllocTicketSlots];
+
+// Device address of the array for the current device.  In host code the symbol's name is only a
+// handle; the address a kernel can use has to be asked for, once per device, with that device current.
+static int noalloc_tickets(unsigned** out) {
+    static unsigned* cached[64] = {nullptr};
+    int dev = 0;
+    FK_CUDA_OK(cudaGetDevice(&dev), "noalloc get device");
+    if (dev < 0 || dev >= 64) return FK_ERR_UNSUPPORTED;
+    if (cached[dev] == nullptr) {
+        unsigned* ptr = nullptr;
+        FK_CUDA_OK(cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_noalloc_tickets), "noalloc symbol address");
+        if (ptr == nullptr) return FK_ERR_CUDA;
+        cached[dev] = ptr;
+    }
+    *out = cached[dev];
+    return FK_OK;
+}
+
+int launch_router_noalloc(RouterParams p, int weight_dtype, cudaStream_t stream) {
+    const int tpb = p.T <= 64 ? 4 : 8;                       // tokens per block, as launch_router picks them
+    if ((p.T + tpb - 1) / tpb > kNoAllocTicketSlots) return FK_ERR_ARG;
+    unsigned* tickets = nullptr;
+    int st = noalloc_tickets(&tickets);
+    if (st != FK_OK) return st;
+    // every call shares the array and finds what the previous call left: start from zero
+    FK_CUDA_OK(cudaMemsetAsync(tickets, 0, sizeof(unsigned) * kNoAllocTicketSlots, stream), "noalloc ticket clear");
+    p.tickets = tickets;
+    return launch_router(p, weight_dtype, stream);
+}
+
+}  // namespace fk

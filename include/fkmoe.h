@@ -123,6 +123,24 @@ int fk_moe_workspace_init(void* workspace, size_t bytes, void* stream);
  * src/fastkernels/reference/qwen36_real.py:333-337. */
 int fk_moe_router(const fk_moe_call* call, void* stream);
 
+/* The router for callers that cannot allocate device memory.  No counterpart in the reference.
+ * Some hosts may not call cudaMalloc at all: a plugin whose device memory is entirely owned and
+ * budgeted by its framework, a serving loop with a latency bound that must never enter the
+ * allocator, a sandboxed extension that is only handed input and output buffers.  fk_moe_router needs a workspace (for its per-tile completion
+ * tickets) that such a caller has nowhere to get from.  This variant keeps the tickets in a fixed
+ * 4 KB array inside the library image (every GPU that loads the library holds it until exit), so the
+ * caller passes only inputs and outputs: call->workspace is ignored.  It calls no cudaMalloc, no
+ * cudaFree and no allocating library routine.
+ *   - at most FK_NOALLOC_MAX_TOKENS tokens per call; more is refused with FK_ERR_ARG and a message
+ *     in fk_last_cuda_error();
+ *   - the first call on each device looks the array's device address up (with that device current);
+ *     make that first call before any stream capture begins;
+ *   - all calls on a device share the one array, cleared on `stream` at the start of every call:
+ *     calls that overlap on the GPU (different streams) race on it, so keep them on one stream or
+ *     otherwise ordered. */
+#define FK_NOALLOC_MAX_TOKENS 4096
+int fk_moe_router_noalloc(const fk_moe_call* call, void* stream);
+
 /* Routed experts (+ optional shared expert, + optional sigmoid gate) for routing given in
  * call->topk_ids_in / topk_weights_in; writes call->out (and layer_hidden if set).
  * Replaces triton_qwen36_{,batched_}routed_experts_decode and
