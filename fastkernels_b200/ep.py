@@ -150,3 +150,49 @@ def ep_payload_bytes(tokens: int, hidden_size: int, top_k: int, world: int, hidd
         "dispatch": remote * tokens * (hidden_size * hidden_bytes + top_k * 12),
         "combine": remote * tokens * hidden_size * 4,
     }
+
+
+class EPDecodePlan:
+    """One rank's expert-parallel layer call with fixed shapes, captured in a CUDA graph.
+
+    The eager `ep_moe_layer` issues a dozen small launches and three collectives from Python; at
+    decode sizes that host work is longer than the GPU work.  Every shape in the exchange is fixed, so
+    the whole call (router, gathers, local experts, all-to-all, rank-ordered sum) is captured once and
+    replayed.  All ranks must construct and run their plans in the same order.
+    """
+
+    def __init__(self, shard: EPShard, tokens: int, *, hidden_dtype=torch.bfloat16, top_k: int = 8, eps: float = 1e-6,
+                 residual: bool = False, group: Optional[dist.ProcessGroup] = None, capture: bool = True):
+        self.shard, self.group, self.top_k, self.eps, self.residual = shard, group, top_k, eps, residual
+        dev = shard.weights.expert_gate_up_weight.device
+        H = shard.weights.router_weight.shape[1]
+        self.hidden = torch.zeros((tokens, H), dtype=hidden_dtype, device=dev)
+        self.graph = None
+        self.out = self.logits = self.topk_ids = self.topk_weights = None
+        # warm-up outside capture: NCCL channels, workspaces, kernel attributes
+        side = torch.cuda.Stream(device=dev)
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(2):
+                self._call()
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize(dev)
+        if capture:
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                self._call()
+            self.graph = g
+
+    def _call(self):
+        self.out, self.logits, self.topk_ids, self.topk_weights = ep_moe_layer(
+            self.hidden, self.shard, top_k=self.top_k, eps=self.eps, group=self.group, residual=self.residual)
+
+    def run(self, hidden: Optional[torch.Tensor] = None):
+        """Returns `(out, logits, topk_ids, topk_weights)`; the tensors are reused by the next run."""
+        if hidden is not None:
+            self.hidden.copy_(hidden, non_blocking=True)
+        if self.graph is not None:
+            self.graph.replay()
+        else:
+            self._call()
+        return self.out, self.logits, self.topk_ids, self.topk_weights
