@@ -62,6 +62,7 @@ SIGNATURES = {
     "fk_moe_layer_host": (C.c_int, [C.POINTER(Call), C.c_void_p, C.c_size_t, C.c_void_p]),
     "fk_single_expert_mlp": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p,
                                        C.c_int, C.c_int, C.c_void_p, C.c_size_t, C.c_void_p]),
+    "fk_residual_rmsnorm": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_float, C.c_void_p]),
     "fk_fused_swiglu": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int64, C.c_int, C.c_void_p]),
     "fk_expert_histogram": (C.c_int, [C.c_void_p, C.c_int, C.c_int64, C.c_int, C.c_void_p, C.c_void_p]),
     "fk_moe_permute": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p,

@@ -351,6 +351,14 @@ int fk_single_expert_mlp(const void* hidden, int hidden_dtype, const void* gate_
     return fk_moe_experts(&c, stream);
 }
 
+int fk_residual_rmsnorm(float* x, const float* update, void* normed, int out_dtype, int tokens, int hidden_size, float eps,
+                        void* stream) {
+    if (!dtype_ok(out_dtype)) return FK_ERR_UNSUPPORTED;
+    if (tokens < 0 || hidden_size < 1) return FK_ERR_ARG;
+    if (tokens > 0 && (!x || !normed)) return FK_ERR_ARG;
+    return launch_residual_norm(x, update, normed, out_dtype, tokens, hidden_size, eps, (cudaStream_t)stream);
+}
+
 int fk_fused_swiglu(const void* gate_up, void* out, int dtype, int64_t rows, int intermediate, void* stream) {
     if (!dtype_ok(dtype)) return FK_ERR_UNSUPPORTED;
     if (rows > 0 && intermediate > 0 && (!gate_up || !out)) return FK_ERR_ARG;

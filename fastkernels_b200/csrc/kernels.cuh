@@ -112,6 +112,8 @@ bool decode1_supported(const DecodeParams& p, int weight_dtype);
 int launch_decode1(const DecodeParams& p, cudaStream_t stream);
 int sm_count();
 
+int launch_residual_norm(float* x, const float* update, void* normed, int out_dtype, int T, int H, float eps, cudaStream_t stream);
+
 int launch_swiglu(const void* gate_up, void* out, int dtype, long long rows, int I, cudaStream_t stream);
 
 }  // namespace fk

@@ -24,7 +24,8 @@ from .spec import MoEWeights
 class MoEDecodePlan:
     def __init__(self, weights: MoEWeights, tokens: int, *, hidden_dtype: torch.dtype = torch.bfloat16,
                  top_k: int = 8, eps: float = 1e-6, norm_offset: float = 1.0, residual: bool = False,
-                 flags: int = 0, device: Optional[torch.device] = None):
+                 flags: int = 0, device: Optional[torch.device] = None, hidden_buffer: Optional[torch.Tensor] = None,
+                 out_buffer: Optional[torch.Tensor] = None):
         self.lib = _lib.load()
         w = weights
         dev = device or w.expert_gate_up_weight.device
@@ -42,8 +43,9 @@ class MoEDecodePlan:
             _as_weight(w.shared_down_weight, wdt), _as_weight(w.shared_expert_gate_weight, wdt),
             None if w.router_bias is None else w.router_bias.to(device=dev, dtype=torch.float32).contiguous(),
         ]
-        self.hidden = torch.zeros((tokens, H), device=dev, dtype=hidden_dtype)
-        self.out = torch.empty((tokens, H), device=dev, dtype=torch.float32)
+        # buffers may be shared between the plans of a layer stack
+        self.hidden = hidden_buffer if hidden_buffer is not None else torch.zeros((tokens, H), device=dev, dtype=hidden_dtype)
+        self.out = out_buffer if out_buffer is not None else torch.empty((tokens, H), device=dev, dtype=torch.float32)
         self.layer_hidden = torch.empty_like(self.out) if residual else None
         self.logits = torch.empty((tokens, E), device=dev, dtype=torch.float32)
         self.topk_ids = torch.empty((tokens, top_k), device=dev, dtype=torch.int64)

@@ -1,0 +1,86 @@
+"""A stack of MoE layers run back to back: x <- x + MoE_l(RMSNorm(x)), unit-gain norm, eps 1e-6.
+
+This is the decode loop of the benchmark's 40-layer configuration with the sequence mixers left
+out.  The reference composes its layers in Python, one call and one residual add per layer
+(src/fastkernels/kernels/triton/qwen36_layer.py:55-106; the streaming runner
+bench/qwen36_full_decode.py:409-419 reloads the weights of every layer from disk).  Here all
+layers stay resident in HBM, the residual add and the next layer's norm are one kernel
+(fk_residual_rmsnorm), and the whole stack is one CUDA graph.
+
+The residual stream `x` is fp32; the normed activations handed to each layer are bf16.
+Works on one GPU (`MoEWeights` per layer) or expert parallel (`EPShard` per layer plus a group).
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+from typing import Optional, Sequence
+
+import torch
+
+from . import _lib
+from .plan import MoEDecodePlan
+
+
+class MoEStackPlan:
+    def __init__(self, layers: Sequence, tokens: int, *, top_k: int = 8, eps: float = 1e-6, norm_eps: float = 1e-6,
+                 act_dtype: torch.dtype = torch.bfloat16, group=None, capture: bool = True, flags: int = 0):
+        from .ep import EPShard
+        self.lib = _lib.load()
+        self.layers = list(layers)
+        self.ep = isinstance(self.layers[0], EPShard)
+        w0 = self.layers[0].weights if self.ep else self.layers[0]
+        dev = w0.expert_gate_up_weight.device
+        H = w0.router_weight.shape[1]
+        self.device, self.tokens, self.hidden_size = dev, tokens, H
+        self.top_k, self.eps, self.norm_eps, self.group = top_k, eps, norm_eps, group
+        self.act_code = {torch.float32: 0, torch.bfloat16: 1, torch.float16: 2}[act_dtype]
+        self.x = torch.zeros((tokens, H), device=dev, dtype=torch.float32)        # residual stream (input and output)
+        self.xin = torch.zeros((tokens, H), device=dev, dtype=act_dtype)          # normed activations of the current layer
+        self.topk_ids = []
+        self.graph = None
+        if not self.ep:
+            self.update = torch.zeros((tokens, H), device=dev, dtype=torch.float32)
+            self.plans = [MoEDecodePlan(w, tokens, hidden_dtype=act_dtype, top_k=top_k, eps=eps, flags=flags,
+                                        hidden_buffer=self.xin, out_buffer=self.update) for w in self.layers]
+        side = torch.cuda.Stream(device=dev)
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            self._forward()
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize(dev)
+        if capture:
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                self._forward()
+            self.graph = g
+
+    def _norm(self, update: Optional[torch.Tensor]) -> None:
+        st = self.lib.fk_residual_rmsnorm(self.x.data_ptr(), None if update is None else update.data_ptr(), self.xin.data_ptr(),
+                                          self.act_code, self.tokens, self.hidden_size, self.norm_eps,
+                                          torch.cuda.current_stream().cuda_stream)
+        _lib.check(st, "fk_residual_rmsnorm")
+
+    def _forward(self) -> None:
+        from .ep import ep_moe_layer
+        update = None
+        self.topk_ids = []
+        for i, layer in enumerate(self.layers):
+            self._norm(update)                       # x += previous update; xin = RMSNorm(x)
+            if self.ep:
+                update, _, ids, _ = ep_moe_layer(self.xin, layer, top_k=self.top_k, eps=self.eps, group=self.group)
+            else:
+                self.plans[i].launch()
+                update, ids = self.update, self.plans[i].topk_ids
+            self.topk_ids.append(ids)
+        self._norm(update)                           # x += last update (xin then holds the norm of the result)
+
+    def run(self, x: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Runs the stack in place on `self.x` (copying `x` in first if given) and returns `self.x`."""
+        if x is not None:
+            self.x.copy_(x, non_blocking=True)
+        if self.graph is not None:
+            self.graph.replay()
+        else:
+            self._forward()
+        return self.x

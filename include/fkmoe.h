@@ -171,6 +171,13 @@ int fk_single_expert_mlp(const void* hidden, int hidden_dtype, const void* gate_
                          int weight_dtype, float* out, int hidden_size, int intermediate,
                          void* workspace, size_t workspace_bytes, void* stream);
 
+/* Layer boundary of a stack of MoE layers: x[t,:] += update[t,:] (fp32, in place; update may be NULL),
+ * then normed[t,:] = x[t,:] * rsqrt(mean(x[t,:]^2) + eps) in `out_dtype` (unit gain).
+ * The reference composes layers in Python (hidden + update, src/fastkernels/kernels/triton/qwen36_layer.py:94-105,
+ * then the next block's norm, src/fastkernels/reference/qwen36_real.py:23-28); this is that step as one kernel. */
+int fk_residual_rmsnorm(float* x, const float* update, void* normed, int out_dtype, int tokens, int hidden_size,
+                        float eps, void* stream);
+
 /* out[n,c] = silu(gate_up[n,c]) * gate_up[n,I+c], fp32 math, stored in the input dtype.
  * Replaces triton_fused_swiglu (src/fastkernels/kernels/triton/moe.py:67); oracle
  * reference_fused_swiglu (src/fastkernels/reference/moe.py:16). */

@@ -252,21 +252,24 @@ def synthetic_moe_decode(hidden, norm_weight, router_weight, expert_gate_up_weig
     return (x + res.output)[0]
 
 
-def moe_stack(hidden, layers, *, top_k: int = 8, eps: float = 1e-6):
+def moe_stack(hidden, layers, *, top_k: int = 8, eps: float = 1e-6, act_dtype=None, return_ids: bool = False):
     """`x <- x + MoE_l(RMSNorm(x))` over a list of layer weight tuples (unit-gain norm, eps 1e-6).
 
     The outer norm output is the layer's input: router, experts, shared expert
     and shared gate all read it (benchmark configuration "stack of 40 layers").
-    Each element of `layers` is the positional weight tuple of `moe_update`.
+    Each element of `layers` is the positional weight tuple of `moe_update`.  The residual stream stays fp32.
     """
     x = hidden.float()
-    unit = None
+    unit = torch.zeros(x.shape[-1])
+    all_ids = []
     for lw in layers:
-        if unit is None:
-            unit = torch.zeros(x.shape[-1])
         xin = rms_norm(x, unit, eps, 1.0)
-        x = x + moe_update(xin, *lw, top_k=top_k, eps=eps).output
-    return x
+        if act_dtype is not None:
+            xin = xin.to(act_dtype)          # activations between layers are stored in this dtype
+        res = moe_update(xin, *lw, top_k=top_k, eps=eps)
+        all_ids.append(res.topk_ids)
+        x = x + res.output
+    return (x, all_ids) if return_ids else x
 
 
 # --------------------------------------------------------------------------- #

@@ -483,3 +483,22 @@ def test_full_size_batches_properties(tokens, hot):
     assert torch.equal(ids.cpu()[sample][clear], ref.topk_ids[clear])
     if bool(clear.all()):
         check_output(out[sample.cuda()], ref.output, torch.bfloat16)
+
+
+# ---------------------------------------------------------------- layer stack
+@pytest.mark.parametrize("tokens", [1, 3])
+def test_layer_stack_matches_oracle(tokens):
+    """x <- x + MoE_l(RMSNorm(x)) over three real-shape layers, one CUDA graph, against the oracle."""
+    from fastkernels_b200.stack import MoEStackPlan
+    layers = [make_moe_weights(50 + l, REAL, dtype=torch.bfloat16, device="cuda") for l in range(3)]
+    x0 = make_hidden(60, tokens, REAL, dtype=torch.float32, device="cuda")
+    plan = MoEStackPlan(layers, tokens)
+    out = plan.run(x0).clone()
+    out2 = plan.run(x0).clone()
+    assert torch.equal(out, out2)
+    ref, ref_ids = O.moe_stack(x0.cpu(), [[None if t is None else t.cpu() for t in w.tuple()] for w in layers],
+                               act_dtype=torch.bfloat16, return_ids=True)
+    same = all(torch.equal(a.cpu(), b) for a, b in zip(plan.topk_ids, ref_ids))
+    if same:
+        delta, ref_delta = (out - x0).cpu(), ref - x0.cpu()
+        assert O.max_abs(delta, ref_delta) <= 2e-2 and O.rel_l2(delta, ref_delta) <= 5e-3
