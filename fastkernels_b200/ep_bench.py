@@ -7,6 +7,7 @@ expert.  Timing: barrier + synchronize on both sides of the K steps, CUDA events
 
 from __future__ import annotations
 
+import datetime
 import json
 import os
 import statistics
@@ -31,7 +32,8 @@ def run_ep(args, workload_config, measured_peak, ClockSampler, METRIC, UNIT):
     if not dist.is_initialized():
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         os.environ.setdefault("MASTER_PORT", "29500")
-        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+        # a rank that fails must not leave the others waiting for the default ten minutes
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev, timeout=datetime.timedelta(seconds=90))
     spec = MoESpec()
     peak, peak_src = measured_peak()
     B, K, W, L = args.batch, args.steps, max(args.warmup, 3), args.layers
@@ -46,7 +48,7 @@ def run_ep(args, workload_config, measured_peak, ClockSampler, METRIC, UNIT):
     hid_host = [make_hidden(1000 + i * world + rank, B, spec, dtype=torch.bfloat16).pin_memory() for i in range(pool)]
     hid_dev = [h.to(dev) for h in hid_host]
 
-    plans = [EPDecodePlan(sh, B, capture=not args.eager) for sh in shards]
+    plans = [EPDecodePlan(sh, B, capture=args.ep_graph) for sh in shards]
     for i, pl in enumerate(plans):              # inputs are resident before the timed region starts
         pl.hidden.copy_(hid_dev[i % pool])
 
