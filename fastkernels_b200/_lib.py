@@ -33,6 +33,7 @@ class Call(C.Structure):
         ("hidden_dtype", C.c_int32), ("weight_dtype", C.c_int32),
         ("eps", C.c_float), ("norm_offset", C.c_float),
         ("flags", C.c_uint32), ("expert_base", C.c_int32),
+        ("shared_token_base", C.c_int32), ("shared_token_count", C.c_int32),
         ("hidden", C.c_void_p), ("norm_weight", C.c_void_p), ("router_weight", C.c_void_p),
         ("router_bias", C.c_void_p),
         ("expert_gate_up", C.c_void_p), ("expert_down", C.c_void_p),

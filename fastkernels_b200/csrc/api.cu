@@ -58,7 +58,12 @@ static int run_experts(const fk_moe_call* c, const Workspace& w, const long long
     pp.inv = at<int>(ws, w.inv);
     pp.meta = at<int>(ws, w.meta);
     pp.passes = at<int4>(ws, w.passes);
-    pp.shared_tokens = c->shared_gate_up ? d.tokens : 0;
+    // the shared expert may be asked for a sub-range of the tokens (expert parallel: the home rank's own tokens)
+    int sh_n = c->shared_token_count > 0 ? c->shared_token_count : d.tokens;
+    int sh0 = c->shared_token_count > 0 ? c->shared_token_base : 0;
+    if (sh0 < 0 || sh0 + sh_n > d.tokens) return FK_ERR_ARG;
+    pp.shared_tokens = c->shared_gate_up ? sh_n : 0;
+    pp.shared_tok0 = sh0;
 
     ExpertParams ep{};
     ep.hidden = c->hidden;
@@ -69,6 +74,7 @@ static int run_experts(const fk_moe_call* c, const Workspace& w, const long long
     ep.shared_down = c->shared_gate_up ? c->shared_down : nullptr;
     ep.T = d.tokens; ep.H = d.hidden; ep.E = d.experts; ep.I = d.intermediate; ep.top_k = d.top_k;
     ep.routes = pp.routes;
+    ep.shared_tok0 = sh0; ep.shared_n = sh_n;
     // path choice: tensor cores from 64 tokens up (or when forced), bulk-copy GEMV below
     const bool generic = (c->flags & FK_FLAG_FORCE_GENERIC) != 0;
     const bool want_tc = !generic && !(c->flags & (FK_FLAG_FORCE_GEMV | FK_FLAG_REGISTER_GEMV)) &&
@@ -93,7 +99,7 @@ static int run_experts(const fk_moe_call* c, const Workspace& w, const long long
         st = launch_experts_tc(ep, at<__nv_bfloat16>(ws, w.xg), at<__nv_bfloat16>(ws, w.actb), stream);
     else if (!generic && !(c->flags & FK_FLAG_REGISTER_GEMV) && stream_path_supported(ep, c->weight_dtype))
         st = launch_experts_stream(ep, stream);
-    else if (!generic && gemv_path_supported(ep, c->weight_dtype))
+    else if (!generic && sh_n == d.tokens && gemv_path_supported(ep, c->weight_dtype))
         st = launch_experts_gemv(ep, stream);
     else
         st = launch_experts_generic(ep, c->weight_dtype, stream);

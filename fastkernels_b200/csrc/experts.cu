@@ -36,14 +36,14 @@ __global__ void gate_up_generic_kernel(ExpertParams p) {
     const long long warp = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
     const long long nwarps = ((long long)gridDim.x * blockDim.x) >> 5;
     const int routed_rows = p.offsets[p.E];
-    const int shared_rows = p.shared_gate_up ? p.T : 0;
+    const int shared_rows = p.shared_gate_up ? p.shared_n : 0;
     const long long total = (long long)(p.routes + shared_rows) * p.I;
     for (long long w = warp; w < total; w += nwarps) {
         int pos = (int)(w / p.I), i = (int)(w - (long long)pos * p.I);
         const WT* wbase;
         int token;
         if (pos >= p.routes) {
-            token = pos - p.routes;
+            token = p.shared_tok0 + pos - p.routes;
             wbase = reinterpret_cast<const WT*>(p.shared_gate_up);
         } else {
             if (pos >= routed_rows) continue;
@@ -71,7 +71,7 @@ __global__ void down_generic_kernel(ExpertParams p) {
     const long long warp = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
     const long long nwarps = ((long long)gridDim.x * blockDim.x) >> 5;
     const int routed_rows = p.offsets[p.E];
-    const int shared_rows = p.shared_down ? p.T : 0;
+    const int shared_rows = p.shared_down ? p.shared_n : 0;
     const long long total = (long long)(p.routes + shared_rows) * p.H;
     for (long long w = warp; w < total; w += nwarps) {
         int pos = (int)(w / p.H), h = (int)(w - (long long)pos * p.H);
@@ -93,7 +93,7 @@ __global__ void down_generic_kernel(ExpertParams p) {
 
 int launch_experts_generic(const ExpertParams& p, int weight_dtype, cudaStream_t stream) {
     if (p.T <= 0) return FK_OK;
-    const int shared_rows = p.shared_gate_up ? p.T : 0;
+    const int shared_rows = p.shared_gate_up ? p.shared_n : 0;
     long long gu_warps = (long long)(p.routes + shared_rows) * p.I;
     long long dn_warps = (long long)(p.routes + shared_rows) * p.H;
     auto blocks = [](long long warps) { long long b = (warps + 7) / 8; return (int)(b > 148 * 16 ? 148 * 16 : (b < 1 ? 1 : b)); };
@@ -136,8 +136,8 @@ __global__ void combine_kernel(ExpertParams p) {
             int pos = p.inv[t * p.top_k + s];
             if (pos >= 0) acc = fmaf(p.topk_weights[t * p.top_k + s], p.y[(size_t)pos * p.H + h], acc);
         }
-        if (p.shared_down) {
-            float sh = p.y[(size_t)(p.routes + t) * p.H + h];
+        if (p.shared_down && t >= p.shared_tok0 && t < p.shared_tok0 + p.shared_n) {
+            float sh = p.y[(size_t)(p.routes + t - p.shared_tok0) * p.H + h];
             acc += p.shared_gate ? p.shared_gate[t] * sh : sh;
         }
         p.out[i] = acc;

@@ -39,6 +39,7 @@ struct PermuteParams {
     int* meta;                // [0] = number of experts with count>0, [1] = number of passes (optional)
     int4* passes;             // optional GEMV pass list: routed experts ascending, then the shared expert
     int shared_tokens;        // tokens the shared expert sees (0: no shared expert)
+    int shared_tok0;          // first of them
     int pass_rows;            // rows per pass: 4 for the GEMV kernels, 64 for the tensor-core GEMM
 };
 int launch_permute(const PermuteParams& p, cudaStream_t stream);
@@ -53,6 +54,7 @@ struct ExpertParams {
     const void* shared_down;
     int T, H, E, I, top_k;
     int routes;                   // T*k
+    int shared_tok0, shared_n;    // the shared expert runs on tokens [shared_tok0, shared_tok0 + shared_n)
     const int* counts;
     const int* offsets;
     const int* touched;

@@ -101,7 +101,7 @@ __global__ void __launch_bounds__(kPermWarps * 32) permute_kernel(PermuteParams 
             __syncthreads();
             const int sp = (p.shared_tokens + PR - 1) / PR;
             for (int j = tid; j < sp; j += blockDim.x)
-                p.passes[routed_passes + j] = make_int4(-1, p.routes + PR * j, min(PR, p.shared_tokens - PR * j), PR * j);
+                p.passes[routed_passes + j] = make_int4(-1, p.routes + PR * j, min(PR, p.shared_tokens - PR * j), p.shared_tok0 + PR * j);
             if (tid == 0 && p.meta) p.meta[1] = routed_passes + sp;
         }
     }

@@ -185,13 +185,13 @@ tc_grouped_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constan
 // packed bf16 activations: xg[pos] = hidden[token of packed row pos]; the shared expert's rows follow
 __global__ void gather_rows_kernel(ExpertParams p, __nv_bfloat16* xg) {
     const int routed = p.offsets[p.E];
-    const int shared_rows = p.shared_gate_up ? p.T : 0;
+    const int shared_rows = p.shared_gate_up ? p.shared_n : 0;
     const int chunks = p.H / 8;
     const long long total = (long long)(p.routes + shared_rows) * chunks;
     for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
         const int pos = (int)(i / chunks), c = (int)(i - (long long)pos * chunks);
         int token;
-        if (pos >= p.routes) token = pos - p.routes;
+        if (pos >= p.routes) token = p.shared_tok0 + pos - p.routes;
         else if (pos < routed) token = p.order[pos] / p.top_k;
         else continue;
         const size_t src = (size_t)token * p.H + c * 8;
@@ -277,7 +277,7 @@ bool tc_path_supported(const ExpertParams& p, int weight_dtype) {
 // gather -> gate_up GEMM (+SwiGLU) -> down GEMM; the pass list in p.passes must hold passes of <= 64 rows
 int launch_experts_tc(const ExpertParams& p, __nv_bfloat16* xg, __nv_bfloat16* actb, cudaStream_t stream) {
     if (p.T <= 0) return FK_OK;
-    const uint64_t rows = (uint64_t)p.routes + (p.shared_gate_up ? p.T : 0);
+    const uint64_t rows = (uint64_t)p.routes + (p.shared_gate_up ? p.shared_n : 0);
     CUtensorMap w_gu, s_gu, a_x, w_dn, s_dn, a_act;
     const void* dummy_gu = p.gate_up ? p.gate_up : p.shared_gate_up;
     const void* dummy_dn = p.down ? p.down : p.shared_down;

@@ -17,10 +17,11 @@ needs no host synchronisation):
      A token goes to every rank that owns one of its 8 experts (5.3 of 8 ranks on average), so
      the fixed-shape gather moves 1.5x the rows a routed all-to-all would, and in exchange
      needs no split-size exchange.
-  3. local experts on all G*T tokens, foreign ids skipped, routing weights applied, slots in order
-                                                                      (fk_moe_experts, FK_FLAG_SKIP_FOREIGN)
+  3. local experts on all G*T tokens, foreign ids skipped, routing weights applied, slots in order,
+     plus the gated shared expert for the rank's own tokens         (one fk_moe_experts call,
+                                                                      FK_FLAG_SKIP_FOREIGN, shared_token_base/count)
   4. combine: all-to-all of the per-rank partial rows back to the tokens' home ranks   (NCCL)
-  5. home rank: partials summed in rank order + gated shared expert (+ residual)
+  5. home rank: the G partials of a token summed (+ residual)
 Results do not depend on scheduling: every sum has a fixed order.
 
 The exchange code is backend-agnostic (gloo on CPU in the tests); the compute steps default to
@@ -76,29 +77,21 @@ def _cuda_router(hidden, w: MoEWeights, top_k, eps):
                                             router_bias=w.router_bias)
 
 
-def _cuda_local_experts(hidden_all, ids_all, weights_all, shard: EPShard):
-    from .moe import qwen36_batched_routed_experts_decode
-    w = shard.weights
-    return qwen36_batched_routed_experts_decode(hidden_all, ids_all, weights_all, w.expert_gate_up_weight,
-                                                w.expert_down_weight, flags=_lib.FLAG_SKIP_FOREIGN,
-                                                expert_base=shard.expert_base)
-
-
-def _cuda_shared_expert(hidden, w: MoEWeights):
+def _cuda_local_experts(hidden_all, ids_all, weights_all, shard: EPShard, own: tuple):
+    """Local routed experts for every gathered token plus the (gated) shared expert for this rank's own
+    tokens `[own[0], own[0] + own[1])`, in one library call."""
     from .moe import _experts
-    T = hidden.shape[0]
-    ids = torch.empty((T, 0), dtype=torch.int64, device=hidden.device)
-    wts = torch.empty((T, 0), dtype=torch.float32, device=hidden.device)
-    # a layer with no routed slots: only the (gated) shared expert contributes
-    return _experts(hidden, ids, wts, w.expert_gate_up_weight[:1], w.expert_down_weight[:1], w.shared_gate_up_weight,
-                    w.shared_down_weight, w.shared_expert_gate_weight)
+    w = shard.weights
+    return _experts(hidden_all, ids_all, weights_all, w.expert_gate_up_weight, w.expert_down_weight,
+                    w.shared_gate_up_weight, w.shared_down_weight, w.shared_expert_gate_weight,
+                    flags=_lib.FLAG_SKIP_FOREIGN, expert_base=shard.expert_base,
+                    shared_token_range=own if w.shared_gate_up_weight is not None else None)
 
 
 # --------------------------------------------------------------------------- the layer
 def ep_moe_layer(hidden: torch.Tensor, shard: EPShard, *, top_k: int = 8, eps: float = 1e-6,
                  group: Optional[dist.ProcessGroup] = None, residual: bool = False,
-                 router_fn: Optional[Callable] = None, local_experts_fn: Optional[Callable] = None,
-                 shared_expert_fn: Optional[Callable] = None):
+                 router_fn: Optional[Callable] = None, local_experts_fn: Optional[Callable] = None):
     """One expert-parallel layer call for this rank's `hidden [T,H]`.
 
     Returns `(output [T,H] f32, logits [T,E] f32, topk_ids [T,k] i64, topk_weights [T,k] f32)`;
@@ -109,35 +102,32 @@ def ep_moe_layer(hidden: torch.Tensor, shard: EPShard, *, top_k: int = 8, eps: f
     world = dist.get_world_size(group)
     if world != shard.world:
         raise ValueError("shard was built for a different world size")
-    if not hidden.is_cuda and (router_fn is None or local_experts_fn is None or shared_expert_fn is None):
+    if not hidden.is_cuda and (router_fn is None or local_experts_fn is None):
         raise RuntimeError("expert-parallel MoE needs CUDA tensors: there is no CPU path in the product")
     router_fn = router_fn or _cuda_router
     local_experts_fn = local_experts_fn or _cuda_local_experts
-    shared_expert_fn = shared_expert_fn or _cuda_shared_expert
     w = shard.weights
     T, H = hidden.shape
 
     logits, ids, weights = router_fn(hidden, w, top_k, eps)
 
-    # dispatch (fixed shape): every rank sees every token and its routing
+    # dispatch (fixed shape): every rank sees every token and its routing.  ids and weights travel in one
+    # int32 buffer (weights bit-cast), so the dispatch is two collectives.
+    routing = torch.cat([ids.to(torch.int32), weights.contiguous().view(torch.int32)], dim=1).contiguous()
     hidden_all = torch.empty((world * T, H), dtype=hidden.dtype, device=hidden.device)
-    ids_all = torch.empty((world * T, top_k), dtype=ids.dtype, device=hidden.device)
-    weights_all = torch.empty((world * T, top_k), dtype=weights.dtype, device=hidden.device)
+    routing_all = torch.empty((world * T, 2 * top_k), dtype=torch.int32, device=hidden.device)
     dist.all_gather_into_tensor(hidden_all, hidden.contiguous(), group=group)
-    dist.all_gather_into_tensor(ids_all, ids.contiguous(), group=group)
-    dist.all_gather_into_tensor(weights_all, weights.contiguous(), group=group)
+    dist.all_gather_into_tensor(routing_all, routing, group=group)
+    ids_all = routing_all[:, :top_k].to(torch.int64)
+    weights_all = routing_all[:, top_k:].contiguous().view(torch.float32)
 
-    partial = local_experts_fn(hidden_all, ids_all, weights_all, shard)          # [world*T, H] f32
-    shared = shared_expert_fn(hidden, w) if w.shared_gate_up_weight is not None else None
+    rank = dist.get_rank(group)
+    partial = local_experts_fn(hidden_all, ids_all, weights_all, shard, (rank * T, T))     # [world*T, H] f32
 
     # combine: rows go back to their home rank; chunk g of `recv` is rank g's partial for our tokens
     recv = torch.empty_like(partial)
     dist.all_to_all_single(recv, partial.contiguous(), group=group)
-    out = recv.view(world, T, H)[0].clone()
-    for g in range(1, world):                                                     # fixed rank order
-        out += recv.view(world, T, H)[g]
-    if shared is not None:
-        out += shared
+    out = recv.view(world, T, H).sum(dim=0)                # one kernel, the same order on every call
     if residual:
         out += hidden.float()
     return out, logits, ids, weights

@@ -186,7 +186,8 @@ def _check_expert_weights(hidden_size, expert_gate_up_weight, expert_down_weight
 
 
 def _experts(hidden2d, topk_ids, topk_weights, expert_gate_up_weight, expert_down_weight, shared_gate_up_weight,
-             shared_down_weight, shared_expert_gate_weight, *, flags=0, expert_base=0, residual=False):
+             shared_down_weight, shared_expert_gate_weight, *, flags=0, expert_base=0, residual=False,
+             shared_token_range=None):
     lib = _lib.load()
     tokens, hidden_size = hidden2d.shape
     num_experts, intermediate = _check_expert_weights(hidden_size, expert_gate_up_weight, expert_down_weight)
@@ -215,6 +216,8 @@ def _experts(hidden2d, topk_ids, topk_weights, expert_gate_up_weight, expert_dow
     call.topk_weights_in = _ptr(wts)
     call.out = _ptr(out)
     call.layer_hidden = _ptr(layer)
+    if shared_token_range is not None:
+        call.shared_token_base, call.shared_token_count = shared_token_range
     with torch.cuda.device(dev):
         _lib.check(lib.fk_moe_experts(C.byref(call), _stream()), "fk_moe_experts")
     return (out, layer) if residual else out

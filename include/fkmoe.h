@@ -72,6 +72,8 @@ typedef struct fk_moe_call {
     uint32_t flags;
     int32_t expert_base;           /* expert-parallel shard: ids in [expert_base, expert_base+E) are local,
                                       others are skipped (0 for a whole layer) */
+    int32_t shared_token_base;     /* fk_moe_experts: run the shared expert only on tokens [base, base+count);  */
+    int32_t shared_token_count;    /* count 0 = all tokens (expert parallel: the rank's own tokens among the gathered ones) */
     const void* hidden;
     const void* norm_weight;
     const void* router_weight;

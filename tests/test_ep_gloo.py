@@ -22,16 +22,16 @@ def _router(hidden, w, top_k, eps):
     return O.router(hidden, w.norm_weight, w.router_weight, top_k=top_k, eps=eps, router_bias=w.router_bias)
 
 
-def _local(hidden_all, ids_all, weights_all, shard):
+def _local(hidden_all, ids_all, weights_all, shard, own):
     local = ids_all - shard.expert_base
     mine = (local >= 0) & (local < shard.local_experts)
     ids = torch.where(mine, local, torch.zeros_like(local))
     wts = torch.where(mine, weights_all, torch.zeros_like(weights_all))
-    return O.routed_experts(hidden_all, ids, wts, shard.weights.expert_gate_up_weight, shard.weights.expert_down_weight)
-
-
-def _shared(hidden, w):
-    return O.shared_expert(hidden, w.shared_gate_up_weight, w.shared_down_weight, w.shared_expert_gate_weight)
+    w = shard.weights
+    out = O.routed_experts(hidden_all, ids, wts, w.expert_gate_up_weight, w.expert_down_weight)
+    sl = slice(own[0], own[0] + own[1])
+    out[sl] += O.shared_expert(hidden_all[sl], w.shared_gate_up_weight, w.shared_down_weight, w.shared_expert_gate_weight)
+    return out
 
 
 def _worker(rank, world, port, tokens, failures):
@@ -45,7 +45,7 @@ def _worker(rank, world, port, tokens, failures):
         assert shard.weights.expert_gate_up_weight.shape[0] == SPEC.num_experts // world
         hidden = make_hidden(50 + rank, tokens, SPEC, dtype=torch.float32)
         out, logits, ids, weights = ep_moe_layer(hidden, shard, top_k=2, residual=True, router_fn=_router,
-                                                 local_experts_fn=_local, shared_expert_fn=_shared)
+                                                 local_experts_fn=_local)
         # single-device oracle on the gathered batch
         all_hidden = torch.cat([make_hidden(50 + r, tokens, SPEC, dtype=torch.float32) for r in range(world)])
         ref = O.moe_update(all_hidden, *full.tuple(), top_k=2, router_bias=full.router_bias)

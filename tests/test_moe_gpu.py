@@ -502,3 +502,23 @@ def test_layer_stack_matches_oracle(tokens):
     if same:
         delta, ref_delta = (out - x0).cpu(), ref - x0.cpu()
         assert O.max_abs(delta, ref_delta) <= 2e-2 and O.rel_l2(delta, ref_delta) <= 5e-3
+
+
+@pytest.mark.parametrize("tokens,lo,n", [(10, 3, 4), (96, 32, 32)])
+def test_shared_expert_on_a_token_sub_range(real_bf16, tokens, lo, n):
+    """The shared expert restricted to tokens [lo, lo+n) (what an expert-parallel rank asks for its own
+    tokens among the gathered ones) on the GEMV path (10 tokens) and the tensor-core path (96 tokens)."""
+    from fastkernels_b200.moe import _experts
+    w = real_bf16
+    hidden = make_hidden(500 + tokens, tokens, REAL, dtype=torch.bfloat16, device="cuda")
+    _, ids, wts = triton_qwen36_batched_moe_router_decode(hidden, w.norm_weight, w.router_weight)
+    routed = triton_qwen36_batched_routed_experts_decode(hidden, ids, wts, w.expert_gate_up_weight, w.expert_down_weight)
+    both = triton_qwen36_batched_routed_shared_experts_decode(hidden, ids, wts, w.expert_gate_up_weight, w.expert_down_weight,
+                                                              w.shared_gate_up_weight, w.shared_down_weight,
+                                                              w.shared_expert_gate_weight)
+    sub = _experts(hidden, ids, wts, w.expert_gate_up_weight, w.expert_down_weight, w.shared_gate_up_weight,
+                   w.shared_down_weight, w.shared_expert_gate_weight, shared_token_range=(lo, n))
+    inside = torch.zeros(tokens, dtype=torch.bool, device="cuda")
+    inside[lo:lo + n] = True
+    torch.testing.assert_close(sub[inside], both[inside], atol=1e-6, rtol=1e-5)
+    torch.testing.assert_close(sub[~inside], routed[~inside], atol=1e-6, rtol=1e-5)
