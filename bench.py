@@ -50,7 +50,7 @@ def parse_args():
     ap.add_argument("--no-sweep", action="store_true", help="skip the per-batch sweep (1..256 tokens)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--flags", type=int, default=0)
-    ap.add_argument("--ep-graph", action="store_true", help="expert-parallel leg: capture each layer call in a CUDA graph")
+    ap.add_argument("--ep-eager", action="store_true", help="expert-parallel leg: no CUDA-graph capture of the layer call")
     return ap.parse_args()
 
 

@@ -48,7 +48,7 @@ def run_ep(args, workload_config, measured_peak, ClockSampler, METRIC, UNIT):
     hid_host = [make_hidden(1000 + i * world + rank, B, spec, dtype=torch.bfloat16).pin_memory() for i in range(pool)]
     hid_dev = [h.to(dev) for h in hid_host]
 
-    plans = [EPDecodePlan(sh, B, capture=args.ep_graph) for sh in shards]
+    plans = [EPDecodePlan(sh, B, capture=not args.ep_eager) for sh in shards]
     for i, pl in enumerate(plans):              # inputs are resident before the timed region starts
         pl.hidden.copy_(hid_dev[i % pool])
 
