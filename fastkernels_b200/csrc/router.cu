@@ -12,6 +12,7 @@
 
 #include "common.cuh"
 #include "kernels.cuh"
+#include "tma.cuh"
 #include "topk.cuh"
 
 namespace fk {
@@ -206,6 +207,159 @@ router_kernel(RouterParams p) {
     }
 }
 
+// bf16 fast path: every warp's weight row is bulk-copied (TMA, untiled form) into shared memory at
+// kernel start, all rows in flight together, and the dot products are short rolled loops over 16-byte
+// shared-memory vectors.  A kernel this short is bound by instruction fetch and load latency, so the
+// code is kept small on purpose.  H must be a multiple of 256.
+template <int TPB>
+__global__ void __launch_bounds__(kRouterWarps * 32) router_fast_kernel(RouterParams p) {
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    const int H = p.H, E = p.E;
+    __nv_bfloat16* wrows = reinterpret_cast<__nv_bfloat16*>(smem_raw);                 // [8][H]
+    float* xs = reinterpret_cast<float*>(smem_raw + (size_t)kRouterWarps * H * 2);     // [TPB][H]
+    float* gain = xs + (size_t)TPB * H;                                               // [H]
+    float* rstd = gain + H;                                                           // [TPB]
+    uint64_t* bars = reinterpret_cast<uint64_t*>(rstd + TPB + (TPB & 1));             // [8]
+    __shared__ int is_last;
+    __shared__ int abort_flag;
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int tok0 = blockIdx.y * TPB;
+    const bool has_gate = p.shared_gate_weight != nullptr && p.shared_gate_out != nullptr;
+    const int e = blockIdx.x * kRouterWarps + warp;
+    const bool is_gate = has_gate && e == E;
+    const bool active = e < E || is_gate;
+    if (tid == 0) abort_flag = 0;
+    if (lane == 0) {
+        mbar_init(&bars[warp], 1);
+        mbar_init_fence();
+        if (active) {
+            const __nv_bfloat16* wrow = is_gate ? reinterpret_cast<const __nv_bfloat16*>(p.shared_gate_weight)
+                                                : reinterpret_cast<const __nv_bfloat16*>(p.router_weight) + (size_t)e * H;
+            mbar_expect_tx(&bars[warp], (uint32_t)H * 2);
+            bulk_load(wrows + (size_t)warp * H, wrow, (uint32_t)H * 2, &bars[warp]);
+        }
+    }
+    // activations -> fp32 in shared memory; norm gains next to them
+    const int chunks = H / 8;
+    for (int i = tid; i < TPB * chunks; i += blockDim.x) {
+        const int t = i / chunks, c = i - t * chunks;
+        const int token = tok0 + t;
+        float v[8];
+        if (token < p.T) {
+            if (p.hidden_dtype == FK_BF16) {
+                const uint4 raw = *reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(p.hidden) + (size_t)token * H + c * 8);
+                v[0] = bf16lo(raw.x); v[1] = bf16hi(raw.x); v[2] = bf16lo(raw.y); v[3] = bf16hi(raw.y);
+                v[4] = bf16lo(raw.z); v[5] = bf16hi(raw.z); v[6] = bf16lo(raw.w); v[7] = bf16hi(raw.w);
+            } else {
+#pragma unroll
+                for (int q = 0; q < 8; ++q) v[q] = load_any(p.hidden, p.hidden_dtype, (size_t)token * H + c * 8 + q);
+            }
+        } else {
+#pragma unroll
+            for (int q = 0; q < 8; ++q) v[q] = 0.f;
+        }
+        float4* dst = reinterpret_cast<float4*>(xs + (size_t)t * H + c * 8);
+        dst[0] = make_float4(v[0], v[1], v[2], v[3]);
+        dst[1] = make_float4(v[4], v[5], v[6], v[7]);
+    }
+    for (int c = tid; c < chunks; c += blockDim.x) {
+        const uint4 raw = *reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(p.norm_weight) + c * 8);
+        const float o = p.norm_offset;
+        float4* dst = reinterpret_cast<float4*>(gain + c * 8);
+        dst[0] = make_float4(o + bf16lo(raw.x), o + bf16hi(raw.x), o + bf16lo(raw.y), o + bf16hi(raw.y));
+        dst[1] = make_float4(o + bf16lo(raw.z), o + bf16hi(raw.z), o + bf16lo(raw.w), o + bf16hi(raw.w));
+    }
+    __syncthreads();
+    for (int t = warp; t < TPB; t += kRouterWarps) {
+        float ss = 0.f;
+#pragma unroll 4
+        for (int h = lane * 4; h < H; h += 128) {
+            const float4 v = *reinterpret_cast<const float4*>(xs + (size_t)t * H + h);
+            ss = fmaf(v.x, v.x, ss); ss = fmaf(v.y, v.y, ss); ss = fmaf(v.z, v.z, ss); ss = fmaf(v.w, v.w, ss);
+        }
+        ss = warp_sum(ss);
+        if (lane == 0) rstd[t] = rsqrtf(ss / (float)H + p.eps);
+    }
+    __syncthreads();
+
+    if (active) {
+        mbar_wait(&bars[warp], 0, &abort_flag);
+        float acc[TPB];
+#pragma unroll
+        for (int t = 0; t < TPB; ++t) acc[t] = 0.f;
+        const unsigned char* wrow = reinterpret_cast<const unsigned char*>(wrows + (size_t)warp * H);
+#pragma unroll 1
+        for (int c = lane * 8; c < H; c += 256) {
+            const uint4 w = lds128(wrow + (size_t)c * 2);
+            float wf[8];
+            wf[0] = bf16lo(w.x); wf[1] = bf16hi(w.x); wf[2] = bf16lo(w.y); wf[3] = bf16hi(w.y);
+            wf[4] = bf16lo(w.z); wf[5] = bf16hi(w.z); wf[6] = bf16lo(w.w); wf[7] = bf16hi(w.w);
+            if (!is_gate) {
+                const float4 g0 = *reinterpret_cast<const float4*>(gain + c), g1 = *reinterpret_cast<const float4*>(gain + c + 4);
+                wf[0] *= g0.x; wf[1] *= g0.y; wf[2] *= g0.z; wf[3] *= g0.w;
+                wf[4] *= g1.x; wf[5] *= g1.y; wf[6] *= g1.z; wf[7] *= g1.w;
+            }
+#pragma unroll
+            for (int t = 0; t < TPB; ++t) {
+                const float4 x0 = *reinterpret_cast<const float4*>(xs + (size_t)t * H + c);
+                const float4 x1 = *reinterpret_cast<const float4*>(xs + (size_t)t * H + c + 4);
+                float a = acc[t];
+                a = fmaf(wf[0], x0.x, a); a = fmaf(wf[1], x0.y, a); a = fmaf(wf[2], x0.z, a); a = fmaf(wf[3], x0.w, a);
+                a = fmaf(wf[4], x1.x, a); a = fmaf(wf[5], x1.y, a); a = fmaf(wf[6], x1.z, a); a = fmaf(wf[7], x1.w, a);
+                acc[t] = a;
+            }
+        }
+#pragma unroll
+        for (int t = 0; t < TPB; ++t) {
+            const float v = warp_sum(acc[t]);
+            if (lane == 0 && tok0 + t < p.T) {
+                if (is_gate) {
+                    p.shared_gate_out[tok0 + t] = sigmoidf_(v);
+                } else {
+                    float logit = v * rstd[t];
+                    if (p.router_bias) logit += p.router_bias[e];
+                    p.logits[(size_t)(tok0 + t) * E + e] = logit;
+                }
+            }
+        }
+    }
+
+    // ticket: the last expert-tile block of this token tile selects the top-k
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+        unsigned t = atomicAdd(p.tickets + blockIdx.y, 1u);
+        is_last = (t == gridDim.x - 1);
+        if (is_last) p.tickets[blockIdx.y] = 0u;    // re-arm for the next launch
+    }
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    for (int t = warp; t < TPB; t += kRouterWarps) {
+        const int token = tok0 + t;
+        if (token >= p.T) continue;
+        const float* row = p.logits + (size_t)token * E;
+        long long* ids = p.topk_ids + (size_t)token * p.top_k;
+        int* ids32 = p.ids32 ? p.ids32 + (size_t)token * p.top_k : nullptr;
+        float* wts = p.topk_weights + (size_t)token * p.top_k;
+        if (E <= 256) topk_warp<8>(row, E, p.top_k, ids, ids32, wts);
+        else topk_warp<32>(row, E, p.top_k, ids, ids32, wts);
+    }
+}
+
+template <int TPB>
+static int launch_router_fast(const RouterParams& p, cudaStream_t stream) {
+    const int gate = (p.shared_gate_weight && p.shared_gate_out) ? 1 : 0;
+    dim3 grid((p.E + gate + kRouterWarps - 1) / kRouterWarps, (p.T + TPB - 1) / TPB);
+    const size_t smem = (size_t)kRouterWarps * p.H * 2 + sizeof(float) * ((size_t)TPB * p.H + p.H + TPB + 2) + 8 * sizeof(uint64_t) + 16;
+    auto kern = router_fast_kernel<TPB>;
+    FK_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), "router attr");
+    kern<<<grid, kRouterWarps * 32, smem, stream>>>(p);
+    FK_LAUNCH_OK("router launch");
+    return FK_OK;
+}
+
 template <typename WT, int VW>
 static int launch_router_t(const RouterParams& p, cudaStream_t stream) {
     dim3 block(kRouterWarps * 32);
@@ -236,6 +390,8 @@ int launch_router(const RouterParams& p, int weight_dtype, cudaStream_t stream) 
         case FK_F32:
             return (aligned && p.H % 4 == 0) ? launch_router_t<float, 4>(p, stream) : launch_router_t<float, 1>(p, stream);
         case FK_BF16:
+            if (aligned && p.H % 256 == 0 && p.H <= 4096 && ((reinterpret_cast<uintptr_t>(p.hidden) | reinterpret_cast<uintptr_t>(p.shared_gate_weight)) & 15) == 0)
+                return p.T <= 64 ? launch_router_fast<4>(p, stream) : launch_router_fast<8>(p, stream);
             return (aligned && p.H % 8 == 0) ? launch_router_t<__nv_bfloat16, 8>(p, stream)
                                              : launch_router_t<__nv_bfloat16, 1>(p, stream);
         case FK_F16:
