@@ -30,19 +30,22 @@ namespace fk {
 
 constexpr int kStageBytes = 32768;
 constexpr int kStages = 4;
-constexpr int kXSlots = 2;
 constexpr int kXSlotBytes = 32768;          // 4 rows x 2048 columns x 4 bytes at most
+constexpr int kXSlots = 2;
 constexpr int kGroupWarps = 8;
 constexpr int kGroups = 2;
 constexpr int kConsumerWarps = kGroups * kGroupWarps;
-constexpr int kStreamThreads = (kConsumerWarps + 2) * 32;
-constexpr int kDownTile = 64;
+constexpr int kStreamThreads = (kConsumerWarps + 2 + kGroups) * 32;   // + two producer warps + one epilogue warp per group
+constexpr int kDownTile = 128;
 
 struct StreamSmem {
     unsigned char stage[kStages][kStageBytes];
     unsigned char xslot[kXSlots][kXSlotBytes];
     float partial[kGroups][2][kGroupWarps][32];
     int4 header[kXSlots];                    // (expert or -1, first packed row, rows, first token)
+    int4 pmeta[kGroups][2];                  // per partial buffer: (first packed row, rows valid, tile, step)
+    uint64_t pfull[kGroups][2];              // partial sums of a stage are complete (8 consumer warps arrive)
+    uint64_t pempty[kGroups][2];             // the epilogue warp has read them
     uint64_t full[kStages];
     uint64_t empty[kStages];
     uint64_t xfull[kXSlots];
@@ -113,8 +116,8 @@ __device__ __forceinline__ void load8_slot(const unsigned char* row, int dtype, 
 // The weight stages of one unit for consumer group `g`, NT activation rows in registers.
 template <int NT, int KCH, bool GU>
 __device__ __forceinline__ void consume_unit(const ExpertParams& p, StreamSmem& s, const unsigned char* xrows, int xdtype,
-                                             int row_pos, int nvalid, int tile, uint32_t& it, int& pbuf,
-                                             uint64_t* xempty, int g, int w8, int lane, int gtid) {
+                                             int row_pos, int nvalid, int tile, uint32_t& it, int& pbuf, uint32_t& nstage,
+                                             uint64_t* xempty, int g, int w8, int lane) {
     constexpr int RG = 8 / KCH;
     constexpr int K = KCH * 256;
     constexpr int TILE = stream_tile(KCH, GU);
@@ -157,6 +160,8 @@ __device__ __forceinline__ void consume_unit(const ExpertParams& p, StreamSmem& 
             for (int r = 0; r < 8; ++r) w[r] = lds128(base + ((size_t)(rg * 8 + r) * K + col0) * 2);
         }
 
+        // the partial buffer must have been drained by the epilogue warp (two stages of this group ago)
+        mbar_wait(&s.pempty[g][pbuf], ((nstage >> 1) & 1u) ^ 1u, &s.abort_flag);
         float* part = s.partial[g][pbuf][w8];
         float dep = 0.f;
 #pragma unroll
@@ -186,34 +191,50 @@ __device__ __forceinline__ void consume_unit(const ExpertParams& p, StreamSmem& 
         }
         x_released = true;
 
-        named_bar_sync(1 + g, kGroupWarps * 32);
-        if (gtid < PER_STAGE * NT) {
-            const int t = gtid % NT;
-            const int o = gtid / NT;              // output index inside the stage
+        // hand the partial sums to the group's epilogue warp; the consumers go straight to their next stage
+        if (w8 == 0 && lane == 0) s.pmeta[g][pbuf] = make_int4(row_pos, nvalid, tile, step);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&s.pfull[g][pbuf]);
+        ++nstage;
+        pbuf ^= 1;
+    }
+}
+
+// Epilogue warp of group g: sums the K-slices of every output of a stage, applies SwiGLU (gate_up) and
+// stores.  It runs beside the consumers, so the final sum and the global stores are off their path.
+template <int KCH, bool GU>
+__device__ __forceinline__ void epilogue_warp(const ExpertParams& p, StreamSmem& s, int g, int lane, uint32_t stages, int nt_unused) {
+    constexpr int RG = 8 / KCH;
+    constexpr int TILE = stream_tile(KCH, GU);
+    constexpr int PER_STAGE = GU ? 4 * RG : 8 * RG;
+    (void)nt_unused;
+    for (uint32_t n = 0; n < stages; ++n) {
+        const int pb = n & 1u;
+        mbar_wait(&s.pfull[g][pb], (n >> 1) & 1u, &s.abort_flag);
+        const int4 m = s.pmeta[g][pb];                       // first packed row, rows valid, tile, step
+        const int NT = m.y == 1 ? 1 : (m.y == 2 ? 2 : 4);
+        for (int idx = lane; idx < PER_STAGE * NT; idx += 32) {
+            const int t = idx % NT;
+            const int o = idx / NT;                          // output index inside the stage
             if (GU) {
                 const int rg2 = o / 4, q = o - rg2 * 4;
                 float gsum = 0.f, usum = 0.f;
 #pragma unroll
                 for (int k2 = 0; k2 < KCH; ++k2) {
-                    gsum += s.partial[g][pbuf][rg2 * KCH + k2][q * NT + t];
-                    usum += s.partial[g][pbuf][rg2 * KCH + k2][(4 + q) * NT + t];
+                    gsum += s.partial[g][pb][rg2 * KCH + k2][q * NT + t];
+                    usum += s.partial[g][pb][rg2 * KCH + k2][(4 + q) * NT + t];
                 }
-                if (t < nvalid) {
-                    const int col = tile * TILE + step * PER_STAGE + o;
-                    p.act[(size_t)(row_pos + t) * p.I + col] = silu_mul(gsum, usum);
-                }
+                if (t < m.y) p.act[(size_t)(m.x + t) * p.I + m.z * TILE + m.w * PER_STAGE + o] = silu_mul(gsum, usum);
             } else {
                 const int rg2 = o / 8, r = o - rg2 * 8;
                 float sum = 0.f;
 #pragma unroll
-                for (int k2 = 0; k2 < KCH; ++k2) sum += s.partial[g][pbuf][rg2 * KCH + k2][r * NT + t];
-                if (t < nvalid) {
-                    const int h = tile * TILE + step * PER_STAGE + o;
-                    p.y[(size_t)(row_pos + t) * p.H + h] = sum;
-                }
+                for (int k2 = 0; k2 < KCH; ++k2) sum += s.partial[g][pb][rg2 * KCH + k2][r * NT + t];
+                if (t < m.y) p.y[(size_t)(m.x + t) * p.H + m.z * TILE + m.w * PER_STAGE + o] = sum;
             }
         }
-        pbuf ^= 1;
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&s.pempty[g][pb]);
     }
 }
 
@@ -237,6 +258,10 @@ __global__ void __launch_bounds__(kStreamThreads, 1) stream_gemv_kernel(ExpertPa
         for (int i = 0; i < kXSlots; ++i) {
             mbar_init(&s.xfull[i], 1);
             mbar_init(&s.xempty[i], kConsumerWarps);
+        }
+        for (int i = 0; i < kGroups * 2; ++i) {
+            mbar_init(&s.pfull[i / 2][i % 2], kGroupWarps);
+            mbar_init(&s.pempty[i / 2][i % 2], 1);
         }
         s.abort_flag = 0;
         mbar_init_fence();
@@ -269,14 +294,15 @@ __global__ void __launch_bounds__(kStreamThreads, 1) stream_gemv_kernel(ExpertPa
                 for (int step = 0; step < STEPS; ++step, ++it) {
                     const int stage = it % kStages;
                     const uint32_t par = (it / kStages) & 1u;
+                    unsigned char* sbuf = s.stage[stage];
                     mbar_wait(&s.empty[stage], par ^ 1u, &s.abort_flag);
                     mbar_expect_tx(&s.full[stage], kStageBytes);
                     const size_t first = (size_t)tile * TILE + (size_t)step * PER_STAGE;
                     if (GU) {
-                        bulk_load(s.stage[stage], W + first * K, kStageBytes / 2, &s.full[stage]);
-                        bulk_load(s.stage[stage] + kStageBytes / 2, W + ((size_t)p.I + first) * K, kStageBytes / 2, &s.full[stage]);
+                        bulk_load(sbuf, W + first * K, kStageBytes / 2, &s.full[stage]);
+                        bulk_load(sbuf + kStageBytes / 2, W + ((size_t)p.I + first) * K, kStageBytes / 2, &s.full[stage]);
                     } else {
-                        bulk_load(s.stage[stage], W + first * K, kStageBytes, &s.full[stage]);
+                        bulk_load(sbuf, W + first * K, kStageBytes, &s.full[stage]);
                     }
                 }
             }
@@ -313,11 +339,16 @@ __global__ void __launch_bounds__(kStreamThreads, 1) stream_gemv_kernel(ExpertPa
                 bulk_load(s.xslot[slot], src, (uint32_t)(pass.z * xrow_bytes), &s.xfull[slot]);
             }
         }
+    } else if (warp >= kConsumerWarps + 2) {
+        // ---------------------------------------------------------------- epilogue warps (one per group)
+        const int g = warp - (kConsumerWarps + 2);
+        const int my_units = units > (int)blockIdx.x ? (units - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
+        epilogue_warp<KCH, GU>(p, s, g, lane, (uint32_t)my_units * (STEPS / 2), 0);
     } else {
         // ---------------------------------------------------------------- consumers
-        const int g = warp / kGroupWarps, w8 = warp % kGroupWarps, gtid = tid - g * kGroupWarps * 32;
+        const int g = warp / kGroupWarps, w8 = warp % kGroupWarps;
         int pbuf = 0;
-        uint32_t it = 0, ui = 0;
+        uint32_t it = 0, ui = 0, nstage = 0;
         for (int unit = blockIdx.x; unit < units; unit += gridDim.x, ++ui) {
             const int tile = unit % tiles;
             const int slot = ui % kXSlots;
@@ -325,9 +356,9 @@ __global__ void __launch_bounds__(kStreamThreads, 1) stream_gemv_kernel(ExpertPa
             mbar_wait(&s.xfull[slot], par, &s.abort_flag);
             const int4 pass = s.header[slot];
             const unsigned char* xrows = s.xslot[slot];
-            if (pass.z == 1) consume_unit<1, KCH, GU>(p, s, xrows, xdtype, pass.y, 1, tile, it, pbuf, &s.xempty[slot], g, w8, lane, gtid);
-            else if (pass.z == 2) consume_unit<2, KCH, GU>(p, s, xrows, xdtype, pass.y, 2, tile, it, pbuf, &s.xempty[slot], g, w8, lane, gtid);
-            else consume_unit<4, KCH, GU>(p, s, xrows, xdtype, pass.y, pass.z, tile, it, pbuf, &s.xempty[slot], g, w8, lane, gtid);
+            if (pass.z == 1) consume_unit<1, KCH, GU>(p, s, xrows, xdtype, pass.y, 1, tile, it, pbuf, nstage, &s.xempty[slot], g, w8, lane);
+            else if (pass.z == 2) consume_unit<2, KCH, GU>(p, s, xrows, xdtype, pass.y, 2, tile, it, pbuf, nstage, &s.xempty[slot], g, w8, lane);
+            else consume_unit<4, KCH, GU>(p, s, xrows, xdtype, pass.y, pass.z, tile, it, pbuf, nstage, &s.xempty[slot], g, w8, lane);
         }
         if (s.abort_flag && lane == 0 && p.error_word) atomicExch(p.error_word, 1);
     }

@@ -67,7 +67,12 @@ __device__ __forceinline__ void bulk_load(void* dst_smem, const void* src_gmem, 
                  : "memory");
 }
 
+// Named barrier for a subset of the block's warps.  bar.sync is an aligned instruction: every lane of a
+// warp has to execute it together, and a warp counts as arrived as soon as it is executed at all.  Code
+// that reaches the barrier after a divergent region (one lane polling a flag, say) must therefore
+// reconverge first, or the barrier opens while that lane is still waiting.
 __device__ __forceinline__ void named_bar_sync(int id, int threads) {
+    __syncwarp();
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
 }
 

@@ -522,3 +522,25 @@ def test_shared_expert_on_a_token_sub_range(real_bf16, tokens, lo, n):
     inside[lo:lo + n] = True
     torch.testing.assert_close(sub[inside], both[inside], atol=1e-6, rtol=1e-5)
     torch.testing.assert_close(sub[~inside], routed[~inside], atol=1e-6, rtol=1e-5)
+
+
+def test_single_token_fused_kernel_sees_fresh_data_every_call(real_bf16_biased):
+    """The fused kernel exchanges logits and activations between its blocks through global memory.
+    Alternating two different tokens on the same workspace makes any read of the previous call's
+    values (a grid barrier that opens early) show up as a mismatch."""
+    from fastkernels_b200.plan import MoEDecodePlan
+    w = real_bf16_biased
+    plan = MoEDecodePlan(w, 1)
+    xa = make_hidden(901, 1, REAL, dtype=torch.bfloat16, device="cuda")
+    xb = (xa * -1.7).to(torch.bfloat16)
+    refs = []
+    for x in (xa, xb):
+        out, logits, ids, weights = plan.run(x)
+        torch.cuda.synchronize()
+        refs.append((out.clone(), ids.clone()))
+    assert not torch.equal(refs[0][0], refs[1][0])
+    for i in range(400):
+        out, _, ids, _ = plan.run(xa if i % 2 == 0 else xb)
+        if i % 20 >= 18:
+            torch.cuda.synchronize()
+            assert torch.equal(out, refs[i % 2][0]) and torch.equal(ids, refs[i % 2][1]), f"call {i}"
