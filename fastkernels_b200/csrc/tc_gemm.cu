@@ -3,12 +3,14 @@
 //
 // Swap-AB: the weight rows are the MMA's M dimension (128 rows per tile, K-major in shared memory,
 // 128-byte swizzle, loaded by tiled TMA), the tokens of one pass are its N dimension (up to 64,
-// rounded up to 16), K runs over the reduction dimension in chunks of 64.  gate_up keeps two fp32
-// accumulators in tensor memory, gate rows and up rows of the same 128 pairs, so the epilogue thread
-// that owns pair p reads gate[p, t] and up[p, t] from its own lane and applies SwiGLU without any
-// exchange; the bf16 result goes to the packed activation buffer that the down GEMM reads back
-// through TMA.  Two accumulator buffers: the MMAs of the next unit run while the epilogue drains
-// the previous one.
+// rounded up to 16), K runs over the reduction dimension in chunks of 64.  A gate_up tile is 64 gate
+// rows stacked on the 64 up rows of the same pairs (two 64-row TMA boxes into one operand tile), so
+// one MMA per K step produces both halves: accumulator lanes 0..63 hold gate[p, t], lanes 64..127
+// hold up[p, t].  The two up warps of the epilogue pass their values through shared memory to the
+// two gate warps, which apply SwiGLU and store bf16 into the packed activation buffer that the down
+// GEMM reads back through TMA.  (Tiles of 64 pairs keep the work units at 0.5 MiB: with 1 MiB units
+// the last round over the 148 SMs ran a third full at 64 tokens.)  Two accumulator buffers: the MMAs
+// of the next unit run while the epilogue drains the previous one.
 //
 // Block = 6 warps: warp 0 issues TMA (one lane), warp 1 owns tensor memory and issues the MMAs (one
 // lane), warps 2..5 are the epilogue (one TMEM lane quarter each).  One persistent block per SM,
@@ -26,15 +28,17 @@
 namespace fk {
 
 constexpr int kTcStages = 4;
+constexpr int kTcStagesGU = 5;
 constexpr int kTcN = 64;                 // tokens per pass (MMA N, rounded up to 16)
 constexpr int kTcThreads = 192;
 constexpr int kTcTileBytes = 128 * 64 * 2;          // one 128-row x 64-column bf16 operand tile
 constexpr int kTcBBytes = kTcN * 64 * 2;
-constexpr int kTcTmemCols = 256;         // 2 buffers x (gate 64 + up 64) columns
+constexpr int kTcTmemCols = 128;         // 2 accumulator buffers x 64 columns
+constexpr int kTcUStride = kTcN + 1;     // row stride (floats) of the up-value exchange buffer
 
 struct TcBarriers {
-    uint64_t full[kTcStages];
-    uint64_t empty[kTcStages];
+    uint64_t full[kTcStagesGU];
+    uint64_t empty[kTcStagesGU];
     uint64_t tfull[2];
     uint64_t tempty[2];
     uint32_t tmem_base;
@@ -56,17 +60,19 @@ tc_grouped_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constan
                   const __grid_constant__ CUtensorMap amap, TcParams p) {
     extern __shared__ unsigned char smem_dyn[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~uintptr_t(1023));
-    constexpr int kStageBytes = (GU ? 2 : 1) * kTcTileBytes + kTcBBytes;
-    TcBarriers& bar = *reinterpret_cast<TcBarriers*>(smem + kTcStages * kStageBytes);
+    constexpr int kStageBytes = kTcTileBytes + kTcBBytes;
+    constexpr int kNumStages = GU ? kTcStagesGU : kTcStages;
+    TcBarriers& bar = *reinterpret_cast<TcBarriers*>(smem + kNumStages * kStageBytes);
+    float* ubuf = reinterpret_cast<float*>(smem + kNumStages * kStageBytes + 1024);   // GU: [2][64][kTcUStride]
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int K = GU ? p.H : p.I;
     const int chunks = K / 64;
-    const int tiles = (GU ? p.I : p.H) / 128;
+    const int tiles = GU ? p.I / 64 : p.H / 128;
     const int rows_per_expert = GU ? 2 * p.I : p.H;
     const int units = p.meta[1] * tiles;
 
     if (tid == 0) {
-        for (int i = 0; i < kTcStages; ++i) { mbar_init(&bar.full[i], 1); mbar_init(&bar.empty[i], 1); }
+        for (int i = 0; i < kNumStages; ++i) { mbar_init(&bar.full[i], 1); mbar_init(&bar.empty[i], 1); }
         for (int i = 0; i < 2; ++i) { mbar_init(&bar.tfull[i], 1); mbar_init(&bar.tempty[i], 4); }
         bar.abort_flag = 0;
         mbar_init_fence();
@@ -89,16 +95,20 @@ tc_grouped_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constan
                 const int mt = unit % tiles;
                 const int npad = (pass.z + 15) & ~15;
                 const CUtensorMap* wm = pass.x < 0 ? &smap : &wmap;
-                const int wrow = (pass.x < 0 ? 0 : pass.x * rows_per_expert) + mt * 128;
+                const int wrow = (pass.x < 0 ? 0 : pass.x * rows_per_expert) + mt * (GU ? 64 : 128);
                 for (int c = 0; c < chunks; ++c, ++it) {
-                    const int stage = it % kTcStages;
-                    const uint32_t par = (it / kTcStages) & 1u;
+                    const int stage = it % kNumStages;
+                    const uint32_t par = (it / kNumStages) & 1u;
                     mbar_wait(&bar.empty[stage], par ^ 1u, &bar.abort_flag);
                     unsigned char* st = smem + stage * kStageBytes;
-                    mbar_expect_tx(&bar.full[stage], (GU ? 2 : 1) * kTcTileBytes + npad * 128);
-                    tma_load_2d(st, wm, c * 64, wrow, &bar.full[stage]);
-                    if (GU) tma_load_2d(st + kTcTileBytes, wm, c * 64, wrow + p.I, &bar.full[stage]);
-                    unsigned char* bt = st + (GU ? 2 : 1) * kTcTileBytes;
+                    mbar_expect_tx(&bar.full[stage], kTcTileBytes + npad * 128);
+                    if (GU) {
+                        tma_load_2d(st, wm, c * 64, wrow, &bar.full[stage]);                            // 64 gate rows
+                        tma_load_2d(st + kTcTileBytes / 2, wm, c * 64, wrow + p.I, &bar.full[stage]);   // 64 up rows
+                    } else {
+                        tma_load_2d(st, wm, c * 64, wrow, &bar.full[stage]);
+                    }
+                    unsigned char* bt = st + kTcTileBytes;
                     for (int j = 0; j < npad / 16; ++j)
                         tma_load_2d(bt + j * 16 * 128, &amap, c * 64, pass.y + j * 16, &bar.full[stage]);
                 }
@@ -115,20 +125,18 @@ tc_grouped_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constan
                 const uint32_t acc = ui & 1u;
                 mbar_wait(&bar.tempty[acc], ((ui >> 1) & 1u) ^ 1u, &bar.abort_flag);
                 tc_fence_after_sync();
-                const uint32_t d0 = tmem_base + acc * 128u;
+                const uint32_t d0 = tmem_base + acc * 64u;
                 for (int c = 0; c < chunks; ++c, ++it) {
-                    const int stage = it % kTcStages;
-                    const uint32_t par = (it / kTcStages) & 1u;
+                    const int stage = it % kNumStages;
+                    const uint32_t par = (it / kNumStages) & 1u;
                     mbar_wait(&bar.full[stage], par, &bar.abort_flag);
                     tc_fence_after_sync();
                     const unsigned char* st = smem + stage * kStageBytes;
-                    const unsigned char* bt = st + (GU ? 2 : 1) * kTcTileBytes;
+                    const unsigned char* bt = st + kTcTileBytes;
 #pragma unroll
                     for (int kk = 0; kk < 4; ++kk) {
-                        const uint64_t b_desc = umma_smem_desc(bt + kk * 32);
                         const uint32_t accum = (c > 0 || kk > 0) ? 1u : 0u;
-                        umma_bf16(d0, umma_smem_desc(st + kk * 32), b_desc, idesc, accum);
-                        if (GU) umma_bf16(d0 + 64u, umma_smem_desc(st + kTcTileBytes + kk * 32), b_desc, idesc, accum);
+                        umma_bf16(d0, umma_smem_desc(st + kk * 32), umma_smem_desc(bt + kk * 32), idesc, accum);
                     }
                     umma_commit(&bar.empty[stage]);      // the stage is free once these MMAs have read it
                 }
@@ -147,19 +155,37 @@ tc_grouped_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constan
             const uint32_t acc = ui & 1u;
             mbar_wait(&bar.tfull[acc], (ui >> 1) & 1u, &bar.abort_flag);
             tc_fence_after_sync();
-            const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + acc * 128u;
-            for (int c16 = 0; c16 < npad / 16; ++c16) {
-                float g[16];
-                tmem_ld16(taddr + c16 * 16, g);
-                if (GU) {
-                    float u[16];
-                    tmem_ld16(taddr + 64u + c16 * 16, u);
+            const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + acc * 64u;
+            if (GU) {
+                // lanes 64..127 hold the up rows: hand them to the warps that hold the gate rows of the same pairs
+                float* ub = ubuf + (size_t)acc * 64 * kTcUStride;
+                if (q >= 2) {
+                    for (int c16 = 0; c16 < npad / 16; ++c16) {
+                        float u[16];
+                        tmem_ld16(taddr + c16 * 16, u);
 #pragma unroll
-                    for (int t = 0; t < 16; ++t) {
-                        const int tok = c16 * 16 + t;
-                        if (tok < n) p.actb[(size_t)(pass.y + tok) * p.I + mt * 128 + r] = __float2bfloat16_rn(silu_mul(g[t], u[t]));
+                        for (int t = 0; t < 16; ++t) ub[(size_t)(r - 64) * kTcUStride + c16 * 16 + t] = u[t];
                     }
-                } else {
+                }
+                named_bar_sync(2, 128);
+                if (q < 2) {
+                    for (int c16 = 0; c16 < npad / 16; ++c16) {
+                        float g[16];
+                        tmem_ld16(taddr + c16 * 16, g);
+#pragma unroll
+                        for (int t = 0; t < 16; ++t) {
+                            const int tok = c16 * 16 + t;
+                            if (tok < n) {
+                                const float u = ub[(size_t)r * kTcUStride + tok];
+                                p.actb[(size_t)(pass.y + tok) * p.I + mt * 64 + r] = __float2bfloat16_rn(silu_mul(g[t], u));
+                            }
+                        }
+                    }
+                }
+            } else {
+                for (int c16 = 0; c16 < npad / 16; ++c16) {
+                    float g[16];
+                    tmem_ld16(taddr + c16 * 16, g);
 #pragma unroll
                     for (int t = 0; t < 16; ++t) {
                         const int tok = c16 * 16 + t;
@@ -266,7 +292,7 @@ static bool tensor_map(const void* base, uint64_t rows, uint64_t cols, uint32_t 
 
 bool tc_path_supported(const ExpertParams& p, int weight_dtype) {
     if (weight_dtype != FK_BF16) return false;
-    if (p.H % 128 != 0 || p.I % 128 != 0 || p.H < 128 || p.I < 128) return false;
+    if (p.H % 128 != 0 || p.I % 64 != 0 || p.H < 128 || p.I < 64) return false;
     uintptr_t bits = reinterpret_cast<uintptr_t>(p.hidden) | reinterpret_cast<uintptr_t>(p.gate_up) |
                      reinterpret_cast<uintptr_t>(p.down) | reinterpret_cast<uintptr_t>(p.shared_gate_up) |
                      reinterpret_cast<uintptr_t>(p.shared_down);
@@ -282,8 +308,8 @@ int launch_experts_tc(const ExpertParams& p, __nv_bfloat16* xg, __nv_bfloat16* a
     const void* dummy_gu = p.gate_up ? p.gate_up : p.shared_gate_up;
     const void* dummy_dn = p.down ? p.down : p.shared_down;
     const uint64_t e_rows = p.gate_up ? (uint64_t)p.E : 0;
-    bool ok = tensor_map(dummy_gu, p.gate_up ? e_rows * 2 * p.I : 2 * p.I, p.H, 128, &w_gu) &&
-              tensor_map(p.shared_gate_up ? p.shared_gate_up : dummy_gu, 2 * (uint64_t)p.I, p.H, 128, &s_gu) &&
+    bool ok = tensor_map(dummy_gu, p.gate_up ? e_rows * 2 * p.I : 2 * p.I, p.H, 64, &w_gu) &&
+              tensor_map(p.shared_gate_up ? p.shared_gate_up : dummy_gu, 2 * (uint64_t)p.I, p.H, 64, &s_gu) &&
               tensor_map(xg, rows, p.H, 16, &a_x) &&
               tensor_map(dummy_dn, p.down ? e_rows * p.H : p.H, p.I, 128, &w_dn) &&
               tensor_map(p.shared_down ? p.shared_down : dummy_dn, (uint64_t)p.H, p.I, 128, &s_dn) &&
@@ -301,7 +327,7 @@ int launch_experts_tc(const ExpertParams& p, __nv_bfloat16* xg, __nv_bfloat16* a
     tp.passes = p.passes; tp.meta = p.meta; tp.actb = actb; tp.y = p.y; tp.error_word = p.error_word; tp.H = p.H; tp.I = p.I;
     {
         auto kern = tc_grouped_kernel<true>;
-        const int smem = kTcStages * (2 * kTcTileBytes + kTcBBytes) + (int)sizeof(TcBarriers) + 1024;
+        const int smem = kTcStagesGU * (kTcTileBytes + kTcBBytes) + 1024 + 2 * 64 * kTcUStride * (int)sizeof(float) + 1024;
         FK_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem), "tc gate_up attr");
         kern<<<sm_count(), kTcThreads, smem, stream>>>(w_gu, s_gu, a_x, tp);
         FK_LAUNCH_OK("tc gate_up launch");
@@ -309,7 +335,7 @@ int launch_experts_tc(const ExpertParams& p, __nv_bfloat16* xg, __nv_bfloat16* a
     stage_mark();   // end of gate_up
     {
         auto kern = tc_grouped_kernel<false>;
-        const int smem = kTcStages * (kTcTileBytes + kTcBBytes) + (int)sizeof(TcBarriers) + 1024;
+        const int smem = kTcStages * (kTcTileBytes + kTcBBytes) + 1024 + 1024;
         FK_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem), "tc down attr");
         kern<<<sm_count(), kTcThreads, smem, stream>>>(w_dn, s_dn, a_act, tp);
         FK_LAUNCH_OK("tc down launch");
