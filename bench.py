@@ -42,14 +42,16 @@ FALLBACK_HBM_GBS = 6650.0
 def parse_args():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=60)
-    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="own", choices=["own", "reference"])
     ap.add_argument("--batch", type=int, default=32, help="decode tokens per GPU per step")
     ap.add_argument("--layers", type=int, default=6, help="resident weight copies rotated between steps")
     ap.add_argument("--no-sweep", action="store_true", help="skip the per-batch sweep (1..256 tokens)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--flags", type=int, default=0)
+    ap.add_argument("--stack-layers", type=int, default=0,
+                    help="also time a stack of this many layers (x <- x + MoE(RMSNorm(x)), one CUDA graph) at 1 and 64 tokens")
     ap.add_argument("--ep-eager", action="store_true", help="expert-parallel leg: no CUDA-graph capture of the layer call")
     return ap.parse_args()
 
@@ -65,50 +67,88 @@ def measured_peak():
 
 
 class ClockSampler:
-    """nvidia-smi clock/throttle samples while a timed region runs (read-only queries)."""
+    """SM clock and throttle-reason samples while the timed regions run (read-only NVML queries every
+    few milliseconds from a thread; `nvidia-smi` polling as the fallback)."""
 
-    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
-              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    REASONS = {"hw_slowdown": 0x8, "sw_power_cap": 0x4, "sw_thermal_slowdown": 0x20, "hw_thermal_slowdown": 0x40}
 
-    def __init__(self, index: int):
-        self.index = index
-        self.proc = None
-        self.lines: list[str] = []
+    def __init__(self, index: int, period_s: float = 0.004):
+        self.index, self.period = index, period_s
+        self.sm, self.reasons, self.smax = [], set(), None
+        self._stop = threading.Event()
+        self._thread = None
+        self._proc = None
 
     def start(self):
         try:
-            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                                          "-i", str(self.index), "-lms", "100"], stdout=subprocess.PIPE, text=True)
+            import pynvml
+            pynvml.nvmlInit()
+            self._nvml = pynvml
+            # NVML enumerates physical devices; honour CUDA_VISIBLE_DEVICES when it is a plain index list
+            vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+            phys = self.index
+            if vis:
+                parts = [v.strip() for v in vis.split(",") if v.strip()]
+                if self.index < len(parts) and parts[self.index].isdigit():
+                    phys = int(parts[self.index])
+            self._h = pynvml.nvmlDeviceGetHandleByIndex(phys)
+            self.smax = float(pynvml.nvmlDeviceGetMaxClockInfo(self._h, pynvml.NVML_CLOCK_SM))
+            self._thread = threading.Thread(target=self._poll, daemon=True)
+            self._thread.start()
+        except Exception:
+            self._thread = None
+            self._start_smi()
+
+    def _poll(self):
+        nv = self._nvml
+        while not self._stop.is_set():
+            try:
+                self.sm.append(float(nv.nvmlDeviceGetClockInfo(self._h, nv.NVML_CLOCK_SM)))
+                mask = int(nv.nvmlDeviceGetCurrentClocksEventReasons(self._h))
+                for name, bit in self.REASONS.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            time.sleep(self.period)
+
+    def _start_smi(self):
+        fields = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+                  "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+                  "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+        try:
+            self._proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={fields}", "--format=csv,noheader,nounits",
+                                           "-i", str(self.index), "-lms", "20"], stdout=subprocess.PIPE, text=True)
             threading.Thread(target=self._pump, daemon=True).start()
         except Exception:
-            self.proc = None
+            self._proc = None
 
     def _pump(self):
-        for line in self.proc.stdout:
-            self.lines.append(line.strip())
-
-    def stop(self) -> dict:
-        if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        time.sleep(0.15)
-        self.proc.terminate()
-        sm, smax, reasons = [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for line in self.lines:
+        for line in self._proc.stdout:
             parts = [p.strip() for p in line.split(",")]
             if len(parts) < 9:
                 continue
             try:
-                sm.append(float(parts[1]))
-                smax.append(float(parts[2]))
+                self.sm.append(float(parts[1]))
+                self.smax = max(self.smax or 0.0, float(parts[2]))
             except ValueError:
                 continue
             for name, val in zip(names, parts[5:9]):
                 if val.lower() == "active":
-                    reasons.add(name)
-        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(smax) if smax else None,
-                "samples": len(sm), "reasons": sorted(reasons)}
+                    self.reasons.add(name)
+
+    def stop(self) -> dict:
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join(timeout=1.0)
+        if self._proc is not None:
+            time.sleep(0.05)
+            self._proc.terminate()
+        if not self.sm:
+            return {"sm_mhz": None, "sm_max_mhz": self.smax, "samples": 0, "reasons": ["no samples"]}
+        return {"sm_mhz": statistics.median(self.sm), "sm_min_mhz": min(self.sm), "sm_max_mhz": self.smax,
+                "samples": len(self.sm), "reasons": sorted(self.reasons)}
 
 
 # --------------------------------------------------------------------------------------------- CPU arm
@@ -267,7 +307,6 @@ def run_single(args):
         stage_sum = st if stage_sum is None else [a + b for a, b in zip(stage_sum, st)]
         if i < L * pool:
             ucount.append(distinct_experts(p.topk_ids))
-    clocks = sampler.stop()
     stage_ms = [s / K for s in stage_sum]
     stage_names = ["router", "permute", "gate_up", "down", "combine"][:len(stage_ms)]
     U = statistics.mean(ucount)
@@ -301,6 +340,7 @@ def run_single(args):
     torch.cuda.synchronize()
     e2e_ms = e0.elapsed_time(e1) / K
     wall_ms = (time.perf_counter() - t0) * 1e3 / K
+    clocks = sampler.stop()
     e2e = {"value": B / (max(e2e_ms, wall_ms) * 1e-3), "unit": UNIT, "ms_per_step": max(e2e_ms, wall_ms),
            "h2d_bytes_per_step": B * H * 2, "d2h_bytes_per_step": B * H * 4 + B * 8 * 12}
 
@@ -332,6 +372,36 @@ def run_single(args):
                "sample": f"{sample} of {B} tokens of one step, median of {reps} calls of the token x route loop "
                          f"(fp32 PyTorch on the host cores)", "ms_per_call": sec * 1e3}
 
+    stack = None
+    if args.stack_layers > 0:
+        from fastkernels_b200.stack import MoEStackPlan
+        del plans
+        torch.cuda.empty_cache()
+        layers = list(weights)
+        for layer in range(len(layers), args.stack_layers):
+            layers.append(make_moe_weights(layer, spec, dtype=torch.bfloat16, device=dev, bias_std=0.5))
+        stack = {"layers": args.stack_layers, "runs": []}
+        for tok in (1, 64):
+            sp = MoEStackPlan(layers, tok)
+            x0 = make_hidden(3000 + tok, tok, spec, dtype=torch.float32, device=dev)
+            for _ in range(3):
+                sp.run(x0)
+            torch.cuda.synchronize()
+            s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            reps = 10
+            s0.record()
+            for _ in range(reps):
+                sp.run(x0)
+            s1.record()
+            torch.cuda.synchronize()
+            t_ms = s0.elapsed_time(s1) / reps
+            u = statistics.mean(distinct_experts(i) for i in sp.topk_ids)
+            by = args.stack_layers * (algorithmic_bytes(spec, tok, 0) + u * spec.expert_bytes_bf16)
+            stack["runs"].append({"tokens": tok, "ms_per_stack_pass": t_ms, "us_per_layer": t_ms * 1e3 / args.stack_layers,
+                                  "tokens_per_s": tok / (t_ms * 1e-3), "aggregate_gbs": by / (t_ms * 1e-3) / 1e9,
+                                  "frac_of_hbm_peak": by / (t_ms * 1e-3) / 1e9 / peak})
+            del sp
+
     line = {
         "metric": METRIC, "value": B / (ms * 1e-3), "unit": UNIT, "n_gpus": 1, "steps": K, "warmup": W,
         "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
@@ -339,6 +409,8 @@ def run_single(args):
         "e2e": e2e, "gpu_launches": int(launches), "launches_per_step": int(per_call), "clocks": clocks,
         "sweep": sweep,
     }
+    if stack is not None:
+        line["stack"] = stack
     print(json.dumps(line), flush=True)
 
 
