@@ -28,9 +28,12 @@
 
 namespace fk {
 
-constexpr int kStageBytes = 32768;
+constexpr int kStageBytes = 32768;          // weight bytes per stage
+constexpr int kRowPad = 16;                 // gate_up rows sit 16 bytes further apart in shared memory than in HBM:
+                                            // rows then start in different banks (tensor-core fragment loads)
+constexpr int kStageAlloc = kStageBytes + 64 * kRowPad;
 constexpr int kStages = 4;
-constexpr int kXSlotBytes = 32768;          // 4 rows x 2048 columns x 4 bytes at most
+constexpr int kXSlotBytes = 32768 + 4 * 16;  // 4 rows x 2048 columns x 4 bytes at most, rows padded apart
 constexpr int kXSlots = 2;
 constexpr int kGroupWarps = 8;
 constexpr int kGroups = 2;
@@ -39,9 +42,9 @@ constexpr int kStreamThreads = (kConsumerWarps + 2 + kGroups) * 32;   // + two p
 constexpr int kDownTile = 128;
 
 struct StreamSmem {
-    unsigned char stage[kStages][kStageBytes];
+    unsigned char stage[kStages][kStageAlloc];
     unsigned char xslot[kXSlots][kXSlotBytes];
-    float partial[kGroups][2][kGroupWarps][32];
+    float partial[kGroups][2][kGroupWarps][64];
     int4 header[kXSlots];                    // (expert or -1, first packed row, rows, first token)
     int4 pmeta[kGroups][2];                  // per partial buffer: (first packed row, rows valid, tile, step)
     uint64_t pfull[kGroups][2];              // partial sums of a stage are complete (8 consumer warps arrive)
@@ -133,7 +136,7 @@ __device__ __forceinline__ void consume_unit(const ExpertParams& p, StreamSmem& 
 #pragma unroll
     for (int t = 0; t < NT; ++t) {
         if (t < nvalid) {
-            load8_slot(xrows + (size_t)t * K * elem_bytes(xdtype), xdtype, col0, x[t]);
+            load8_slot(xrows + (size_t)t * (K * elem_bytes(xdtype) + (GU ? kRowPad : 0)), xdtype, col0, x[t]);
         } else {
 #pragma unroll
             for (int i = 0; i < 8; ++i) x[t][i] = 0.f;
@@ -152,8 +155,8 @@ __device__ __forceinline__ void consume_unit(const ExpertParams& p, StreamSmem& 
         if (GU) {
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
-                w[q] = lds128(base + ((size_t)(rg * 4 + q) * K + col0) * 2);
-                w[4 + q] = lds128(base + kStageBytes / 2 + ((size_t)(rg * 4 + q) * K + col0) * 2);
+                w[q] = lds128(base + (size_t)(rg * 4 + q) * (K * 2 + kRowPad) + (size_t)col0 * 2);
+                w[4 + q] = lds128(base + (size_t)(4 * RG + rg * 4 + q) * (K * 2 + kRowPad) + (size_t)col0 * 2);
             }
         } else {
 #pragma unroll
@@ -200,6 +203,79 @@ __device__ __forceinline__ void consume_unit(const ExpertParams& p, StreamSmem& 
     }
 }
 
+// bf16 tensor-core variant of the gate_up consumer (activations in bf16): the 8 weight rows of the warp's
+// row group are the M rows of m16n8k16 MMAs (rows 8..15 of the tile are zero), up to 8 tokens are its N
+// columns, and the warp's 256-column K slice is 16 MMAs.  The MMAs replace 8 unpack + 8*tokens FMA
+// instructions per 8 weights per lane, which is what kept the CUDA-core version from reaching the copy
+// rate; products of bf16 values are exact in fp32 either way.  Partial sums land as [row 0..7][token 0..7].
+__device__ __forceinline__ void mma_bf16_16x8x16(float (&c)[4], uint32_t a0, uint32_t a2, uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a0), "r"(0u), "r"(a2), "r"(0u), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t lds32(const void* smem_ptr) {
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(smem_u32(smem_ptr)));
+    return v;
+}
+
+template <int KCH>
+__device__ __forceinline__ void consume_unit_mma(const ExpertParams& p, StreamSmem& s, const unsigned char* xrows,
+                                                 int row_pos, int nvalid, int tile, uint32_t& it, int& pbuf, uint32_t& nstage,
+                                                 uint64_t* xempty, int g, int w8, int lane) {
+    constexpr int RG = 8 / KCH;
+    constexpr int K = KCH * 256;
+    constexpr int TILE = stream_tile(KCH, true);
+    constexpr int PER_STAGE = 4 * RG;
+    constexpr int STEPS = TILE / PER_STAGE;
+    constexpr int WSTRIDE = K * 2 + kRowPad;
+    const int kw = w8 % KCH, rg = w8 / KCH;
+    const int gid = lane >> 2, tig = lane & 3;          // fragment coordinates: row / token = gid, k pair = tig
+    // B fragments: token gid, this warp's K slice, 16 k-steps x 2 registers
+    uint32_t bf[16][2];
+    {
+        const unsigned char* xr = xrows + (size_t)gid * WSTRIDE + (size_t)(kw * 256 + 2 * tig) * 2;
+#pragma unroll
+        for (int ks = 0; ks < 16; ++ks) {
+            bf[ks][0] = gid < nvalid ? lds32(xr + ks * 32) : 0u;
+            bf[ks][1] = gid < nvalid ? lds32(xr + ks * 32 + 16) : 0u;
+        }
+    }
+    bool x_released = false;
+    // weight row of this lane inside the stage: rows 0..3 of the fragment are gate rows, 4..7 the up rows
+    const int srow = gid < 4 ? rg * 4 + gid : 4 * RG + rg * 4 + (gid - 4);
+#pragma unroll 1
+    for (int step = 0; step < STEPS; ++step, ++it) {
+        if ((int)(it & 1u) != g) continue;
+        const int stage = it % kStages;
+        const uint32_t par = (it / kStages) & 1u;
+        mbar_wait(&s.full[stage], par, &s.abort_flag);
+        const unsigned char* wr = s.stage[stage] + (size_t)srow * WSTRIDE + (size_t)(kw * 256 + 2 * tig) * 2;
+        float c0[4] = {0.f, 0.f, 0.f, 0.f}, c1[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int ks = 0; ks < 16; ks += 2) {
+            mma_bf16_16x8x16(c0, lds32(wr + ks * 32), lds32(wr + ks * 32 + 16), bf[ks][0], bf[ks][1]);
+            mma_bf16_16x8x16(c1, lds32(wr + (ks + 1) * 32), lds32(wr + (ks + 1) * 32 + 16), bf[ks + 1][0], bf[ks + 1][1]);
+        }
+        const float v0 = c0[0] + c1[0], v1 = c0[1] + c1[1];      // row gid, tokens 2*tig and 2*tig+1
+        const float dep = v0 + v1;
+        if (lane == 0) {
+            mbar_arrive_after(&s.empty[stage], dep);
+            if (!x_released) mbar_arrive_after(xempty, dep);
+        }
+        x_released = true;
+        mbar_wait(&s.pempty[g][pbuf], ((nstage >> 1) & 1u) ^ 1u, &s.abort_flag);
+        float* part = s.partial[g][pbuf][w8];
+        *reinterpret_cast<float2*>(part + gid * 8 + 2 * tig) = make_float2(v0, v1);
+        if (w8 == 0 && lane == 0) s.pmeta[g][pbuf] = make_int4(row_pos, nvalid | (1 << 16), tile, step);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&s.pfull[g][pbuf]);
+        ++nstage;
+        pbuf ^= 1;
+    }
+}
+
 // Epilogue warp of group g: sums the K-slices of every output of a stage, applies SwiGLU (gate_up) and
 // stores.  It runs beside the consumers, so the final sum and the global stores are off their path.
 template <int KCH, bool GU>
@@ -211,8 +287,10 @@ __device__ __forceinline__ void epilogue_warp(const ExpertParams& p, StreamSmem&
     for (uint32_t n = 0; n < stages; ++n) {
         const int pb = n & 1u;
         mbar_wait(&s.pfull[g][pb], (n >> 1) & 1u, &s.abort_flag);
-        const int4 m = s.pmeta[g][pb];                       // first packed row, rows valid, tile, step
-        const int NT = m.y == 1 ? 1 : (m.y == 2 ? 2 : 4);
+        int4 m = s.pmeta[g][pb];                             // first packed row, rows valid, tile, step
+        const bool mma_layout = (m.y >> 16) != 0;            // tensor-core consumers: partial[row 0..7][token 0..7]
+        m.y &= 0xffff;
+        const int NT = mma_layout ? 8 : (m.y == 1 ? 1 : (m.y == 2 ? 2 : 4));
         for (int idx = lane; idx < PER_STAGE * NT; idx += 32) {
             const int t = idx % NT;
             const int o = idx / NT;                          // output index inside the stage
@@ -275,7 +353,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) stream_gemv_kernel(ExpertPa
 
     if (warp == kConsumerWarps) {
         // ---------------------------------------------------------------- weight producer
-        if (lane == 0) {
+        {
             uint32_t it = 0;
             int unit = blockIdx.x;
             int4 next = unit < units ? p.passes[unit / tiles] : make_int4(0, 0, 0, 0);
@@ -295,13 +373,19 @@ __global__ void __launch_bounds__(kStreamThreads, 1) stream_gemv_kernel(ExpertPa
                     const int stage = it % kStages;
                     const uint32_t par = (it / kStages) & 1u;
                     unsigned char* sbuf = s.stage[stage];
-                    mbar_wait(&s.empty[stage], par ^ 1u, &s.abort_flag);
-                    mbar_expect_tx(&s.full[stage], kStageBytes);
+                    if (lane == 0) {
+                        mbar_wait(&s.empty[stage], par ^ 1u, &s.abort_flag);
+                        mbar_expect_tx(&s.full[stage], kStageBytes);
+                    }
+                    __syncwarp();
                     const size_t first = (size_t)tile * TILE + (size_t)step * PER_STAGE;
                     if (GU) {
-                        bulk_load(sbuf, W + first * K, kStageBytes / 2, &s.full[stage]);
-                        bulk_load(sbuf + kStageBytes / 2, W + ((size_t)p.I + first) * K, kStageBytes / 2, &s.full[stage]);
-                    } else {
+                        // one copy per weight row (gate rows first, then the up rows of the same pairs), rows padded apart
+                        for (int r = lane; r < 2 * PER_STAGE; r += 32) {
+                            const size_t grow = r < PER_STAGE ? first + r : (size_t)p.I + first + (r - PER_STAGE);
+                            bulk_load(sbuf + (size_t)r * (K * 2 + kRowPad), W + grow * K, K * 2, &s.full[stage]);
+                        }
+                    } else if (lane == 0) {
                         bulk_load(sbuf, W + first * K, kStageBytes, &s.full[stage]);
                     }
                 }
@@ -334,7 +418,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) stream_gemv_kernel(ExpertPa
             }
             __syncwarp();
             if (GU) {
-                if (lane < pass.z) bulk_load(s.xslot[slot] + (size_t)lane * xrow_bytes, src, xrow_bytes, &s.xfull[slot]);
+                if (lane < pass.z) bulk_load(s.xslot[slot] + (size_t)lane * (xrow_bytes + kRowPad), src, xrow_bytes, &s.xfull[slot]);
             } else if (lane == 0) {
                 bulk_load(s.xslot[slot], src, (uint32_t)(pass.z * xrow_bytes), &s.xfull[slot]);
             }
@@ -356,7 +440,9 @@ __global__ void __launch_bounds__(kStreamThreads, 1) stream_gemv_kernel(ExpertPa
             mbar_wait(&s.xfull[slot], par, &s.abort_flag);
             const int4 pass = s.header[slot];
             const unsigned char* xrows = s.xslot[slot];
-            if (pass.z == 1) consume_unit<1, KCH, GU>(p, s, xrows, xdtype, pass.y, 1, tile, it, pbuf, nstage, &s.xempty[slot], g, w8, lane);
+            if (GU && xdtype == FK_BF16)
+                consume_unit_mma<KCH>(p, s, xrows, pass.y, pass.z, tile, it, pbuf, nstage, &s.xempty[slot], g, w8, lane);
+            else if (pass.z == 1) consume_unit<1, KCH, GU>(p, s, xrows, xdtype, pass.y, 1, tile, it, pbuf, nstage, &s.xempty[slot], g, w8, lane);
             else if (pass.z == 2) consume_unit<2, KCH, GU>(p, s, xrows, xdtype, pass.y, 2, tile, it, pbuf, nstage, &s.xempty[slot], g, w8, lane);
             else consume_unit<4, KCH, GU>(p, s, xrows, xdtype, pass.y, pass.z, tile, it, pbuf, nstage, &s.xempty[slot], g, w8, lane);
         }
