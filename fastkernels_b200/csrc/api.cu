@@ -1,6 +1,7 @@
 // C ABI of libfkmoe (declarations and reference citations: include/fkmoe.h).
 
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 
 #include "common.cuh"
@@ -11,6 +12,11 @@ namespace fk {
 static thread_local char g_last_error[256] = "";
 static unsigned long long g_launches = 0;
 thread_local StageTimer* g_stage_timer = nullptr;
+
+bool pdl_enabled() {
+    static const bool on = [] { const char* e = getenv("FKMOE_NO_PDL"); return !(e && e[0] == '1'); }();
+    return on;
+}
 
 void note_launch() { __atomic_fetch_add(&g_launches, 1ull, __ATOMIC_RELAXED); }
 

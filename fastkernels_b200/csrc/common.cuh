@@ -111,6 +111,13 @@ __device__ __forceinline__ float warp_max(float v) {
     return v;
 }
 
+// Programmatic dependent launch: a kernel launched with launch_pdl() may become resident while the
+// kernel before it in the stream is still draining.  It must call pdl_wait() before it touches global
+// memory (the wait returns once the previous grid has completed and its writes are visible);
+// pdl_trigger() lets the next kernel in the stream start its own prologue early.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 __device__ __forceinline__ float silu_mul(float g, float u) { return g / (1.0f + expf(-g)) * u; }
 __device__ __forceinline__ float sigmoidf_(float x) { return 1.0f / (1.0f + expf(-x)); }
 
@@ -144,6 +151,24 @@ inline void stage_mark() {
             return FK_ERR_CUDA;                          \
         }                                                \
     } while (0)
+namespace fk {
+bool pdl_enabled();
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kern, KArgs(args)...);
+}
+}  // namespace fk
+
 #define FK_LAUNCH_OK(where)                              \
     do {                                                 \
         fk::note_launch();                               \

@@ -128,6 +128,8 @@ int launch_experts_generic(const ExpertParams& p, int weight_dtype, cudaStream_t
 // Ordered combine
 // ---------------------------------------------------------------------------------------------
 __global__ void combine_kernel(ExpertParams p) {
+    pdl_trigger();
+    pdl_wait();
     const long long total = (long long)p.T * p.H;
     for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
         int t = (int)(i / p.H), h = (int)(i - (long long)t * p.H);
@@ -150,7 +152,7 @@ int launch_combine(const ExpertParams& p, cudaStream_t stream) {
     long long total = (long long)p.T * p.H;
     int blocks = (int)((total + 255) / 256);
     if (blocks > 148 * 8) blocks = 148 * 8;
-    combine_kernel<<<blocks, 256, 0, stream>>>(p);
+    FK_CUDA_OK(launch_pdl(combine_kernel, dim3(blocks), dim3(256), 0, stream, p), "combine launch");
     FK_LAUNCH_OK("combine launch");
     return FK_OK;
 }

@@ -344,7 +344,9 @@ __global__ void __launch_bounds__(kStreamThreads, 1) stream_gemv_kernel(ExpertPa
         s.abort_flag = 0;
         mbar_init_fence();
     }
+    pdl_trigger();
     __syncthreads();
+    pdl_wait();               // pass list, packed order and activations come from the kernels before
 
     const int tiles = (GU ? p.I : p.H) / TILE;
     const int units = p.meta[1] * tiles;
@@ -479,7 +481,7 @@ static int launch_stream_t(const ExpertParams& p, cudaStream_t stream) {
     auto kern = stream_gemv_kernel<KCH, GU>;
     const int smem = (int)sizeof(StreamSmem) + 128;
     FK_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem), "stream gemv attr");
-    kern<<<sm_count(), kStreamThreads, smem, stream>>>(p);
+    FK_CUDA_OK(launch_pdl(kern, dim3(sm_count()), dim3(kStreamThreads), (size_t)smem, stream, p), "stream gemv launch");
     FK_LAUNCH_OK(GU ? "gate_up stream launch" : "down stream launch");
     return FK_OK;
 }

@@ -31,7 +31,9 @@ __global__ void __launch_bounds__(kPermWarps * 32) permute_kernel(PermuteParams 
     __shared__ int warp_cnt[kPermWarps], warp_flag[kPermWarps];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
 
+    pdl_trigger();
     for (int i = tid; i < kPermWarps * E; i += blockDim.x) whist[i] = 0;
+    pdl_wait();               // the ids come from the router
     __syncthreads();
 
     const int seg = (R + kPermWarps - 1) / kPermWarps;
@@ -132,7 +134,7 @@ int launch_permute(const PermuteParams& p, cudaStream_t stream) {
     if (p.E < 1 || p.E > FK_MAX_EXPERTS || p.routes < 0) return FK_ERR_ARG;
     size_t smem = sizeof(int) * ((size_t)kPermWarps * p.E + p.E + 2);
     FK_CUDA_OK(cudaFuncSetAttribute(permute_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), "permute attr");
-    permute_kernel<<<1, kPermWarps * 32, smem, stream>>>(p);
+    FK_CUDA_OK(launch_pdl(permute_kernel, dim3(1), dim3(kPermWarps * 32), smem, stream, p), "permute launch");
     FK_LAUNCH_OK("permute launch");
     return FK_OK;
 }

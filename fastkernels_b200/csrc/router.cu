@@ -61,6 +61,8 @@ router_kernel(RouterParams p) {
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int tok0 = blockIdx.y * TPB;
     const int H = p.H, E = p.E;
+    pdl_trigger();
+    pdl_wait();
     const WT* norm_w = reinterpret_cast<const WT*>(p.norm_weight);
     const WT* router_w = reinterpret_cast<const WT*>(p.router_weight);
 
@@ -225,6 +227,8 @@ __global__ void __launch_bounds__(kRouterWarps * 32) router_fast_kernel(RouterPa
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int tok0 = blockIdx.y * TPB;
+    pdl_trigger();
+    pdl_wait();
     const bool has_gate = p.shared_gate_weight != nullptr && p.shared_gate_out != nullptr;
     const int e = blockIdx.x * kRouterWarps + warp;
     const bool is_gate = has_gate && e == E;
@@ -355,7 +359,7 @@ static int launch_router_fast(const RouterParams& p, cudaStream_t stream) {
     const size_t smem = (size_t)kRouterWarps * p.H * 2 + sizeof(float) * ((size_t)TPB * p.H + p.H + TPB + 2) + 8 * sizeof(uint64_t) + 16;
     auto kern = router_fast_kernel<TPB>;
     FK_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), "router attr");
-    kern<<<grid, kRouterWarps * 32, smem, stream>>>(p);
+    FK_CUDA_OK(launch_pdl(kern, grid, dim3(kRouterWarps * 32), smem, stream, p), "router launch");
     FK_LAUNCH_OK("router launch");
     return FK_OK;
 }
@@ -369,14 +373,14 @@ static int launch_router_t(const RouterParams& p, cudaStream_t stream) {
         dim3 grid((p.E + (p.shared_gate_weight && p.shared_gate_out ? 1 : 0) + kRouterWarps - 1) / kRouterWarps, (p.T + TPB - 1) / TPB);
         auto kern = router_kernel<WT, VW, TPB>;
         FK_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), "router attr");
-        kern<<<grid, block, smem, stream>>>(p);
+        FK_CUDA_OK(launch_pdl(kern, grid, block, smem, stream, p), "router launch");
     } else {
         constexpr int TPB = 8;
         size_t smem = sizeof(float) * ((size_t)TPB * p.H + TPB + p.H);
         dim3 grid((p.E + (p.shared_gate_weight && p.shared_gate_out ? 1 : 0) + kRouterWarps - 1) / kRouterWarps, (p.T + TPB - 1) / TPB);
         auto kern = router_kernel<WT, VW, TPB>;
         FK_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), "router attr");
-        kern<<<grid, block, smem, stream>>>(p);
+        FK_CUDA_OK(launch_pdl(kern, grid, block, smem, stream, p), "router launch");
     }
     FK_LAUNCH_OK("router launch");
     return FK_OK;

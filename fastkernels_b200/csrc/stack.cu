@@ -10,6 +10,8 @@ namespace fk {
 __global__ void __launch_bounds__(256) residual_norm_kernel(float* __restrict__ x, const float* __restrict__ update,
                                                             void* __restrict__ normed, int out_dtype, int H, float eps) {
     __shared__ float red[8];
+    pdl_trigger();
+    pdl_wait();
     float* row = x + (size_t)blockIdx.x * H;
     const float* up = update ? update + (size_t)blockIdx.x * H : nullptr;
     float ss = 0.f;
@@ -35,7 +37,7 @@ __global__ void __launch_bounds__(256) residual_norm_kernel(float* __restrict__ 
 
 int launch_residual_norm(float* x, const float* update, void* normed, int out_dtype, int T, int H, float eps, cudaStream_t stream) {
     if (T <= 0) return FK_OK;
-    residual_norm_kernel<<<T, 256, 0, stream>>>(x, update, normed, out_dtype, H, eps);
+    FK_CUDA_OK(launch_pdl(residual_norm_kernel, dim3(T), dim3(256), 0, stream, x, update, normed, out_dtype, H, eps), "residual norm launch");
     FK_LAUNCH_OK("residual norm launch");
     return FK_OK;
 }

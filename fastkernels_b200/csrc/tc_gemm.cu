@@ -69,8 +69,6 @@ tc_grouped_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constan
     const int chunks = K / 64;
     const int tiles = GU ? p.I / 64 : p.H / 128;
     const int rows_per_expert = GU ? 2 * p.I : p.H;
-    const int units = p.meta[1] * tiles;
-
     if (tid == 0) {
         for (int i = 0; i < kNumStages; ++i) { mbar_init(&bar.full[i], 1); mbar_init(&bar.empty[i], 1); }
         for (int i = 0; i < 2; ++i) { mbar_init(&bar.tfull[i], 1); mbar_init(&bar.tempty[i], 4); }
@@ -81,10 +79,13 @@ tc_grouped_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constan
         prefetch_tensormap(&amap);
     }
     if (warp == 1) tmem_alloc(&bar.tmem_base, kTcTmemCols);
+    pdl_trigger();
     tc_fence_before_sync();
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem_base = bar.tmem_base;
+    pdl_wait();               // pass list and gathered activations come from the kernels before
+    const int units = p.meta[1] * tiles;
 
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer
@@ -210,6 +211,8 @@ tc_grouped_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constan
 
 // packed bf16 activations: xg[pos] = hidden[token of packed row pos]; the shared expert's rows follow
 __global__ void gather_rows_kernel(ExpertParams p, __nv_bfloat16* xg) {
+    pdl_trigger();
+    pdl_wait();
     const int routed = p.offsets[p.E];
     const int shared_rows = p.shared_gate_up ? p.shared_n : 0;
     const int chunks = p.H / 8;
@@ -320,7 +323,7 @@ int launch_experts_tc(const ExpertParams& p, __nv_bfloat16* xg, __nv_bfloat16* a
         long long total = (long long)rows * (p.H / 8);
         int blocks = (int)((total + 255) / 256);
         if (blocks > sm_count() * 8) blocks = sm_count() * 8;
-        gather_rows_kernel<<<blocks, 256, 0, stream>>>(p, xg);
+        FK_CUDA_OK(launch_pdl(gather_rows_kernel, dim3(blocks), dim3(256), 0, stream, p, xg), "gather rows launch");
         FK_LAUNCH_OK("gather rows launch");
     }
     TcParams tp{};
@@ -329,7 +332,7 @@ int launch_experts_tc(const ExpertParams& p, __nv_bfloat16* xg, __nv_bfloat16* a
         auto kern = tc_grouped_kernel<true>;
         const int smem = kTcStagesGU * (kTcTileBytes + kTcBBytes) + 1024 + 2 * 64 * kTcUStride * (int)sizeof(float) + 1024;
         FK_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem), "tc gate_up attr");
-        kern<<<sm_count(), kTcThreads, smem, stream>>>(w_gu, s_gu, a_x, tp);
+        FK_CUDA_OK(launch_pdl(kern, dim3(sm_count()), dim3(kTcThreads), (size_t)smem, stream, w_gu, s_gu, a_x, tp), "tc gate_up launch");
         FK_LAUNCH_OK("tc gate_up launch");
     }
     stage_mark();   // end of gate_up
@@ -337,7 +340,7 @@ int launch_experts_tc(const ExpertParams& p, __nv_bfloat16* xg, __nv_bfloat16* a
         auto kern = tc_grouped_kernel<false>;
         const int smem = kTcStages * (kTcTileBytes + kTcBBytes) + 1024 + 1024;
         FK_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem), "tc down attr");
-        kern<<<sm_count(), kTcThreads, smem, stream>>>(w_dn, s_dn, a_act, tp);
+        FK_CUDA_OK(launch_pdl(kern, dim3(sm_count()), dim3(kTcThreads), (size_t)smem, stream, w_dn, s_dn, a_act, tp), "tc down launch");
         FK_LAUNCH_OK("tc down launch");
     }
     stage_mark();   // end of down
