@@ -213,13 +213,17 @@ router_kernel(RouterParams p) {
 // kernel start, all rows in flight together, and the dot products are short rolled loops over 16-byte
 // shared-memory vectors.  A kernel this short is bound by instruction fetch and load latency, so the
 // code is kept small on purpose.  H must be a multiple of 256.
-template <int TPB>
+// XB: the activations are bf16 and stay bf16 in shared memory (half the space, so a block can hold 32
+// tokens and amortise each weight row over all of them); otherwise they are widened to fp32.
+template <int TPB, bool XB>
 __global__ void __launch_bounds__(kRouterWarps * 32) router_fast_kernel(RouterParams p) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     const int H = p.H, E = p.E;
     __nv_bfloat16* wrows = reinterpret_cast<__nv_bfloat16*>(smem_raw);                 // [8][H]
-    float* xs = reinterpret_cast<float*>(smem_raw + (size_t)kRouterWarps * H * 2);     // [TPB][H]
-    float* gain = xs + (size_t)TPB * H;                                               // [H]
+    constexpr int XE = XB ? 2 : 4;                                                    // bytes per stored activation
+    unsigned char* xs_raw = smem_raw + (size_t)kRouterWarps * H * 2;                  // [TPB][H] bf16 or fp32
+    float* xs = reinterpret_cast<float*>(xs_raw);
+    float* gain = reinterpret_cast<float*>(xs_raw + (size_t)TPB * H * XE);            // [H]
     float* rstd = gain + H;                                                           // [TPB]
     uint64_t* bars = reinterpret_cast<uint64_t*>(rstd + TPB + (TPB & 1));             // [8]
     __shared__ int is_last;
@@ -234,19 +238,30 @@ __global__ void __launch_bounds__(kRouterWarps * 32) router_fast_kernel(RouterPa
     const bool is_gate = has_gate && e == E;
     const bool active = e < E || is_gate;
     if (tid == 0) abort_flag = 0;
+    // Each warp's barrier covers its weight row and, when the activations stay bf16, the rows of the
+    // tokens whose mean square the warp takes: all copies of the block are in flight at once.
     if (lane == 0) {
         mbar_init(&bars[warp], 1);
         mbar_init_fence();
+        uint32_t bytes = active ? (uint32_t)H * 2 : 0u;
+        if (XB)
+            for (int t = warp; t < TPB; t += kRouterWarps)
+                if (tok0 + t < p.T) bytes += (uint32_t)H * 2;
+        mbar_expect_tx(&bars[warp], bytes);
         if (active) {
             const __nv_bfloat16* wrow = is_gate ? reinterpret_cast<const __nv_bfloat16*>(p.shared_gate_weight)
                                                 : reinterpret_cast<const __nv_bfloat16*>(p.router_weight) + (size_t)e * H;
-            mbar_expect_tx(&bars[warp], (uint32_t)H * 2);
             bulk_load(wrows + (size_t)warp * H, wrow, (uint32_t)H * 2, &bars[warp]);
         }
+        if (XB)
+            for (int t = warp; t < TPB; t += kRouterWarps)
+                if (tok0 + t < p.T)
+                    bulk_load(xs_raw + (size_t)t * H * 2, reinterpret_cast<const __nv_bfloat16*>(p.hidden) + (size_t)(tok0 + t) * H,
+                              (uint32_t)H * 2, &bars[warp]);
     }
     // activations -> fp32 in shared memory; norm gains next to them
     const int chunks = H / 8;
-    for (int i = tid; i < TPB * chunks; i += blockDim.x) {
+    for (int i = tid; i < (XB ? 0 : TPB * chunks); i += blockDim.x) {
         const int t = i / chunks, c = i - t * chunks;
         const int token = tok0 + t;
         float v[8];
@@ -275,12 +290,25 @@ __global__ void __launch_bounds__(kRouterWarps * 32) router_fast_kernel(RouterPa
         dst[1] = make_float4(o + bf16lo(raw.z), o + bf16hi(raw.z), o + bf16lo(raw.w), o + bf16hi(raw.w));
     }
     __syncthreads();
+    if (XB) mbar_wait(&bars[warp], 0, &abort_flag);     // this warp's rows (and its weight row) have landed
     for (int t = warp; t < TPB; t += kRouterWarps) {
         float ss = 0.f;
+        if (XB) {
+#pragma unroll 2
+            for (int h = lane * 8; h < H; h += 256) {
+                const uint4 v = *reinterpret_cast<const uint4*>(xs_raw + ((size_t)t * H + h) * 2);
+                float f;
+                f = bf16lo(v.x); ss = fmaf(f, f, ss); f = bf16hi(v.x); ss = fmaf(f, f, ss);
+                f = bf16lo(v.y); ss = fmaf(f, f, ss); f = bf16hi(v.y); ss = fmaf(f, f, ss);
+                f = bf16lo(v.z); ss = fmaf(f, f, ss); f = bf16hi(v.z); ss = fmaf(f, f, ss);
+                f = bf16lo(v.w); ss = fmaf(f, f, ss); f = bf16hi(v.w); ss = fmaf(f, f, ss);
+            }
+        } else {
 #pragma unroll 4
-        for (int h = lane * 4; h < H; h += 128) {
-            const float4 v = *reinterpret_cast<const float4*>(xs + (size_t)t * H + h);
-            ss = fmaf(v.x, v.x, ss); ss = fmaf(v.y, v.y, ss); ss = fmaf(v.z, v.z, ss); ss = fmaf(v.w, v.w, ss);
+            for (int h = lane * 4; h < H; h += 128) {
+                const float4 v = *reinterpret_cast<const float4*>(xs + (size_t)t * H + h);
+                ss = fmaf(v.x, v.x, ss); ss = fmaf(v.y, v.y, ss); ss = fmaf(v.z, v.z, ss); ss = fmaf(v.w, v.w, ss);
+            }
         }
         ss = warp_sum(ss);
         if (lane == 0) rstd[t] = rsqrtf(ss / (float)H + p.eps);
@@ -288,7 +316,7 @@ __global__ void __launch_bounds__(kRouterWarps * 32) router_fast_kernel(RouterPa
     __syncthreads();
 
     if (active) {
-        mbar_wait(&bars[warp], 0, &abort_flag);
+        if (!XB) mbar_wait(&bars[warp], 0, &abort_flag);
         float acc[TPB];
 #pragma unroll
         for (int t = 0; t < TPB; ++t) acc[t] = 0.f;
@@ -306,8 +334,15 @@ __global__ void __launch_bounds__(kRouterWarps * 32) router_fast_kernel(RouterPa
             }
 #pragma unroll
             for (int t = 0; t < TPB; ++t) {
-                const float4 x0 = *reinterpret_cast<const float4*>(xs + (size_t)t * H + c);
-                const float4 x1 = *reinterpret_cast<const float4*>(xs + (size_t)t * H + c + 4);
+                float4 x0, x1;
+                if (XB) {
+                    const uint4 xv = *reinterpret_cast<const uint4*>(xs_raw + ((size_t)t * H + c) * 2);
+                    x0 = make_float4(bf16lo(xv.x), bf16hi(xv.x), bf16lo(xv.y), bf16hi(xv.y));
+                    x1 = make_float4(bf16lo(xv.z), bf16hi(xv.z), bf16lo(xv.w), bf16hi(xv.w));
+                } else {
+                    x0 = *reinterpret_cast<const float4*>(xs + (size_t)t * H + c);
+                    x1 = *reinterpret_cast<const float4*>(xs + (size_t)t * H + c + 4);
+                }
                 float a = acc[t];
                 a = fmaf(wf[0], x0.x, a); a = fmaf(wf[1], x0.y, a); a = fmaf(wf[2], x0.z, a); a = fmaf(wf[3], x0.w, a);
                 a = fmaf(wf[4], x1.x, a); a = fmaf(wf[5], x1.y, a); a = fmaf(wf[6], x1.z, a); a = fmaf(wf[7], x1.w, a);
@@ -352,12 +387,12 @@ __global__ void __launch_bounds__(kRouterWarps * 32) router_fast_kernel(RouterPa
     }
 }
 
-template <int TPB>
+template <int TPB, bool XB>
 static int launch_router_fast(const RouterParams& p, cudaStream_t stream) {
     const int gate = (p.shared_gate_weight && p.shared_gate_out) ? 1 : 0;
     dim3 grid((p.E + gate + kRouterWarps - 1) / kRouterWarps, (p.T + TPB - 1) / TPB);
-    const size_t smem = (size_t)kRouterWarps * p.H * 2 + sizeof(float) * ((size_t)TPB * p.H + p.H + TPB + 2) + 8 * sizeof(uint64_t) + 16;
-    auto kern = router_fast_kernel<TPB>;
+    const size_t smem = (size_t)kRouterWarps * p.H * 2 + (size_t)TPB * p.H * (XB ? 2 : 4) + sizeof(float) * ((size_t)p.H + TPB + 2) + 8 * sizeof(uint64_t) + 16;
+    auto kern = router_fast_kernel<TPB, XB>;
     FK_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), "router attr");
     FK_CUDA_OK(launch_pdl(kern, grid, dim3(kRouterWarps * 32), smem, stream, p), "router launch");
     FK_LAUNCH_OK("router launch");
@@ -395,7 +430,17 @@ int launch_router(const RouterParams& p, int weight_dtype, cudaStream_t stream) 
             return (aligned && p.H % 4 == 0) ? launch_router_t<float, 4>(p, stream) : launch_router_t<float, 1>(p, stream);
         case FK_BF16:
             if (aligned && p.H % 256 == 0 && p.H <= 4096 && ((reinterpret_cast<uintptr_t>(p.hidden) | reinterpret_cast<uintptr_t>(p.shared_gate_weight)) & 15) == 0)
-                return p.T <= 64 ? launch_router_fast<4>(p, stream) : launch_router_fast<8>(p, stream);
+            {
+                // 32 bf16 tokens per block from 32 tokens up; small batches keep 4-token blocks for parallelism
+                // tokens per block grow with the batch so that the grid stays near two blocks per SM
+                if (p.hidden_dtype == FK_BF16) {
+                    if (p.T <= 32) return launch_router_fast<4, true>(p, stream);
+                    if (p.T <= 64) return launch_router_fast<8, true>(p, stream);
+                    if (p.T <= 128) return launch_router_fast<16, true>(p, stream);
+                    return launch_router_fast<32, true>(p, stream);
+                }
+                return p.T <= 64 ? launch_router_fast<4, false>(p, stream) : launch_router_fast<8, false>(p, stream);
+            }
             return (aligned && p.H % 8 == 0) ? launch_router_t<__nv_bfloat16, 8>(p, stream)
                                              : launch_router_t<__nv_bfloat16, 1>(p, stream);
         case FK_F16:
@@ -436,7 +481,7 @@ static int noalloc_tickets(unsigned** out) {
 }
 
 int launch_router_noalloc(RouterParams p, int weight_dtype, cudaStream_t stream) {
-    const int tpb = p.T <= 64 ? 4 : 8;                       // tokens per block, as launch_router picks them
+    const int tpb = 4;                                       // fewest tokens per block launch_router may pick
     if ((p.T + tpb - 1) / tpb > kNoAllocTicketSlots) return FK_ERR_ARG;
     unsigned* tickets = nullptr;
     int st = noalloc_tickets(&tickets);
