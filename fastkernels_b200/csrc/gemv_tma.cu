@@ -22,8 +22,11 @@
 //
 // Reference math: src/fastkernels/reference/qwen36_real.py:343-347.
 
+#include <cuda.h>
+
 #include "common.cuh"
 #include "kernels.cuh"
+#include "tcgen05.cuh"
 #include "tma.cuh"
 
 namespace fk {
@@ -276,6 +279,99 @@ __device__ __forceinline__ void consume_unit_mma(const ExpertParams& p, StreamSm
     }
 }
 
+// Tensor-core variant of the down consumer (bf16 models).  The activations are the fp32 SwiGLU outputs;
+// each is split into a bf16 head and a bf16 remainder (together 16 mantissa bits, relative error 2^-17),
+// so every weight fragment feeds two MMAs.  A warp owns 16 output rows (a full M tile, fetched with one
+// ldmatrix.x4 per k-step from the padded rows) and a 128-column K slice; a pass has at most 4 tokens,
+// so only N columns 0..3 are kept.  Partial sums land as [row 0..15][token 0..3].
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* smem_ptr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_u32(smem_ptr)));
+}
+__device__ __forceinline__ void mma_bf16_full(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void split_bf16x2(float x, float y, uint32_t& head, uint32_t& rest) {
+    const __nv_bfloat162 h = __floats2bfloat162_rn(x, y);
+    const float2 hf = __bfloat1622float2(h);
+    const __nv_bfloat162 l = __floats2bfloat162_rn(x - hf.x, y - hf.y);
+    head = *reinterpret_cast<const uint32_t*>(&h);
+    rest = *reinterpret_cast<const uint32_t*>(&l);
+}
+
+template <int KCH>
+__device__ __forceinline__ void consume_unit_mma_down(const ExpertParams& p, StreamSmem& s, const unsigned char* xrows,
+                                                      int row_pos, int nvalid, int tile, uint32_t& it, int& pbuf, uint32_t& nstage,
+                                                      uint64_t* xempty, int g, int w8, int lane) {
+    static_assert(KCH <= 4, "a stage must hold at least 16 rows");
+    constexpr int K = KCH * 256;
+    constexpr int TILE = stream_tile(KCH, false);
+    constexpr int PER_STAGE = 64 / KCH;
+    constexpr int STEPS = TILE / PER_STAGE;
+    constexpr int KS = 2 * KCH;                          // 128-column K slices per 16-row tile
+    const int rt = w8 / KS, ks = w8 % KS;
+    const int gid = lane >> 2, tig = lane & 3;
+    // B fragments: token gid, 8 k-steps, head and remainder
+    uint32_t bh[8][2], bl[8][2];
+    {
+        const unsigned char* xr = xrows + (size_t)gid * (K * 4) + (size_t)(ks * 128 + 2 * tig) * 4;
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+            float2 v0 = make_float2(0.f, 0.f), v1 = make_float2(0.f, 0.f);
+            if (gid < nvalid) {
+                v0 = *reinterpret_cast<const float2*>(xr + q * 64);
+                v1 = *reinterpret_cast<const float2*>(xr + q * 64 + 32);
+            }
+            split_bf16x2(v0.x, v0.y, bh[q][0], bl[q][0]);
+            split_bf16x2(v1.x, v1.y, bh[q][1], bl[q][1]);
+        }
+    }
+    bool x_released = false;
+    // ldmatrix row address of this lane: matrices 0..3 = (rows 0-7, k 0-7), (rows 8-15, k 0-7), (rows 0-7, k 8-15), (rows 8-15, k 8-15).
+    // A stage is K/64 slabs of [PER_STAGE rows x 128 bytes]; inside a slab the 16-byte chunk c of row r sits at chunk c ^ (r & 7).
+    const int lrow = rt * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
+    const int lofs = (ks * 2) * (PER_STAGE * 128) + lrow * 128;
+    const int lx = (lane >> 4) ^ (lane & 7);
+#pragma unroll 1
+    for (int step = 0; step < STEPS; ++step, ++it) {
+        if ((int)(it & 1u) != g) continue;
+        const int stage = it % kStages;
+        const uint32_t par = (it / kStages) & 1u;
+        mbar_wait(&s.full[stage], par, &s.abort_flag);
+        const unsigned char* wr = s.stage[stage] + lofs;
+        float c0[4] = {0.f, 0.f, 0.f, 0.f}, c1[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+            uint32_t a[4];
+            ldmatrix_x4(a, wr + (q >> 2) * (PER_STAGE * 128) + ((((q & 3) * 2) ^ lx) << 4));
+            mma_bf16_full(c0, a, bh[q][0], bh[q][1]);
+            mma_bf16_full(c1, a, bl[q][0], bl[q][1]);
+        }
+        const float2 lo = make_float2(c0[0] + c1[0], c0[1] + c1[1]);     // row gid,     tokens 2*tig, 2*tig+1
+        const float2 hi = make_float2(c0[2] + c1[2], c0[3] + c1[3]);     // row gid + 8, same tokens
+        const float dep = lo.x + hi.x;
+        if (lane == 0) {
+            mbar_arrive_after(&s.empty[stage], dep);
+            if (!x_released) mbar_arrive_after(xempty, dep);
+        }
+        x_released = true;
+        mbar_wait(&s.pempty[g][pbuf], ((nstage >> 1) & 1u) ^ 1u, &s.abort_flag);
+        float* part = s.partial[g][pbuf][w8];
+        if (tig < 2) {
+            *reinterpret_cast<float2*>(part + gid * 4 + 2 * tig) = lo;
+            *reinterpret_cast<float2*>(part + (gid + 8) * 4 + 2 * tig) = hi;
+        }
+        if (w8 == 0 && lane == 0) s.pmeta[g][pbuf] = make_int4(row_pos, nvalid | (2 << 16), tile, step);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&s.pfull[g][pbuf]);
+        ++nstage;
+        pbuf ^= 1;
+    }
+}
+
 // Epilogue warp of group g: sums the K-slices of every output of a stage, applies SwiGLU (gate_up) and
 // stores.  It runs beside the consumers, so the final sum and the global stores are off their path.
 template <int KCH, bool GU>
@@ -288,8 +384,23 @@ __device__ __forceinline__ void epilogue_warp(const ExpertParams& p, StreamSmem&
         const int pb = n & 1u;
         mbar_wait(&s.pfull[g][pb], (n >> 1) & 1u, &s.abort_flag);
         int4 m = s.pmeta[g][pb];                             // first packed row, rows valid, tile, step
-        const bool mma_layout = (m.y >> 16) != 0;            // tensor-core consumers: partial[row 0..7][token 0..7]
+        const int layout = m.y >> 16;                        // 1: tensor-core gate_up, partial[row 0..7][token 0..7]
+        const bool mma_layout = layout == 1;                 // 2: tensor-core down,    partial[row 0..15][token 0..3]
         m.y &= 0xffff;
+        if (!GU && layout == 2) {
+            constexpr int KS = 2 * KCH;
+            for (int idx = lane; idx < PER_STAGE * 4; idx += 32) {
+                const int t = idx & 3, o = idx >> 2;
+                const int rt = o >> 4, r16 = o & 15;
+                float sum = 0.f;
+#pragma unroll
+                for (int k2 = 0; k2 < (KS <= 8 ? KS : 8); ++k2) sum += s.partial[g][pb][(rt * KS + k2) & 7][r16 * 4 + t];
+                if (t < m.y) p.y[(size_t)(m.x + t) * p.H + m.z * TILE + m.w * PER_STAGE + o] = sum;
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&s.pempty[g][pb]);
+            continue;
+        }
         const int NT = mma_layout ? 8 : (m.y == 1 ? 1 : (m.y == 2 ? 2 : 4));
         for (int idx = lane; idx < PER_STAGE * NT; idx += 32) {
             const int t = idx % NT;
@@ -316,10 +427,15 @@ __device__ __forceinline__ void epilogue_warp(const ExpertParams& p, StreamSmem&
     }
 }
 
-template <int KCH, bool GU>
-__global__ void __launch_bounds__(kStreamThreads, 1) stream_gemv_kernel(ExpertParams p) {
+// TM (down only): the weight stages are filled by tiled TMA copies through tensor maps (`wmap` for the
+// routed experts' [E*H, I] matrix, `smap` for the shared expert's [H, I]) in the 128-byte swizzled layout
+// that the tensor-core consumer's ldmatrix reads without bank conflicts.
+template <int KCH, bool GU, bool TM>
+__global__ void __launch_bounds__(kStreamThreads, 1) stream_gemv_kernel(const __grid_constant__ CUtensorMap wmap,
+                                                                        const __grid_constant__ CUtensorMap smap, ExpertParams p) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
-    StreamSmem& s = *reinterpret_cast<StreamSmem*>(smem_raw);
+    // the swizzle pattern is a function of the shared-memory address: stages start on 1 KB boundaries
+    StreamSmem& s = *reinterpret_cast<StreamSmem*>(smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u));
     constexpr int RG = 8 / KCH;
     constexpr int K = KCH * 256;
     constexpr int TILE = stream_tile(KCH, GU);
@@ -387,6 +503,12 @@ __global__ void __launch_bounds__(kStreamThreads, 1) stream_gemv_kernel(ExpertPa
                             const size_t grow = r < PER_STAGE ? first + r : (size_t)p.I + first + (r - PER_STAGE);
                             bulk_load(sbuf + (size_t)r * (K * 2 + kRowPad), W + grow * K, K * 2, &s.full[stage]);
                         }
+                    } else if (TM) {
+                        // one box of [PER_STAGE rows x 64 columns] per 128-byte column slab, 128-byte swizzle
+                        const CUtensorMap* map = pass.x < 0 ? &smap : &wmap;
+                        const int y = (pass.x < 0 ? 0 : pass.x * p.H) + (int)first;
+                        for (int sl = lane; sl < K / 64; sl += 32)
+                            tma_load_2d(sbuf + (size_t)sl * (PER_STAGE * 128), map, sl * 64, y, &s.full[stage]);
                     } else if (lane == 0) {
                         bulk_load(sbuf, W + first * K, kStageBytes, &s.full[stage]);
                     }
@@ -444,6 +566,8 @@ __global__ void __launch_bounds__(kStreamThreads, 1) stream_gemv_kernel(ExpertPa
             const unsigned char* xrows = s.xslot[slot];
             if (GU && xdtype == FK_BF16)
                 consume_unit_mma<KCH>(p, s, xrows, pass.y, pass.z, tile, it, pbuf, nstage, &s.xempty[slot], g, w8, lane);
+            else if (TM)
+                consume_unit_mma_down<(KCH <= 4 ? KCH : 4)>(p, s, xrows, pass.y, pass.z, tile, it, pbuf, nstage, &s.xempty[slot], g, w8, lane);
             else if (pass.z == 1) consume_unit<1, KCH, GU>(p, s, xrows, xdtype, pass.y, 1, tile, it, pbuf, nstage, &s.xempty[slot], g, w8, lane);
             else if (pass.z == 2) consume_unit<2, KCH, GU>(p, s, xrows, xdtype, pass.y, 2, tile, it, pbuf, nstage, &s.xempty[slot], g, w8, lane);
             else consume_unit<4, KCH, GU>(p, s, xrows, xdtype, pass.y, pass.z, tile, it, pbuf, nstage, &s.xempty[slot], g, w8, lane);
@@ -476,33 +600,47 @@ int sm_count() {
     return cached[dev];
 }
 
-template <int KCH, bool GU>
-static int launch_stream_t(const ExpertParams& p, cudaStream_t stream) {
-    auto kern = stream_gemv_kernel<KCH, GU>;
-    const int smem = (int)sizeof(StreamSmem) + 128;
+template <int KCH, bool GU, bool TM>
+static int launch_stream_t(const ExpertParams& p, cudaStream_t stream, const CUtensorMap& wmap, const CUtensorMap& smap) {
+    auto kern = stream_gemv_kernel<KCH, GU, TM>;
+    const int smem = (int)sizeof(StreamSmem) + 1024;
     FK_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem), "stream gemv attr");
-    FK_CUDA_OK(launch_pdl(kern, dim3(sm_count()), dim3(kStreamThreads), (size_t)smem, stream, p), "stream gemv launch");
+    FK_CUDA_OK(launch_pdl(kern, dim3(sm_count()), dim3(kStreamThreads), (size_t)smem, stream, wmap, smap, p), "stream gemv launch");
     FK_LAUNCH_OK(GU ? "gate_up stream launch" : "down stream launch");
     return FK_OK;
+}
+
+template <int KCH>
+static int launch_down(const ExpertParams& p, cudaStream_t stream) {
+    CUtensorMap wmap{}, smap{};
+    if (KCH <= 4 && p.hidden_dtype == FK_BF16) {
+        // bf16 model: tensor-core consumer over swizzled stages, if the driver can encode the maps
+        const void* any = p.down ? p.down : p.shared_down;
+        const bool ok = weight_tensor_map(any, p.down ? (uint64_t)p.E * p.H : (uint64_t)p.H, p.I, 64 / KCH, &wmap) &&
+                        weight_tensor_map(p.shared_down ? p.shared_down : any, (uint64_t)p.H, p.I, 64 / KCH, &smap);
+        if (ok) return launch_stream_t<KCH, false, (KCH <= 4)>(p, stream, wmap, smap);
+    }
+    return launch_stream_t<KCH, false, false>(p, stream, wmap, smap);
 }
 
 int launch_experts_stream(const ExpertParams& p, cudaStream_t stream) {
     if (p.T <= 0) return FK_OK;
     int st;
+    const CUtensorMap none{};
     switch (p.H / 256) {
-        case 1: st = launch_stream_t<1, true>(p, stream); break;
-        case 2: st = launch_stream_t<2, true>(p, stream); break;
-        case 4: st = launch_stream_t<4, true>(p, stream); break;
-        case 8: st = launch_stream_t<8, true>(p, stream); break;
+        case 1: st = launch_stream_t<1, true, false>(p, stream, none, none); break;
+        case 2: st = launch_stream_t<2, true, false>(p, stream, none, none); break;
+        case 4: st = launch_stream_t<4, true, false>(p, stream, none, none); break;
+        case 8: st = launch_stream_t<8, true, false>(p, stream, none, none); break;
         default: return FK_ERR_UNSUPPORTED;
     }
     if (st != FK_OK) return st;
     stage_mark();   // end of gate_up
     switch (p.I / 256) {
-        case 1: st = launch_stream_t<1, false>(p, stream); break;
-        case 2: st = launch_stream_t<2, false>(p, stream); break;
-        case 4: st = launch_stream_t<4, false>(p, stream); break;
-        case 8: st = launch_stream_t<8, false>(p, stream); break;
+        case 1: st = launch_down<1>(p, stream); break;
+        case 2: st = launch_down<2>(p, stream); break;
+        case 4: st = launch_down<4>(p, stream); break;
+        case 8: st = launch_down<8>(p, stream); break;
         default: return FK_ERR_UNSUPPORTED;
     }
     if (st != FK_OK) return st;

@@ -269,7 +269,7 @@ struct MapKeyHash {
 };
 
 // 2-D bf16 tensor [rows, cols] row-major, box = [box_rows, 64 columns], 128-byte swizzle, zero fill outside
-static bool tensor_map(const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows, CUtensorMap* out) {
+bool weight_tensor_map(const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows, CUtensorMap* out) {
     static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
     static std::mutex mu;
     MapKey key{base, rows, cols, box_rows};
@@ -311,12 +311,12 @@ int launch_experts_tc(const ExpertParams& p, __nv_bfloat16* xg, __nv_bfloat16* a
     const void* dummy_gu = p.gate_up ? p.gate_up : p.shared_gate_up;
     const void* dummy_dn = p.down ? p.down : p.shared_down;
     const uint64_t e_rows = p.gate_up ? (uint64_t)p.E : 0;
-    bool ok = tensor_map(dummy_gu, p.gate_up ? e_rows * 2 * p.I : 2 * p.I, p.H, 64, &w_gu) &&
-              tensor_map(p.shared_gate_up ? p.shared_gate_up : dummy_gu, 2 * (uint64_t)p.I, p.H, 64, &s_gu) &&
-              tensor_map(xg, rows, p.H, 16, &a_x) &&
-              tensor_map(dummy_dn, p.down ? e_rows * p.H : p.H, p.I, 128, &w_dn) &&
-              tensor_map(p.shared_down ? p.shared_down : dummy_dn, (uint64_t)p.H, p.I, 128, &s_dn) &&
-              tensor_map(actb, rows, p.I, 16, &a_act);
+    bool ok = weight_tensor_map(dummy_gu, p.gate_up ? e_rows * 2 * p.I : 2 * p.I, p.H, 64, &w_gu) &&
+              weight_tensor_map(p.shared_gate_up ? p.shared_gate_up : dummy_gu, 2 * (uint64_t)p.I, p.H, 64, &s_gu) &&
+              weight_tensor_map(xg, rows, p.H, 16, &a_x) &&
+              weight_tensor_map(dummy_dn, p.down ? e_rows * p.H : p.H, p.I, 128, &w_dn) &&
+              weight_tensor_map(p.shared_down ? p.shared_down : dummy_dn, (uint64_t)p.H, p.I, 128, &s_dn) &&
+              weight_tensor_map(actb, rows, p.I, 16, &a_act);
     if (!ok) return FK_ERR_UNSUPPORTED;
 
     {

@@ -82,4 +82,8 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, float (&v)[16]) {
     for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
 }
 
+// Cached tensor map of a row-major bf16 matrix [rows, cols] with boxes of [box_rows, 64 columns] and
+// 128-byte swizzle (tc_gemm.cu).  False when the driver's encoder is not available.
+bool weight_tensor_map(const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows, CUtensorMap* out);
+
 }  // namespace fk
