@@ -86,7 +86,8 @@ static int run_experts(const fk_moe_call* c, const Workspace& w, const long long
     const bool want_tc = !generic && !(c->flags & (FK_FLAG_FORCE_GEMV | FK_FLAG_REGISTER_GEMV)) &&
                          ((c->flags & FK_FLAG_FORCE_TENSOR) || d.tokens >= 64);
     const bool use_tc = want_tc && tc_path_supported(ep, c->weight_dtype);
-    pp.pass_rows = use_tc ? 64 : 4;
+    const bool use_stream = !use_tc && !generic && !(c->flags & FK_FLAG_REGISTER_GEMV) && stream_path_supported(ep, c->weight_dtype);
+    pp.pass_rows = use_tc ? 64 : (use_stream ? stream_pass_rows(ep) : 4);
     int st = launch_permute(pp, stream);
     if (st != FK_OK) return st;
     stage_mark();   // end of permute
@@ -103,7 +104,7 @@ static int run_experts(const fk_moe_call* c, const Workspace& w, const long long
     ep.error_word = at<int>(ws, w.meta) + 2;
     if (use_tc)
         st = launch_experts_tc(ep, at<__nv_bfloat16>(ws, w.xg), at<__nv_bfloat16>(ws, w.actb), stream);
-    else if (!generic && !(c->flags & FK_FLAG_REGISTER_GEMV) && stream_path_supported(ep, c->weight_dtype))
+    else if (use_stream)
         st = launch_experts_stream(ep, stream);
     else if (!generic && sh_n == d.tokens && gemv_path_supported(ep, c->weight_dtype))
         st = launch_experts_gemv(ep, stream);

@@ -12,7 +12,7 @@
 // Work is split evenly by bytes: every block streams the same share of every matrix.
 //
 // A producer warp issues bulk copies (one weight row or gate/up pair per 8 KB stage) into a
-// 22-stage shared-memory ring and runs ahead across the barriers: phase C addresses depend only on
+// 24-stage shared-memory ring and runs ahead across the barriers: phase C addresses depend only on
 // the expert ids, so those rows are already in flight while the blocks wait at barrier 2.  Eight
 // consumer warps take the stages round-robin; a stage is handled by one warp (16-byte shared loads,
 // the token's activations in registers, shuffle reduction), so consumers never synchronise with
@@ -31,9 +31,15 @@
 
 namespace fk {
 
-constexpr int kD1Stages = 22;
+constexpr int kD1Stages = 24;
 constexpr int kD1StageBytes = 8192;
 constexpr int kD1Consumers = 8;                  // warps
+// Stage `it` lives in slot it % kD1Stages and is consumed by warp it % kD1Consumers.  The slot count must be a
+// multiple of the warp count: then a slot always belongs to the same warp, which meets its laps in order.  With
+// any other ratio another warp can reach lap k of a slot while lap k-1 is still in flight (bulk copies complete
+// out of order, e.g. after a TLB miss), and a one-bit phase parity cannot tell "lap k landed" from "lap k-1 has
+// not landed yet": the warp would read the slot early and release it twice.
+static_assert(kD1Stages % kD1Consumers == 0, "every ring slot must belong to one consumer warp");
 constexpr int kD1Threads = (kD1Consumers + 1) * 32;
 constexpr int kD1MaxRows = 64;                   // output rows per block (H / #blocks rounded up)
 

@@ -36,7 +36,7 @@ constexpr int kRowPad = 16;                 // gate_up rows sit 16 bytes further
                                             // rows then start in different banks (tensor-core fragment loads)
 constexpr int kStageAlloc = kStageBytes + 64 * kRowPad;
 constexpr int kStages = 4;
-constexpr int kXSlotBytes = 32768 + 4 * 16;  // 4 rows x 2048 columns x 4 bytes at most, rows padded apart
+constexpr int kXSlotBytes = 32768 + 8 * 16;  // 4 fp32 rows or 8 bf16 rows of 2048 columns at most, rows padded apart
 constexpr int kXSlots = 2;
 constexpr int kGroupWarps = 8;
 constexpr int kGroups = 2;
@@ -47,7 +47,7 @@ constexpr int kDownTile = 128;
 struct StreamSmem {
     unsigned char stage[kStages][kStageAlloc];
     unsigned char xslot[kXSlots][kXSlotBytes];
-    float partial[kGroups][2][kGroupWarps][64];
+    float partial[kGroups][2][kGroupWarps][128];
     int4 header[kXSlots];                    // (expert or -1, first packed row, rows, first token)
     int4 pmeta[kGroups][2];                  // per partial buffer: (first packed row, rows valid, tile, step)
     uint64_t pfull[kGroups][2];              // partial sums of a stage are complete (8 consumer warps arrive)
@@ -282,8 +282,7 @@ __device__ __forceinline__ void consume_unit_mma(const ExpertParams& p, StreamSm
 // Tensor-core variant of the down consumer (bf16 models).  The activations are the fp32 SwiGLU outputs;
 // each is split into a bf16 head and a bf16 remainder (together 16 mantissa bits, relative error 2^-17),
 // so every weight fragment feeds two MMAs.  A warp owns 16 output rows (a full M tile, fetched with one
-// ldmatrix.x4 per k-step from the padded rows) and a 128-column K slice; a pass has at most 4 tokens,
-// so only N columns 0..3 are kept.  Partial sums land as [row 0..15][token 0..3].
+// ldmatrix.x4 per k-step from the padded rows) and a 128-column K slice; the up to 8 tokens of a pass are the N columns.  Partial sums land as [row 0..15][token 0..7].
 __device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* smem_ptr) {
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_u32(smem_ptr)));
@@ -360,10 +359,8 @@ __device__ __forceinline__ void consume_unit_mma_down(const ExpertParams& p, Str
         x_released = true;
         mbar_wait(&s.pempty[g][pbuf], ((nstage >> 1) & 1u) ^ 1u, &s.abort_flag);
         float* part = s.partial[g][pbuf][w8];
-        if (tig < 2) {
-            *reinterpret_cast<float2*>(part + gid * 4 + 2 * tig) = lo;
-            *reinterpret_cast<float2*>(part + (gid + 8) * 4 + 2 * tig) = hi;
-        }
+        *reinterpret_cast<float2*>(part + gid * 8 + 2 * tig) = lo;
+        *reinterpret_cast<float2*>(part + (gid + 8) * 8 + 2 * tig) = hi;
         if (w8 == 0 && lane == 0) s.pmeta[g][pbuf] = make_int4(row_pos, nvalid | (2 << 16), tile, step);
         __syncwarp();
         if (lane == 0) mbar_arrive(&s.pfull[g][pbuf]);
@@ -385,16 +382,16 @@ __device__ __forceinline__ void epilogue_warp(const ExpertParams& p, StreamSmem&
         mbar_wait(&s.pfull[g][pb], (n >> 1) & 1u, &s.abort_flag);
         int4 m = s.pmeta[g][pb];                             // first packed row, rows valid, tile, step
         const int layout = m.y >> 16;                        // 1: tensor-core gate_up, partial[row 0..7][token 0..7]
-        const bool mma_layout = layout == 1;                 // 2: tensor-core down,    partial[row 0..15][token 0..3]
+        const bool mma_layout = layout == 1;                 // 2: tensor-core down,    partial[row 0..15][token 0..7]
         m.y &= 0xffff;
         if (!GU && layout == 2) {
             constexpr int KS = 2 * KCH;
-            for (int idx = lane; idx < PER_STAGE * 4; idx += 32) {
-                const int t = idx & 3, o = idx >> 2;
+            for (int idx = lane; idx < PER_STAGE * 8; idx += 32) {
+                const int t = idx & 7, o = idx >> 3;
                 const int rt = o >> 4, r16 = o & 15;
                 float sum = 0.f;
 #pragma unroll
-                for (int k2 = 0; k2 < (KS <= 8 ? KS : 8); ++k2) sum += s.partial[g][pb][(rt * KS + k2) & 7][r16 * 4 + t];
+                for (int k2 = 0; k2 < (KS <= 8 ? KS : 8); ++k2) sum += s.partial[g][pb][(rt * KS + k2) & 7][r16 * 8 + t];
                 if (t < m.y) p.y[(size_t)(m.x + t) * p.H + m.z * TILE + m.w * PER_STAGE + o] = sum;
             }
             __syncwarp();
@@ -574,6 +571,16 @@ __global__ void __launch_bounds__(kStreamThreads, 1) stream_gemv_kernel(const __
         }
         if (s.abort_flag && lane == 0 && p.error_word) atomicExch(p.error_word, 1);
     }
+}
+
+// Rows per pass the streaming kernels want from the permutation: the tensor-core consumers (bf16 models)
+// take 8 tokens as the N columns of an MMA, the CUDA-core consumers keep 4 tokens in registers.
+int stream_pass_rows(const ExpertParams& p) {
+    CUtensorMap probe;
+    const void* any = p.down ? p.down : p.shared_down;
+    const bool mma = p.hidden_dtype == FK_BF16 && p.I <= 1024 && any != nullptr &&
+                     weight_tensor_map(any, p.down ? (uint64_t)p.E * p.H : (uint64_t)p.H, p.I, 64 / (p.I / 256), &probe);
+    return mma ? 8 : 4;
 }
 
 static bool kch_supported(int k) { return k == 256 || k == 512 || k == 1024 || k == 2048; }

@@ -40,7 +40,7 @@ struct PermuteParams {
     int4* passes;             // optional GEMV pass list: routed experts ascending, then the shared expert
     int shared_tokens;        // tokens the shared expert sees (0: no shared expert)
     int shared_tok0;          // first of them
-    int pass_rows;            // rows per pass: 4 for the GEMV kernels, 64 for the tensor-core GEMM
+    int pass_rows;            // rows per pass: 4 or 8 for the GEMV kernels, 64 for the tensor-core GEMM
 };
 int launch_permute(const PermuteParams& p, cudaStream_t stream);
 int launch_histogram(const void* ids, int ids_are_int64, long long count, int E, int* counts, cudaStream_t stream);
@@ -78,6 +78,7 @@ int launch_experts_gemv(const ExpertParams& p, cudaStream_t stream);
 // bf16 grouped GEMV fed by bulk copies through a shared-memory ring (same shapes as the GEMV path)
 bool stream_path_supported(const ExpertParams& p, int weight_dtype);
 int launch_experts_stream(const ExpertParams& p, cudaStream_t stream);
+int stream_pass_rows(const ExpertParams& p);    // 8 when both streaming kernels run their tensor-core consumers, else 4
 // tcgen05 grouped GEMM (bf16, H and I multiples of 128); needs a pass list of <= 64-row passes
 bool tc_path_supported(const ExpertParams& p, int weight_dtype);
 int launch_experts_tc(const ExpertParams& p, __nv_bfloat16* xg, __nv_bfloat16* actb, cudaStream_t stream);
