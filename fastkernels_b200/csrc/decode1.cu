@@ -312,6 +312,22 @@ __global__ void __launch_bounds__(kD1Threads, 1) decode1_kernel(DecodeParams p) 
     const int G = gridDim.x, blk = blockIdx.x;
     const int H = p.H, I = p.I;
     const int nchH = H / 256, nchI = I / 256;
+    if (tid == 0) { D1_TRACE(0); if (p.trace) p.trace[(size_t)blk * 16 + 8] = (unsigned long long)clock64(); }
+
+    // The producer warp prepares the ring itself (one slot per lane) and starts phase A before the block
+    // meets: the first copies are then in flight while the consumers still wait for their activations.
+    if (warp == kD1Consumers) {
+        if (lane < kD1Stages) {
+            mbar_init(&s.full[lane], 1);
+            mbar_init(&s.empty[lane], 1);
+        }
+        if (lane == 0) {
+            mbar_init(&s.ids_ready, 1);
+            s.abort_flag = 0;
+        }
+        mbar_init_fence();
+        __syncwarp();
+    }
 
     // the token's activations: issue these loads before anything else (the first global access of a
     // block pays the longest latency of the whole kernel)
@@ -336,18 +352,6 @@ __global__ void __launch_bounds__(kD1Threads, 1) decode1_kernel(DecodeParams p) 
         }
     }
 
-    if (tid == 0) {
-        for (int i = 0; i < kD1Stages; ++i) {
-            mbar_init(&s.full[i], 1);
-            mbar_init(&s.empty[i], 1);
-        }
-        mbar_init(&s.ids_ready, 1);
-        s.abort_flag = 0;
-        mbar_init_fence();
-    }
-    __syncthreads();
-
-    if (tid == 0) { D1_TRACE(0); if (p.trace) p.trace[(size_t)blk * 16 + 8] = (unsigned long long)clock64(); }
     const D1Plan pl = make_plan(p, blk, G);
     const int nA = pl.nA_router + pl.nA_gate + pl.nA_pair;
     const int nB = pl.nB_pair + pl.nB_down;
@@ -393,6 +397,7 @@ __global__ void __launch_bounds__(kD1Threads, 1) decode1_kernel(DecodeParams p) 
             if (lane < kD1Stages && it < nA) issue(it);
         }
         __syncwarp();
+        __syncthreads();                                               // the consumers may use the barriers from here on
         if (lane == 0) D1_TRACE(2);
         mbar_wait(&s.ids_ready, 0, &s.abort_flag);                     // the consumers select the experts
         if (lane == 0) D1_TRACE(4);
@@ -403,6 +408,7 @@ __global__ void __launch_bounds__(kD1Threads, 1) decode1_kernel(DecodeParams p) 
         }
     } else {
         // ------------------------------------------------------------------ consumer warps
+        __syncthreads();                                               // ring barriers initialised by the producer warp
         const int cthreads = kD1Consumers * 32;
         float ss = 0.f;
 #pragma unroll
