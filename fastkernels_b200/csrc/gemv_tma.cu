@@ -457,9 +457,16 @@ __global__ void __launch_bounds__(kStreamThreads, 1) stream_gemv_kernel(const __
         s.abort_flag = 0;
         mbar_init_fence();
     }
-    pdl_trigger();
     __syncthreads();
-    pdl_wait();               // pass list, packed order and activations come from the kernels before
+    if (GU) {
+        pdl_wait();           // pass list and packed order come from the permutation kernel
+        pdl_trigger();        // only now: the down kernel reads the pass list without waiting (below)
+    } else {
+        // The down kernel is released while the gate_up kernel still runs (which has itself waited for the
+        // permutation).  Its blocks take over SMs as gate_up blocks leave, and their weight producers fill the
+        // rings at once: weights and pass list are final.  Only the activation producer has to wait for gate_up.
+        pdl_trigger();
+    }
 
     const int tiles = (GU ? p.I : p.H) / TILE;
     const int units = p.meta[1] * tiles;
@@ -517,6 +524,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) stream_gemv_kernel(const __
         uint32_t ui = 0;
         int unit = blockIdx.x;
         int4 next = unit < units ? p.passes[unit / tiles] : make_int4(0, 0, 0, 0);
+        if (!GU) pdl_wait();  // the activations are the gate_up kernel's output
         for (; unit < units; unit += gridDim.x, ++ui) {
             const int4 pass = next;
             const int nu = unit + gridDim.x;

@@ -232,7 +232,6 @@ __global__ void __launch_bounds__(kRouterWarps * 32) router_fast_kernel(RouterPa
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int tok0 = blockIdx.y * TPB;
     pdl_trigger();
-    pdl_wait();
     const bool has_gate = p.shared_gate_weight != nullptr && p.shared_gate_out != nullptr;
     const int e = blockIdx.x * kRouterWarps + warp;
     const bool is_gate = has_gate && e == E;
@@ -249,16 +248,19 @@ __global__ void __launch_bounds__(kRouterWarps * 32) router_fast_kernel(RouterPa
                 if (tok0 + t < p.T) bytes += (uint32_t)H * 2;
         mbar_expect_tx(&bars[warp], bytes);
         if (active) {
+            // weights are constants: their copy starts while the kernel before this one is still draining
             const __nv_bfloat16* wrow = is_gate ? reinterpret_cast<const __nv_bfloat16*>(p.shared_gate_weight)
                                                 : reinterpret_cast<const __nv_bfloat16*>(p.router_weight) + (size_t)e * H;
             bulk_load(wrows + (size_t)warp * H, wrow, (uint32_t)H * 2, &bars[warp]);
         }
+        pdl_wait();           // the activations (and the tickets) may come from the kernel before
         if (XB)
             for (int t = warp; t < TPB; t += kRouterWarps)
                 if (tok0 + t < p.T)
                     bulk_load(xs_raw + (size_t)t * H * 2, reinterpret_cast<const __nv_bfloat16*>(p.hidden) + (size_t)(tok0 + t) * H,
                               (uint32_t)H * 2, &bars[warp]);
     }
+    pdl_wait();
     // activations -> fp32 in shared memory; norm gains next to them
     const int chunks = H / 8;
     for (int i = tid; i < (XB ? 0 : TPB * chunks); i += blockDim.x) {
@@ -399,6 +401,216 @@ static int launch_router_fast(const RouterParams& p, cudaStream_t stream) {
     return FK_OK;
 }
 
+// ---------------------------------------------------------------------------------------------
+// Tensor-core router for larger batches (bf16 activations and weights, H <= 2048, H % 256 == 0)
+// ---------------------------------------------------------------------------------------------
+// From a few dozen tokens on the CUDA-core router is bound by instruction issue (one FMA and one
+// unpack per product).  Here a block owns 16 tokens x 32 experts; its 8 warps split K, each running
+// m16n8k16 MMAs with the tokens as M and the experts as N, and the K-slices meet in shared memory.
+// The A operand is x * (offset + norm_weight), an fp32 value, split into three bf16 terms (8 + 8 + 8
+// mantissa bits: the split is exact), so the products are exact and only the fp32 accumulation
+// rounds, as in the CUDA-core kernels.  The shared gate g . x uses the raw bf16 activations (one MMA).
+// Rows sit 16 bytes further apart in shared memory than in HBM, so fragment loads hit 32 banks.
+constexpr int kRmTokens = 16;
+constexpr int kRmExperts = 32;
+constexpr int kRmWarps = 16;               // K slices per block
+
+__device__ __forceinline__ uint32_t rm_lds32(const unsigned char* ptr) {
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(smem_u32(ptr)));
+    return v;
+}
+__device__ __forceinline__ void rm_mma(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+// (x, y) -> three packed bf16 pairs whose sum is (x, y) exactly
+__device__ __forceinline__ void rm_split3(float x, float y, uint32_t& h, uint32_t& m, uint32_t& l) {
+    __nv_bfloat162 a = __floats2bfloat162_rn(x, y);
+    float2 af = __bfloat1622float2(a);
+    const float rx = x - af.x, ry = y - af.y;
+    __nv_bfloat162 b = __floats2bfloat162_rn(rx, ry);
+    float2 bf = __bfloat1622float2(b);
+    __nv_bfloat162 c = __floats2bfloat162_rn(rx - bf.x, ry - bf.y);
+    h = *reinterpret_cast<uint32_t*>(&a);
+    m = *reinterpret_cast<uint32_t*>(&b);
+    l = *reinterpret_cast<uint32_t*>(&c);
+}
+
+__global__ void __launch_bounds__(kRmWarps * 32, 1) router_mma_kernel(RouterParams p) {
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    const int H = p.H, E = p.E;
+    const int RS = H * 2 + 16;                                                        // padded row stride in bytes
+    unsigned char* xs = smem_raw;                                                     // [16][RS]  activations
+    unsigned char* ws = xs + (size_t)kRmTokens * RS;                                  // [33][RS]  expert rows (+ gate row)
+    float* gain = reinterpret_cast<float*>(ws + (size_t)(kRmExperts + 1) * RS);       // [H]
+    float* rstd = gain + H;                                                           // [16]
+    uint64_t* bar = reinterpret_cast<uint64_t*>(rstd + kRmTokens);
+    float* partial = reinterpret_cast<float*>(ws);                                    // [kRmWarps][16][33], after the MMAs
+    __shared__ int is_last;
+    __shared__ int abort_flag;
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int tok0 = blockIdx.y * kRmTokens, e0 = blockIdx.x * kRmExperts;
+    const int ntok = min(kRmTokens, p.T - tok0), nexp = min(kRmExperts, E - e0);
+    const bool with_gate = blockIdx.x == 0 && p.shared_gate_weight != nullptr && p.shared_gate_out != nullptr;
+    pdl_trigger();
+    if (tid == 0) {
+        abort_flag = 0;
+        mbar_init(bar, 1);
+        mbar_init_fence();
+        mbar_expect_tx(bar, (uint32_t)((ntok + nexp + (with_gate ? 1 : 0)) * H * 2));
+    }
+    __syncthreads();
+    // weights are constants: their copies start while the kernel before this one is still draining
+    if (warp == 1) {
+        if (lane < nexp)
+            bulk_load(ws + (size_t)lane * RS, reinterpret_cast<const __nv_bfloat16*>(p.router_weight) + (size_t)(e0 + lane) * H,
+                      (uint32_t)H * 2, bar);
+        if (lane == 0 && with_gate) bulk_load(ws + (size_t)kRmExperts * RS, p.shared_gate_weight, (uint32_t)H * 2, bar);
+    }
+    pdl_wait();
+    if (warp == 0 && lane < ntok)
+        bulk_load(xs + (size_t)lane * RS, reinterpret_cast<const __nv_bfloat16*>(p.hidden) + (size_t)(tok0 + lane) * H,
+                  (uint32_t)H * 2, bar);
+    for (int c = tid; c < H / 8; c += blockDim.x) {
+        const uint4 raw = *reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(p.norm_weight) + c * 8);
+        const float o = p.norm_offset;
+        float4* dst = reinterpret_cast<float4*>(gain + c * 8);
+        dst[0] = make_float4(o + bf16lo(raw.x), o + bf16hi(raw.x), o + bf16lo(raw.y), o + bf16hi(raw.y));
+        dst[1] = make_float4(o + bf16lo(raw.z), o + bf16hi(raw.z), o + bf16lo(raw.w), o + bf16hi(raw.w));
+    }
+    __syncthreads();
+    mbar_wait(bar, 0, &abort_flag);
+
+    // mean squares: two tokens per warp
+    for (int t = warp; t < kRmTokens; t += kRmWarps) {
+        float ss = 0.f;
+        if (t < ntok) {
+            for (int h = lane * 8; h < H; h += 256) {
+                const uint4 v = lds128(xs + (size_t)t * RS + (size_t)h * 2);
+                float f;
+                f = bf16lo(v.x); ss = fmaf(f, f, ss); f = bf16hi(v.x); ss = fmaf(f, f, ss);
+                f = bf16lo(v.y); ss = fmaf(f, f, ss); f = bf16hi(v.y); ss = fmaf(f, f, ss);
+                f = bf16lo(v.z); ss = fmaf(f, f, ss); f = bf16hi(v.z); ss = fmaf(f, f, ss);
+                f = bf16lo(v.w); ss = fmaf(f, f, ss); f = bf16hi(v.w); ss = fmaf(f, f, ss);
+            }
+        }
+        ss = warp_sum(ss);
+        if (lane == 0) rstd[t] = rsqrtf(ss / (float)H + p.eps);
+    }
+
+    // this warp's K slice: H/kRmWarps columns, 16 per MMA
+    const int gid = lane >> 2, tig = lane & 3;
+    const int ksteps = H / (16 * kRmWarps);
+    float acc[4][4], gacc[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        gacc[j] = 0.f;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) acc[j][q] = 0.f;
+    }
+    {
+        const int kbase = warp * (H / kRmWarps) + 2 * tig;
+        const unsigned char* xa = xs + (size_t)gid * RS + (size_t)kbase * 2;
+        const unsigned char* xb = xa + (size_t)8 * RS;
+        const unsigned char* wb = ws + (size_t)gid * RS + (size_t)kbase * 2;
+        const float* gp = gain + kbase;
+#pragma unroll 2
+        for (int ks = 0; ks < ksteps; ++ks) {
+            const uint32_t x00 = rm_lds32(xa + ks * 32), x01 = rm_lds32(xa + ks * 32 + 16);   // row gid:     k, k + 8
+            const uint32_t x10 = rm_lds32(xb + ks * 32), x11 = rm_lds32(xb + ks * 32 + 16);   // row gid + 8
+            const float2 g0 = *reinterpret_cast<const float2*>(gp + ks * 16);
+            const float2 g1 = *reinterpret_cast<const float2*>(gp + ks * 16 + 8);
+            uint32_t ah[4], am[4], al[4];
+            rm_split3(bf16lo(x00) * g0.x, bf16hi(x00) * g0.y, ah[0], am[0], al[0]);
+            rm_split3(bf16lo(x10) * g0.x, bf16hi(x10) * g0.y, ah[1], am[1], al[1]);
+            rm_split3(bf16lo(x01) * g1.x, bf16hi(x01) * g1.y, ah[2], am[2], al[2]);
+            rm_split3(bf16lo(x11) * g1.x, bf16hi(x11) * g1.y, ah[3], am[3], al[3]);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const unsigned char* wr = wb + (size_t)j * 8 * RS + ks * 32;
+                const uint32_t b0 = rm_lds32(wr), b1 = rm_lds32(wr + 16);
+                rm_mma(acc[j], ah[0], ah[1], ah[2], ah[3], b0, b1);
+                rm_mma(acc[j], am[0], am[1], am[2], am[3], b0, b1);
+                rm_mma(acc[j], al[0], al[1], al[2], al[3], b0, b1);
+            }
+            if (with_gate) {
+                // N column 0 is the gate row; the other seven columns read rows that do not exist: keep them zero
+                const unsigned char* wr = ws + (size_t)kRmExperts * RS + (size_t)kbase * 2 + ks * 32;
+                const uint32_t b0 = gid == 0 ? rm_lds32(wr) : 0u, b1 = gid == 0 ? rm_lds32(wr + 16) : 0u;
+                rm_mma(gacc, x00, x10, x01, x11, b0, b1);
+            }
+        }
+    }
+    __syncthreads();                       // every warp is done with the weight rows: their space takes the partial sums
+    {
+        float* pw = partial + (size_t)warp * kRmTokens * 33;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            pw[gid * 33 + j * 8 + 2 * tig] = acc[j][0];
+            pw[gid * 33 + j * 8 + 2 * tig + 1] = acc[j][1];
+            pw[(gid + 8) * 33 + j * 8 + 2 * tig] = acc[j][2];
+            pw[(gid + 8) * 33 + j * 8 + 2 * tig + 1] = acc[j][3];
+        }
+        if (with_gate && tig == 0) {
+            pw[gid * 33 + 32] = gacc[0];
+            pw[(gid + 8) * 33 + 32] = gacc[2];
+        }
+    }
+    __syncthreads();
+    for (int idx = tid; idx < kRmTokens * kRmExperts; idx += blockDim.x) {
+        const int t = idx >> 5, e = idx & 31;
+        float sum = 0.f;
+#pragma unroll
+        for (int w = 0; w < kRmWarps; ++w) sum += partial[(size_t)(w * kRmTokens + t) * 33 + e];
+        if (t < ntok && e < nexp) {
+            float logit = sum * rstd[t];
+            if (p.router_bias) logit += p.router_bias[e0 + e];
+            p.logits[(size_t)(tok0 + t) * E + e0 + e] = logit;
+        }
+    }
+    if (with_gate && tid < ntok) {
+        float sum = 0.f;
+#pragma unroll
+        for (int w = 0; w < kRmWarps; ++w) sum += partial[(size_t)(w * kRmTokens + tid) * 33 + 32];
+        p.shared_gate_out[tok0 + tid] = sigmoidf_(sum);
+    }
+
+    // ticket: the last expert-tile block of this token tile selects the top-k
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+        unsigned t = atomicAdd(p.tickets + blockIdx.y, 1u);
+        is_last = (t == gridDim.x - 1);
+        if (is_last) p.tickets[blockIdx.y] = 0u;    // re-arm for the next launch
+    }
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    for (int t = warp; t < ntok; t += kRmWarps) {
+        const int token = tok0 + t;
+        const float* row = p.logits + (size_t)token * E;
+        long long* ids = p.topk_ids + (size_t)token * p.top_k;
+        int* ids32 = p.ids32 ? p.ids32 + (size_t)token * p.top_k : nullptr;
+        float* wts = p.topk_weights + (size_t)token * p.top_k;
+        if (E <= 256) topk_warp<8>(row, E, p.top_k, ids, ids32, wts);
+        else topk_warp<32>(row, E, p.top_k, ids, ids32, wts);
+    }
+}
+
+static int launch_router_mma(const RouterParams& p, cudaStream_t stream) {
+    dim3 grid((p.E + kRmExperts - 1) / kRmExperts, (p.T + kRmTokens - 1) / kRmTokens);
+    const size_t rs = (size_t)p.H * 2 + 16;
+    const size_t smem = (kRmTokens + kRmExperts + 1) * rs + sizeof(float) * ((size_t)p.H + kRmTokens) + 16;
+    FK_CUDA_OK(cudaFuncSetAttribute(router_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), "router attr");
+    FK_CUDA_OK(launch_pdl(router_mma_kernel, grid, dim3(kRmWarps * 32), smem, stream, p), "router launch");
+    FK_LAUNCH_OK("router launch");
+    return FK_OK;
+}
+
 template <typename WT, int VW>
 static int launch_router_t(const RouterParams& p, cudaStream_t stream) {
     dim3 block(kRouterWarps * 32);
@@ -434,6 +646,10 @@ int launch_router(const RouterParams& p, int weight_dtype, cudaStream_t stream) 
                 // 32 bf16 tokens per block from 32 tokens up; small batches keep 4-token blocks for parallelism
                 // tokens per block grow with the batch so that the grid stays near two blocks per SM
                 if (p.hidden_dtype == FK_BF16) {
+                    static const int mma_from = getenv("FKMOE_ROUTER_MMA_FROM") ? atoi(getenv("FKMOE_ROUTER_MMA_FROM")) : 64;
+                    if (p.T >= mma_from && p.H <= 2048 && p.H % (16 * kRmWarps) == 0 &&
+                        (size_t)(kRmWarps * kRmTokens * 33) * sizeof(float) <= (size_t)33 * (p.H * 2 + 16))
+                        return launch_router_mma(p, stream);
                     if (p.T <= 32) return launch_router_fast<4, true>(p, stream);
                     if (p.T <= 64) return launch_router_fast<8, true>(p, stream);
                     if (p.T <= 128) return launch_router_fast<16, true>(p, stream);

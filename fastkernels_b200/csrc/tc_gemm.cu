@@ -27,8 +27,9 @@
 
 namespace fk {
 
-constexpr int kTcStages = 4;
-constexpr int kTcStagesGU = 5;
+constexpr int kTcStages = 8;              // down: 8 x 24 KB; enough bytes in flight per SM to cover the HBM latency
+constexpr int kTcStagesGU = 7;            // gate_up: 7 x 24 KB beside the 33 KB up-value exchange buffer
+constexpr int kTcStagesMax = kTcStages > kTcStagesGU ? kTcStages : kTcStagesGU;
 constexpr int kTcN = 64;                 // tokens per pass (MMA N, rounded up to 16)
 constexpr int kTcThreads = 192;
 constexpr int kTcTileBytes = 128 * 64 * 2;          // one 128-row x 64-column bf16 operand tile
@@ -37,8 +38,8 @@ constexpr int kTcTmemCols = 128;         // 2 accumulator buffers x 64 columns
 constexpr int kTcUStride = kTcN + 1;     // row stride (floats) of the up-value exchange buffer
 
 struct TcBarriers {
-    uint64_t full[kTcStagesGU];
-    uint64_t empty[kTcStagesGU];
+    uint64_t full[kTcStagesMax];
+    uint64_t empty[kTcStagesMax];
     uint64_t tfull[2];
     uint64_t tempty[2];
     uint32_t tmem_base;
@@ -91,8 +92,10 @@ tc_grouped_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constan
         // ------------------------------------------------------------------ TMA producer
         if (lane == 0) {
             uint32_t it = 0;
+            int4 next = (int)blockIdx.x < units ? p.passes[blockIdx.x / tiles] : make_int4(0, 0, 0, 0);
             for (int unit = blockIdx.x; unit < units; unit += gridDim.x) {
-                const int4 pass = p.passes[unit / tiles];
+                const int4 pass = next;                      // looked up one unit ahead: off the copy-issue path
+                if (unit + (int)gridDim.x < units) next = p.passes[(unit + gridDim.x) / tiles];
                 const int mt = unit % tiles;
                 const int npad = (pass.z + 15) & ~15;
                 const CUtensorMap* wm = pass.x < 0 ? &smap : &wmap;
