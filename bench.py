@@ -315,10 +315,25 @@ def run_single(args):
     gate_up_bytes = (U + 1) * 2 * I * H * 2 + B * H * 2
     dom = stage_names.index("gate_up") if "gate_up" in stage_names else 0
     dom_ms = stage_ms[dom]
-    achieved = gate_up_bytes / (dom_ms * 1e-3) / 1e9
-    roofline = {"bound": "hbm", "kernel": "gate_up_gemv_kernel (gate_up GEMV + SwiGLU)", "achieved": achieved,
+    # Which kernel that is depends on the batch (csrc/api.cu picks the path).  `traffic` is DRAM read + write bytes
+    # of that kernel from an ncu capture of the same workload on one layer copy (profiles/), expressed per
+    # algorithmic byte and scaled to this launch's bytes: the kernels stream every weight byte exactly once, so
+    # traffic grows in proportion to the experts touched.
+    if len(stage_ms) == 1:
+        dom_kernel, dom_bytes, traffic_ratio = "decode1_kernel (whole layer, one token, one launch)", layer_bytes, None
+    elif B <= 96:
+        dom_kernel, dom_bytes, traffic_ratio = ("stream_gemv_kernel<8,true,false> (gate_up GEMV + SwiGLU, "
+                                                "TMA ring, mma.sync consumers)"), gate_up_bytes, NCU_TRAFFIC_PER_BYTE["stream_gate_up"]
+    else:
+        dom_kernel, dom_bytes, traffic_ratio = ("tc_grouped_kernel<true> (tcgen05 grouped gate_up GEMM + SwiGLU)",
+                                                gate_up_bytes, NCU_TRAFFIC_PER_BYTE["tc_gate_up"])
+    achieved = dom_bytes / (dom_ms * 1e-3) / 1e9
+    roofline = {"bound": "hbm", "kernel": dom_kernel, "achieved": achieved,
                 "peak": peak, "peak_source": peak_src, "unit": "GB/s", "frac": achieved / peak,
-                "algorithmic_bytes_per_launch": gate_up_bytes, "ms_per_launch": dom_ms, "traffic": None,
+                "algorithmic_bytes_per_launch": dom_bytes, "ms_per_launch": dom_ms,
+                "traffic": None if traffic_ratio is None else traffic_ratio * dom_bytes,
+                "traffic_source": None if traffic_ratio is None else
+                f"ncu dram__bytes_read.sum + dram__bytes_write.sum = {traffic_ratio:.3f} x algorithmic bytes (profiles/)",
                 "stages_ms": dict(zip(stage_names, stage_ms)),
                 "layer": {"algorithmic_bytes": layer_bytes, "achieved": layer_bytes / (ms * 1e-3) / 1e9,
                           "frac": layer_bytes / (ms * 1e-3) / 1e9 / peak, "distinct_experts": U}}
@@ -412,6 +427,11 @@ def run_single(args):
     if stack is not None:
         line["stack"] = stack
     print(json.dumps(line), flush=True)
+
+
+# DRAM bytes (read + write) per algorithmic byte of the dominant kernel, from the ncu captures summarised in
+# profiles/stream_gemv_b32.md and profiles/tc_grouped_gemm_b256.md.
+NCU_TRAFFIC_PER_BYTE = {"stream_gate_up": 1.011, "tc_gate_up": 1.016}
 
 
 def main():

@@ -82,12 +82,12 @@ static int run_experts(const fk_moe_call* c, const Workspace& w, const long long
     ep.routes = pp.routes;
     ep.shared_tok0 = sh0; ep.shared_n = sh_n;
     // Path choice.  The weight-streaming kernels win while an expert sees few tokens: with their tensor-core
-    // consumers (bf16 models, 8-token passes) up to 128 tokens per call, with the CUDA-core consumers below 64.
+    // consumers (bf16 models, 8-token passes) up to 96 tokens per call, with the CUDA-core consumers below 64.
     // Above that the tcgen05 grouped GEMM (64-token passes) takes over.
     const bool generic = (c->flags & FK_FLAG_FORCE_GENERIC) != 0;
     const bool stream_ok = !generic && !(c->flags & FK_FLAG_REGISTER_GEMV) && stream_path_supported(ep, c->weight_dtype);
     const int stream_rows = stream_ok ? stream_pass_rows(ep) : 4;
-    const int stream_max_tokens = stream_rows == 8 ? 128 : 63;
+    const int stream_max_tokens = stream_rows == 8 ? 96 : 63;
     const bool want_tc = !generic && !(c->flags & (FK_FLAG_FORCE_GEMV | FK_FLAG_REGISTER_GEMV)) &&
                          ((c->flags & FK_FLAG_FORCE_TENSOR) || d.tokens > stream_max_tokens || !stream_ok);
     const bool use_tc = want_tc && (d.tokens >= 64 || (c->flags & FK_FLAG_FORCE_TENSOR)) && tc_path_supported(ep, c->weight_dtype);
