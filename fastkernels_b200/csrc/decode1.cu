@@ -12,7 +12,7 @@
 // Work is split evenly by bytes: every block streams the same share of every matrix.
 //
 // A producer warp issues bulk copies (one weight row or gate/up pair per 8 KB stage) into a
-// 24-stage shared-memory ring and runs ahead across the barriers: phase C addresses depend only on
+// 16-stage shared-memory ring and runs ahead across the barriers: phase C addresses depend only on
 // the expert ids, so those rows are already in flight while the blocks wait at barrier 2.  Eight
 // consumer warps take the stages round-robin; a stage is handled by one warp (16-byte shared loads,
 // the token's activations in registers, shuffle reduction), so consumers never synchronise with
@@ -31,7 +31,7 @@
 
 namespace fk {
 
-constexpr int kD1Stages = 24;
+constexpr int kD1Stages = 16;
 constexpr int kD1StageBytes = 8192;
 constexpr int kD1Consumers = 8;                  // warps
 // Stage `it` lives in slot it % kD1Stages and is consumed by warp it % kD1Consumers.  The slot count must be a
@@ -48,6 +48,9 @@ struct D1Smem {
     uint64_t full[kD1Stages];
     uint64_t empty[kD1Stages];
     uint64_t ids_ready;
+    uint64_t xready;                              // the token's activations and the norm weights are in shared memory
+    uint64_t staged_a;                            // logits and shared activations of all blocks are in shared memory
+    uint64_t staged_b;                            // routed activations of all blocks are in shared memory
     int4 desc[kD1Stages];                         // what each stage holds (written by the producer)
     float dpart[FK_MAX_TOP_K][kD1MaxRows];       // un-weighted down outputs per slot
     float ysh[kD1MaxRows];                       // shared-expert down outputs
@@ -133,6 +136,10 @@ __device__ __forceinline__ unsigned ld_acquire_u32(const unsigned* p) {
     asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
     return v;
 }
+
+// Orders this thread's earlier generic-proxy accesses (and what it has acquired from other threads) before its
+// later bulk copies, which read and write memory through the async proxy.
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async;" ::: "memory"); }
 
 // Bounded spin until *word >= target; false on time-out.
 __device__ __forceinline__ bool spin_until(const unsigned* word, unsigned target, volatile int* abort_flag) {
@@ -254,15 +261,15 @@ __device__ __forceinline__ void select_warp(const float* probs, int E, int top_k
     }
 }
 
-// Block-wide softmax, then top-k by one warp (threads = cthreads consumer threads, E <= 1024).
+// Block-wide softmax over the logits in `probs` (shared memory), then top-k by one warp (threads = cthreads
+// consumer threads, E <= 1024).
 // Every thread owns the experts e = ctid, ctid + cthreads, ... for the softmax.
 // Writes ids/weights to shared memory (and to global memory from block 0).
 __device__ __forceinline__ void block_topk(const DecodeParams& p, D1Smem& s, float* probs, int ctid, int cthreads, bool write_global) {
     const int E = p.E, lane = ctid & 31, w = ctid >> 5;
     float m = -INFINITY;
     for (int e = ctid; e < E; e += cthreads) {
-        const float l = __ldcg(p.logits + e);
-        probs[e] = l;
+        const float l = probs[e];                 // the logits were bulk-copied here
         m = fmaxf(m, l);
     }
     m = warp_max(m);
@@ -308,6 +315,8 @@ __global__ void __launch_bounds__(kD1Threads, 1) decode1_kernel(DecodeParams p) 
     float* ract_s = reinterpret_cast<float*>(smem_raw + sizeof(D1Smem));          // [top_k][I]; softmax scratch before
     float* sact_s = ract_s + (size_t)FK_MAX_TOP_K * p.I;                          // [I]
     float* xg_s = sact_s + p.I;                                                   // [H]  x * (offset + norm_weight)
+    unsigned char* xraw_s = reinterpret_cast<unsigned char*>(xg_s + p.H);         // [H] activations as stored (<= 4 bytes each)
+    unsigned char* nw_s = xraw_s + (size_t)p.H * 4;                               // [H] bf16 norm weights
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int G = gridDim.x, blk = blockIdx.x;
     const int H = p.H, I = p.I;
@@ -323,32 +332,20 @@ __global__ void __launch_bounds__(kD1Threads, 1) decode1_kernel(DecodeParams p) 
         }
         if (lane == 0) {
             mbar_init(&s.ids_ready, 1);
+            mbar_init(&s.xready, 1);
+            mbar_init(&s.staged_a, 1);
+            mbar_init(&s.staged_b, 1);
             s.abort_flag = 0;
         }
         mbar_init_fence();
         __syncwarp();
-    }
-
-    // the token's activations: issue these loads before anything else (the first global access of a
-    // block pays the longest latency of the whole kernel)
-    float x[8][8];
-    if (warp < kD1Consumers) {
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            if (j < nchH) {
-                const size_t el = (size_t)j * 256 + lane * 8;
-                if (p.hidden_dtype == FK_BF16) {
-                    uint4 v = *reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(p.hidden) + el);
-                    x[j][0] = bf16lo(v.x); x[j][1] = bf16hi(v.x); x[j][2] = bf16lo(v.y); x[j][3] = bf16hi(v.y);
-                    x[j][4] = bf16lo(v.z); x[j][5] = bf16hi(v.z); x[j][6] = bf16lo(v.w); x[j][7] = bf16hi(v.w);
-                } else {
-#pragma unroll
-                    for (int i = 0; i < 8; ++i) x[j][i] = load_any(p.hidden, p.hidden_dtype, el + i);
-                }
-            } else {
-#pragma unroll
-                for (int i = 0; i < 8; ++i) x[j][i] = 0.f;
-            }
+        // One copy of the token and of the norm weights per block.  (Plain loads by every consumer warp of
+        // every block all hit the same few L2 lines and took 4 us to come back.)
+        if (lane == 0) {
+            const uint32_t xb = (uint32_t)H * (p.hidden_dtype == FK_F32 ? 4u : 2u);
+            mbar_expect_tx(&s.xready, xb + (uint32_t)H * 2u);
+            bulk_load(xraw_s, p.hidden, xb, &s.xready);
+            bulk_load(nw_s, p.norm_weight, (uint32_t)H * 2u, &s.xready);
         }
     }
 
@@ -366,7 +363,7 @@ __global__ void __launch_bounds__(kD1Threads, 1) decode1_kernel(DecodeParams p) 
         // ------------------------------------------------------------------ producer warp
         // Lane l owns ring slot l: the lanes decode and issue up to kD1Stages stages side by side, so the
         // issue rate does not depend on one thread's instruction latency.
-        auto issue = [&](int it) {
+        auto issue = [&](int it, bool wait) {
             const D1Stage st = decode_stage(pl, p, it, blk, G);
             const int slot = it % kD1Stages;
             const uint32_t par = (it / kD1Stages) & 1u;
@@ -386,7 +383,7 @@ __global__ void __launch_bounds__(kD1Threads, 1) decode1_kernel(DecodeParams p) 
                     src0 = down + ((size_t)s.ids[st.a] * H + pl.h0 + st.b) * I; bytes0 = st.c * I * 2; break;
                 default: break;
             }
-            mbar_wait(&s.empty[slot], par ^ 1u, &s.abort_flag);
+            if (wait) mbar_wait(&s.empty[slot], par ^ 1u, &s.abort_flag);
             s.desc[slot] = make_int4(st.kind, st.a, st.b, st.c);
             mbar_expect_tx(&s.full[slot], bytes0 + bytes1);
             bulk_load(s.stage[slot], src0, bytes0, &s.full[slot]);
@@ -394,7 +391,7 @@ __global__ void __launch_bounds__(kD1Threads, 1) decode1_kernel(DecodeParams p) 
         };
         for (int base = 0; base < nA; base += kD1Stages) {            // phase A: static addresses
             const int it = base + lane;
-            if (lane < kD1Stages && it < nA) issue(it);
+            if (lane < kD1Stages && it < nA) issue(it, true);
         }
         __syncwarp();
         __syncthreads();                                               // the consumers may use the barriers from here on
@@ -404,12 +401,42 @@ __global__ void __launch_bounds__(kD1Threads, 1) decode1_kernel(DecodeParams p) 
         // phases B and C: addresses depend on the ids only, so C is issued as soon as ring slots free up
         for (int base = (nA / kD1Stages) * kD1Stages; base < total; base += kD1Stages) {
             const int it = base + lane;
-            if (lane < kD1Stages && it >= nA && it < total) issue(it);
+            if (lane < kD1Stages && it >= nA && it < total) issue(it, true);
         }
     } else {
         // ------------------------------------------------------------------ consumer warps
         __syncthreads();                                               // ring barriers initialised by the producer warp
         const int cthreads = kD1Consumers * 32;
+        mbar_wait(&s.xready, 0, &s.abort_flag);
+        // the token's activations, 8 consecutive columns of every 256-column chunk per lane
+        float x[8][8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            if (j < nchH) {
+                const size_t el = (size_t)j * 256 + lane * 8;
+                if (p.hidden_dtype == FK_BF16) {
+                    const uint4 v = lds128(xraw_s + el * 2);
+                    x[j][0] = bf16lo(v.x); x[j][1] = bf16hi(v.x); x[j][2] = bf16lo(v.y); x[j][3] = bf16hi(v.y);
+                    x[j][4] = bf16lo(v.z); x[j][5] = bf16hi(v.z); x[j][6] = bf16lo(v.w); x[j][7] = bf16hi(v.w);
+                } else if (p.hidden_dtype == FK_F32) {
+                    const uint4 a = lds128(xraw_s + el * 4), b = lds128(xraw_s + el * 4 + 16);
+                    x[j][0] = __uint_as_float(a.x); x[j][1] = __uint_as_float(a.y); x[j][2] = __uint_as_float(a.z); x[j][3] = __uint_as_float(a.w);
+                    x[j][4] = __uint_as_float(b.x); x[j][5] = __uint_as_float(b.y); x[j][6] = __uint_as_float(b.z); x[j][7] = __uint_as_float(b.w);
+                } else {
+                    const uint4 v = lds128(xraw_s + el * 2);
+                    const __half2* h = reinterpret_cast<const __half2*>(&v);
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const float2 f = __half22float2(h[i]);
+                        x[j][2 * i] = f.x; x[j][2 * i + 1] = f.y;
+                    }
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) x[j][i] = 0.f;
+            }
+        }
+
         float ss = 0.f;
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
@@ -424,7 +451,7 @@ __global__ void __launch_bounds__(kD1Threads, 1) decode1_kernel(DecodeParams p) 
             for (int j = 0; j < 8; ++j) {
                 if (j < nchH) {
                     const int c = j * 256 + lane * 8;
-                    const uint4 g = *reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(p.norm_weight) + c);
+                    const uint4 g = lds128(nw_s + (size_t)c * 2);
                     const float o = p.norm_offset;
                     float4 lo = make_float4(x[j][0] * (o + bf16lo(g.x)), x[j][1] * (o + bf16hi(g.x)),
                                             x[j][2] * (o + bf16lo(g.y)), x[j][3] * (o + bf16hi(g.y)));
@@ -453,14 +480,20 @@ __global__ void __launch_bounds__(kD1Threads, 1) decode1_kernel(DecodeParams p) 
                         D1_TRACE(1);
                         spin_until(p.bar + 0, (unsigned)G, &s.abort_flag);
                         D1_TRACE(3);
+                        // What the other blocks published is fetched by ONE bulk copy per block.  (Plain loads by
+                        // every thread of every block pile thousands of requests onto a handful of L2 lines.)
+                        fence_proxy_async();
+                        const uint32_t sb = p.shared_gate_up ? (uint32_t)I * 4u : 0u;
+                        mbar_expect_tx(&s.staged_a, (uint32_t)p.E * 4u + sb);
+                        bulk_load(ract_s, p.logits, (uint32_t)p.E * 4u, &s.staged_a);
+                        if (sb) bulk_load(sact_s, p.sact, sb, &s.staged_a);
                     }
+                    if (!p.shared_gate_up && tid < I / 4) reinterpret_cast<float4*>(sact_s)[tid] = make_float4(0.f, 0.f, 0.f, 0.f);
                     named_bar_sync(1, cthreads);
+                    mbar_wait(&s.staged_a, 0, &s.abort_flag);
                     block_topk(p, s, ract_s, tid, cthreads, blk == 0);
                     if (tid == 0) mbar_arrive(&s.ids_ready);
-                    if (tid < I / 4) {
-                        const float4 v = p.shared_gate_up ? __ldcg(reinterpret_cast<const float4*>(p.sact) + tid) : make_float4(0.f, 0.f, 0.f, 0.f);
-                        reinterpret_cast<float4*>(sact_s)[tid] = v;
-                    }
+                    fence_proxy_async();              // the softmax scratch is overwritten by a bulk copy later
                     named_bar_sync(1, cthreads);
                 } else if (phase == 1) {
                     // publish the routed activations, wait for every block's, stage them in shared memory
@@ -471,21 +504,13 @@ __global__ void __launch_bounds__(kD1Threads, 1) decode1_kernel(DecodeParams p) 
                         D1_TRACE(5);
                         spin_until(p.bar + 1, (unsigned)G, &s.abort_flag);
                         D1_TRACE(6);
+                        fence_proxy_async();
+                        const uint32_t rb = (uint32_t)(p.top_k * I) * 4u;
+                        mbar_expect_tx(&s.staged_b, rb);
+                        bulk_load(ract_s, p.ract, rb, &s.staged_b);
                     }
                     named_bar_sync(1, cthreads);
-                    const int n4 = p.top_k * I / 4;
-                    float4 tmp[4];
-#pragma unroll
-                    for (int q = 0; q < 4; ++q) {
-                        const int i = tid + q * cthreads;
-                        tmp[q] = i < n4 ? __ldcg(reinterpret_cast<const float4*>(p.ract) + i) : make_float4(0.f, 0.f, 0.f, 0.f);
-                    }
-#pragma unroll
-                    for (int q = 0; q < 4; ++q) {
-                        const int i = tid + q * cthreads;
-                        if (i < n4) reinterpret_cast<float4*>(ract_s)[i] = tmp[q];
-                    }
-                    named_bar_sync(1, cthreads);
+                    mbar_wait(&s.staged_b, 0, &s.abort_flag);
                 } else {
                     break;
                 }
@@ -575,12 +600,14 @@ bool decode1_supported(const DecodeParams& p, int weight_dtype) {
     uintptr_t bits = reinterpret_cast<uintptr_t>(p.hidden) | reinterpret_cast<uintptr_t>(p.norm_weight) |
                      reinterpret_cast<uintptr_t>(p.router_weight) | reinterpret_cast<uintptr_t>(p.gate_up) |
                      reinterpret_cast<uintptr_t>(p.down) | reinterpret_cast<uintptr_t>(p.shared_gate_up) |
-                     reinterpret_cast<uintptr_t>(p.shared_down) | reinterpret_cast<uintptr_t>(p.shared_gate);
+                     reinterpret_cast<uintptr_t>(p.shared_down) | reinterpret_cast<uintptr_t>(p.shared_gate) |
+                     reinterpret_cast<uintptr_t>(p.logits);
+    if (p.E % 4 != 0) return false;            // the logits travel as one bulk copy
     return (bits & 15) == 0;
 }
 
 int launch_decode1(const DecodeParams& p, cudaStream_t stream) {
-    const int smem = (int)(sizeof(D1Smem) + sizeof(float) * ((size_t)(FK_MAX_TOP_K + 1) * p.I + p.H) + 128);
+    const int smem = (int)(sizeof(D1Smem) + sizeof(float) * ((size_t)(FK_MAX_TOP_K + 1) * p.I + p.H) + (size_t)p.H * 6 + 128);
     FK_CUDA_OK(cudaFuncSetAttribute(decode1_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem), "decode1 attr");
     DecodeParams copy = p;
     void* args[] = {&copy};
