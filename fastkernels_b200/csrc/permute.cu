@@ -1,6 +1,6 @@
 // Expert histogram, exclusive offsets and the stable expert-major permutation of the T*k routes.
 //
-// One block of 32 warps.  Each warp owns a contiguous segment of the flattened id array; a
+// One block of 8 warps (few routes) or 32 warps.  Each warp owns a contiguous segment of the flattened id array; a
 // per-warp histogram in shared memory turns into per-warp base offsets, so rows land in
 // flat-index order inside every expert group (order == argsort(ids.flatten(), stable)).
 // Oracle: reference_expert_histogram (src/fastkernels/reference/moe.py:24-30) for the counts;
@@ -26,17 +26,18 @@ __device__ __forceinline__ int local_expert(const PermuteParams& p, int r) {
 __global__ void __launch_bounds__(kPermWarps * 32) permute_kernel(PermuteParams p) {
     extern __shared__ int sm[];
     const int E = p.E, R = p.routes;
-    int* whist = sm;                       // [kPermWarps][E]
-    int* offs = sm + kPermWarps * E;       // [E+1]
+    const int NW = blockDim.x >> 5;        // warps in this launch (8 or kPermWarps)
+    int* whist = sm;                       // [NW][E]
+    int* offs = sm + NW * E;               // [E+1]
     __shared__ int warp_cnt[kPermWarps], warp_flag[kPermWarps];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
 
     pdl_trigger();
-    for (int i = tid; i < kPermWarps * E; i += blockDim.x) whist[i] = 0;
+    for (int i = tid; i < NW * E; i += blockDim.x) whist[i] = 0;
     pdl_wait();               // the ids come from the router
     __syncthreads();
 
-    const int seg = (R + kPermWarps - 1) / kPermWarps;
+    const int seg = (R + NW - 1) / NW;
     const int seg_lo = min(R, warp * seg), seg_hi = min(R, seg_lo + seg);
     for (int base = seg_lo; base < seg_hi; base += 32) {
         int r = base + lane;
@@ -52,7 +53,7 @@ __global__ void __launch_bounds__(kPermWarps * 32) permute_kernel(PermuteParams 
         const int e = tid;
         int c = 0;
         if (e < E) {
-            for (int w = 0; w < kPermWarps; ++w) {
+            for (int w = 0; w < NW; ++w) {
                 int v = whist[w * E + e];
                 whist[w * E + e] = c;
                 c += v;
@@ -132,9 +133,12 @@ __global__ void __launch_bounds__(kPermWarps * 32) permute_kernel(PermuteParams 
 
 int launch_permute(const PermuteParams& p, cudaStream_t stream) {
     if (p.E < 1 || p.E > FK_MAX_EXPERTS || p.routes < 0) return FK_ERR_ARG;
-    size_t smem = sizeof(int) * ((size_t)kPermWarps * p.E + p.E + 2);
-    FK_CUDA_OK(cudaFuncSetAttribute(permute_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), "permute attr");
-    FK_CUDA_OK(launch_pdl(permute_kernel, dim3(1), dim3(kPermWarps * 32), smem, stream, p), "permute launch");
+    // a short dependency chain matters more than width while there are few routes; E must fit the block
+    const int warps = (p.routes <= 768 && p.E <= 256) ? 8 : kPermWarps;
+    size_t smem = sizeof(int) * ((size_t)warps * p.E + p.E + 2);
+    FK_CUDA_OK(cudaFuncSetAttribute(permute_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    (int)(sizeof(int) * ((size_t)kPermWarps * p.E + p.E + 2))), "permute attr");
+    FK_CUDA_OK(launch_pdl(permute_kernel, dim3(1), dim3(warps * 32), smem, stream, p), "permute launch");
     FK_LAUNCH_OK("permute launch");
     return FK_OK;
 }

@@ -226,6 +226,7 @@ __global__ void __launch_bounds__(kRouterWarps * 32) router_fast_kernel(RouterPa
     float* gain = reinterpret_cast<float*>(xs_raw + (size_t)TPB * H * XE);            // [H]
     float* rstd = gain + H;                                                           // [TPB]
     uint64_t* bars = reinterpret_cast<uint64_t*>(rstd + TPB + (TPB & 1));             // [8]
+    unsigned char* nwraw = reinterpret_cast<unsigned char*>(bars + kRouterWarps);     // [H] bf16 norm weights as stored
     __shared__ int is_last;
     __shared__ int abort_flag;
 
@@ -243,6 +244,7 @@ __global__ void __launch_bounds__(kRouterWarps * 32) router_fast_kernel(RouterPa
         mbar_init(&bars[warp], 1);
         mbar_init_fence();
         uint32_t bytes = active ? (uint32_t)H * 2 : 0u;
+        if (warp == 0) bytes += (uint32_t)H * 2;     // the norm weights ride on warp 0's barrier
         if (XB)
             for (int t = warp; t < TPB; t += kRouterWarps)
                 if (tok0 + t < p.T) bytes += (uint32_t)H * 2;
@@ -253,6 +255,8 @@ __global__ void __launch_bounds__(kRouterWarps * 32) router_fast_kernel(RouterPa
                                                 : reinterpret_cast<const __nv_bfloat16*>(p.router_weight) + (size_t)e * H;
             bulk_load(wrows + (size_t)warp * H, wrow, (uint32_t)H * 2, &bars[warp]);
         }
+        // one copy per block: per-thread loads of the same 4 KB from hundreds of blocks queue up on a few L2 lines
+        if (warp == 0) bulk_load(nwraw, p.norm_weight, (uint32_t)H * 2, &bars[0]);
         pdl_wait();           // the activations (and the tickets) may come from the kernel before
         if (XB)
             for (int t = warp; t < TPB; t += kRouterWarps)
@@ -284,14 +288,15 @@ __global__ void __launch_bounds__(kRouterWarps * 32) router_fast_kernel(RouterPa
         dst[0] = make_float4(v[0], v[1], v[2], v[3]);
         dst[1] = make_float4(v[4], v[5], v[6], v[7]);
     }
+    __syncthreads();
+    mbar_wait(&bars[0], 0, &abort_flag);                // norm weights (and warp 0's rows)
     for (int c = tid; c < chunks; c += blockDim.x) {
-        const uint4 raw = *reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(p.norm_weight) + c * 8);
+        const uint4 raw = lds128(nwraw + (size_t)c * 16);
         const float o = p.norm_offset;
         float4* dst = reinterpret_cast<float4*>(gain + c * 8);
         dst[0] = make_float4(o + bf16lo(raw.x), o + bf16hi(raw.x), o + bf16lo(raw.y), o + bf16hi(raw.y));
         dst[1] = make_float4(o + bf16lo(raw.z), o + bf16hi(raw.z), o + bf16lo(raw.w), o + bf16hi(raw.w));
     }
-    __syncthreads();
     if (XB) mbar_wait(&bars[warp], 0, &abort_flag);     // this warp's rows (and its weight row) have landed
     for (int t = warp; t < TPB; t += kRouterWarps) {
         float ss = 0.f;
@@ -393,7 +398,7 @@ template <int TPB, bool XB>
 static int launch_router_fast(const RouterParams& p, cudaStream_t stream) {
     const int gate = (p.shared_gate_weight && p.shared_gate_out) ? 1 : 0;
     dim3 grid((p.E + gate + kRouterWarps - 1) / kRouterWarps, (p.T + TPB - 1) / TPB);
-    const size_t smem = (size_t)kRouterWarps * p.H * 2 + (size_t)TPB * p.H * (XB ? 2 : 4) + sizeof(float) * ((size_t)p.H + TPB + 2) + 8 * sizeof(uint64_t) + 16;
+    const size_t smem = (size_t)kRouterWarps * p.H * 2 + (size_t)TPB * p.H * (XB ? 2 : 4) + sizeof(float) * ((size_t)p.H + TPB + 2) + 8 * sizeof(uint64_t) + (size_t)p.H * 2 + 16;
     auto kern = router_fast_kernel<TPB, XB>;
     FK_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), "router attr");
     FK_CUDA_OK(launch_pdl(kern, grid, dim3(kRouterWarps * 32), smem, stream, p), "router launch");
@@ -448,6 +453,7 @@ __global__ void __launch_bounds__(kRmWarps * 32, 1) router_mma_kernel(RouterPara
     float* gain = reinterpret_cast<float*>(ws + (size_t)(kRmExperts + 1) * RS);       // [H]
     float* rstd = gain + H;                                                           // [16]
     uint64_t* bar = reinterpret_cast<uint64_t*>(rstd + kRmTokens);
+    unsigned char* nwraw = reinterpret_cast<unsigned char*>(bar + 2);                 // [H] bf16 norm weights as stored
     float* partial = reinterpret_cast<float*>(ws);                                    // [kRmWarps][16][33], after the MMAs
     __shared__ int is_last;
     __shared__ int abort_flag;
@@ -461,7 +467,7 @@ __global__ void __launch_bounds__(kRmWarps * 32, 1) router_mma_kernel(RouterPara
         abort_flag = 0;
         mbar_init(bar, 1);
         mbar_init_fence();
-        mbar_expect_tx(bar, (uint32_t)((ntok + nexp + (with_gate ? 1 : 0)) * H * 2));
+        mbar_expect_tx(bar, (uint32_t)((ntok + nexp + (with_gate ? 1 : 0) + 1) * H * 2));
     }
     __syncthreads();
     // weights are constants: their copies start while the kernel before this one is still draining
@@ -470,20 +476,21 @@ __global__ void __launch_bounds__(kRmWarps * 32, 1) router_mma_kernel(RouterPara
             bulk_load(ws + (size_t)lane * RS, reinterpret_cast<const __nv_bfloat16*>(p.router_weight) + (size_t)(e0 + lane) * H,
                       (uint32_t)H * 2, bar);
         if (lane == 0 && with_gate) bulk_load(ws + (size_t)kRmExperts * RS, p.shared_gate_weight, (uint32_t)H * 2, bar);
+        if (lane == 1) bulk_load(nwraw, p.norm_weight, (uint32_t)H * 2, bar);
     }
     pdl_wait();
     if (warp == 0 && lane < ntok)
         bulk_load(xs + (size_t)lane * RS, reinterpret_cast<const __nv_bfloat16*>(p.hidden) + (size_t)(tok0 + lane) * H,
                   (uint32_t)H * 2, bar);
+    mbar_wait(bar, 0, &abort_flag);
     for (int c = tid; c < H / 8; c += blockDim.x) {
-        const uint4 raw = *reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(p.norm_weight) + c * 8);
+        const uint4 raw = lds128(nwraw + (size_t)c * 16);
         const float o = p.norm_offset;
         float4* dst = reinterpret_cast<float4*>(gain + c * 8);
         dst[0] = make_float4(o + bf16lo(raw.x), o + bf16hi(raw.x), o + bf16lo(raw.y), o + bf16hi(raw.y));
         dst[1] = make_float4(o + bf16lo(raw.z), o + bf16hi(raw.z), o + bf16lo(raw.w), o + bf16hi(raw.w));
     }
     __syncthreads();
-    mbar_wait(bar, 0, &abort_flag);
 
     // mean squares: two tokens per warp
     for (int t = warp; t < kRmTokens; t += kRmWarps) {
@@ -604,7 +611,7 @@ __global__ void __launch_bounds__(kRmWarps * 32, 1) router_mma_kernel(RouterPara
 static int launch_router_mma(const RouterParams& p, cudaStream_t stream) {
     dim3 grid((p.E + kRmExperts - 1) / kRmExperts, (p.T + kRmTokens - 1) / kRmTokens);
     const size_t rs = (size_t)p.H * 2 + 16;
-    const size_t smem = (kRmTokens + kRmExperts + 1) * rs + sizeof(float) * ((size_t)p.H + kRmTokens) + 16;
+    const size_t smem = (kRmTokens + kRmExperts + 1) * rs + sizeof(float) * ((size_t)p.H + kRmTokens) + 16 + (size_t)p.H * 2;
     FK_CUDA_OK(cudaFuncSetAttribute(router_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), "router attr");
     FK_CUDA_OK(launch_pdl(router_mma_kernel, grid, dim3(kRmWarps * 32), smem, stream, p), "router launch");
     FK_LAUNCH_OK("router launch");
