@@ -127,7 +127,57 @@ int launch_experts_generic(const ExpertParams& p, int weight_dtype, cudaStream_t
 // ---------------------------------------------------------------------------------------------
 // Ordered combine
 // ---------------------------------------------------------------------------------------------
-__global__ void combine_kernel(ExpertParams p) {
+// One thread per token and four output columns: the positions and weights of all slots are fetched first, then
+// all rows, so the kernel is two dependent memory round trips deep whatever top_k is.  Slots are summed in order.
+__global__ void __launch_bounds__(256) combine_kernel(ExpertParams p) {
+    pdl_trigger();
+    pdl_wait();
+    const int H4 = p.H >> 2;
+    const long long total = (long long)p.T * H4;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const int t = (int)(i / H4), h = (int)(i - (long long)t * H4) * 4;
+        int pos[FK_MAX_TOP_K];
+        float w[FK_MAX_TOP_K];
+#pragma unroll
+        for (int s = 0; s < FK_MAX_TOP_K; ++s) {
+            pos[s] = s < p.top_k ? p.inv[t * p.top_k + s] : -1;
+            w[s] = s < p.top_k ? p.topk_weights[t * p.top_k + s] : 0.f;
+        }
+        const bool shared = p.shared_down && t >= p.shared_tok0 && t < p.shared_tok0 + p.shared_n;
+        float4 v[FK_MAX_TOP_K], sh = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int s = 0; s < FK_MAX_TOP_K; ++s)
+            v[s] = pos[s] >= 0 ? *reinterpret_cast<const float4*>(p.y + (size_t)pos[s] * p.H + h) : make_float4(0.f, 0.f, 0.f, 0.f);
+        float gate = 1.f;
+        if (shared) {
+            sh = *reinterpret_cast<const float4*>(p.y + (size_t)(p.routes + t - p.shared_tok0) * p.H + h);
+            if (p.shared_gate) gate = p.shared_gate[t];
+        }
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int s = 0; s < FK_MAX_TOP_K; ++s) {
+            if (pos[s] >= 0) {
+                acc.x = fmaf(w[s], v[s].x, acc.x); acc.y = fmaf(w[s], v[s].y, acc.y);
+                acc.z = fmaf(w[s], v[s].z, acc.z); acc.w = fmaf(w[s], v[s].w, acc.w);
+            }
+        }
+        if (shared) {
+            if (p.shared_gate) { acc.x += gate * sh.x; acc.y += gate * sh.y; acc.z += gate * sh.z; acc.w += gate * sh.w; }
+            else { acc.x += sh.x; acc.y += sh.y; acc.z += sh.z; acc.w += sh.w; }
+        }
+        *reinterpret_cast<float4*>(p.out + (size_t)t * p.H + h) = acc;
+        if (p.layer_hidden) {
+            const size_t o = (size_t)t * p.H + h;
+            float4 r;
+            r.x = load_any(p.hidden, p.hidden_dtype, o) + acc.x; r.y = load_any(p.hidden, p.hidden_dtype, o + 1) + acc.y;
+            r.z = load_any(p.hidden, p.hidden_dtype, o + 2) + acc.z; r.w = load_any(p.hidden, p.hidden_dtype, o + 3) + acc.w;
+            *reinterpret_cast<float4*>(p.layer_hidden + o) = r;
+        }
+    }
+}
+
+// any H, any alignment
+__global__ void combine_scalar_kernel(ExpertParams p) {
     pdl_trigger();
     pdl_wait();
     const long long total = (long long)p.T * p.H;
@@ -149,10 +199,13 @@ __global__ void combine_kernel(ExpertParams p) {
 
 int launch_combine(const ExpertParams& p, cudaStream_t stream) {
     if (p.T <= 0) return FK_OK;
-    long long total = (long long)p.T * p.H;
+    const bool vec = p.H % 4 == 0 && p.top_k <= FK_MAX_TOP_K &&
+                     ((reinterpret_cast<uintptr_t>(p.out) | reinterpret_cast<uintptr_t>(p.y) | reinterpret_cast<uintptr_t>(p.layer_hidden)) & 15) == 0;
+    long long total = (long long)p.T * (vec ? p.H / 4 : p.H);
     int blocks = (int)((total + 255) / 256);
     if (blocks > 148 * 8) blocks = 148 * 8;
-    FK_CUDA_OK(launch_pdl(combine_kernel, dim3(blocks), dim3(256), 0, stream, p), "combine launch");
+    if (vec) FK_CUDA_OK(launch_pdl(combine_kernel, dim3(blocks), dim3(256), 0, stream, p), "combine launch");
+    else FK_CUDA_OK(launch_pdl(combine_scalar_kernel, dim3(blocks), dim3(256), 0, stream, p), "combine launch");
     FK_LAUNCH_OK("combine launch");
     return FK_OK;
 }

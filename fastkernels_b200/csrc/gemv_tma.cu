@@ -57,6 +57,7 @@ struct StreamSmem {
     uint64_t xfull[kXSlots];
     uint64_t xempty[kXSlots];
     int abort_flag;
+    int units;                               // passes x tiles, fetched once per block
 };
 
 template <int V> struct Lg2 { static constexpr int value = 1 + Lg2<V / 2>::value; };
@@ -457,9 +458,12 @@ __global__ void __launch_bounds__(kStreamThreads, 1) stream_gemv_kernel(const __
         s.abort_flag = 0;
         mbar_init_fence();
     }
+    if (GU) pdl_wait();       // pass list and packed order come from the permutation kernel
+    // one thread fetches the pass count for the block (a load by every warp of every block queues thousands of
+    // requests on one L2 line)
+    if (tid == 0) s.units = p.meta[1] * ((GU ? p.I : p.H) / TILE);
     __syncthreads();
     if (GU) {
-        pdl_wait();           // pass list and packed order come from the permutation kernel
         pdl_trigger();        // only now: the down kernel reads the pass list without waiting (below)
     } else {
         // The down kernel is released while the gate_up kernel still runs (which has itself waited for the
@@ -469,7 +473,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) stream_gemv_kernel(const __
     }
 
     const int tiles = (GU ? p.I : p.H) / TILE;
-    const int units = p.meta[1] * tiles;
+    const int units = s.units;
     const int xdtype = GU ? p.hidden_dtype : FK_F32;
     const int xrow_bytes = K * elem_bytes(xdtype);
 

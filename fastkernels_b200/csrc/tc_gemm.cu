@@ -44,6 +44,7 @@ struct TcBarriers {
     uint64_t tempty[2];
     uint32_t tmem_base;
     int abort_flag;
+    int units;
 };
 
 struct TcParams {
@@ -86,7 +87,9 @@ tc_grouped_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constan
     tc_fence_after_sync();
     const uint32_t tmem_base = bar.tmem_base;
     pdl_wait();               // pass list and gathered activations come from the kernels before
-    const int units = p.meta[1] * tiles;
+    if (tid == 0) bar.units = p.meta[1] * tiles;      // one load per block, not one per warp
+    __syncthreads();
+    const int units = bar.units;
 
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer

@@ -544,3 +544,26 @@ def test_single_token_fused_kernel_sees_fresh_data_every_call(real_bf16_biased):
         if i % 20 >= 18:
             torch.cuda.synchronize()
             assert torch.equal(out, refs[i % 2][0]) and torch.equal(ids, refs[i % 2][1]), f"call {i}"
+
+
+def test_single_token_fused_kernel_first_run_on_fresh_weights():
+    """Freshly allocated weights are read through cold pages, so the bulk copies of a block complete far
+    out of order.  The first call after a warm-up on a different token must already equal the later calls
+    (a consumer that took a ring slot one lap early would have used stale data on exactly this call)."""
+    from fastkernels_b200.plan import MoEDecodePlan
+    x = make_hidden(77, 1, REAL, dtype=torch.bfloat16, device="cuda")
+    for rep in range(3):
+        w = make_moe_weights(300 + rep, REAL, dtype=torch.bfloat16, device="cuda", bias_std=0.5)
+        plan = MoEDecodePlan(w, 1)
+        plan.run(torch.zeros_like(x))                      # warm-up on other data: leaves different values behind
+        outs = []
+        for _ in range(3):
+            out, _, ids, _ = plan.run(x)
+            outs.append((out.clone(), ids.clone()))
+        torch.cuda.synchronize()
+        assert torch.equal(outs[0][0], outs[2][0]) and torch.equal(outs[1][0], outs[2][0]), f"weights {rep}"
+        assert torch.equal(outs[0][1], outs[2][1])
+        ref = oracle_layer(x, w, 8)
+        if bool((ref.margin > 2e-6).all()):
+            assert torch.equal(outs[0][1].cpu(), ref.topk_ids)
+        del plan, w
