@@ -320,7 +320,10 @@ def run_single(args):
     # algorithmic byte and scaled to this launch's bytes: the kernels stream every weight byte exactly once, so
     # traffic grows in proportion to the experts touched.
     if len(stage_ms) == 1:
-        dom_kernel, dom_bytes, traffic_ratio = "decode1_kernel (whole layer, one token, one launch)", layer_bytes, None
+        # the step is this one kernel: its duration is the graph-replayed step (the stage events add their own gap)
+        dom_kernel, dom_bytes, traffic_ratio = ("decode1_kernel (whole layer, one token, one launch)", layer_bytes,
+                                                NCU_TRAFFIC_PER_BYTE["decode1"])
+        dom_ms = ms
     elif B <= 96:
         dom_kernel, dom_bytes, traffic_ratio = ("stream_gemv_kernel<8,true,false> (gate_up GEMV + SwiGLU, "
                                                 "TMA ring, mma.sync consumers)"), gate_up_bytes, NCU_TRAFFIC_PER_BYTE["stream_gate_up"]
@@ -430,8 +433,8 @@ def run_single(args):
 
 
 # DRAM bytes (read + write) per algorithmic byte of the dominant kernel, from the ncu captures summarised in
-# profiles/stream_gemv_b32.md and profiles/tc_grouped_gemm_b256.md.
-NCU_TRAFFIC_PER_BYTE = {"stream_gate_up": 1.011, "tc_gate_up": 1.016}
+# profiles/stream_gemv_b32.md, profiles/tc_grouped_gemm_b256.md and profiles/decode1_fused_b1.md.
+NCU_TRAFFIC_PER_BYTE = {"stream_gate_up": 1.011, "tc_gate_up": 1.016, "decode1": 1.007}
 
 
 def main():
