@@ -84,3 +84,37 @@ class MoEStackPlan:
         else:
             self._forward()
         return self.x
+
+
+class ResidentMoELayers:
+    """All MoE layers of a checkpoint packed once and kept in HBM, called layer by layer.
+
+    This is the shape of the reference's decode loop at its MoE call site
+    (bench/qwen36_full_decode.py:407-419: `hidden = triton_moe_layer(hidden, *weights, top_k=k)[0]`,
+    where the reference reloads every layer's tensors from safetensors on every token): here the layers
+    are packed from the checkpoint mapping once (`weights.pack_qwen36_moe_weights_from_state_dict`, in
+    the compute dtype, straight onto the GPU), each layer owns a prepared call (`MoEDecodePlan`) for the
+    fixed token count, and `layer(i, hidden)` returns the new residual stream `hidden + MoE_i(hidden)`.
+    The sequence mixers between the MoE sublayers stay with the caller.
+    """
+
+    def __init__(self, layers: Sequence, tokens: int, *, hidden_dtype: torch.dtype = torch.bfloat16, top_k: int = 8,
+                 eps: float = 1e-6, flags: int = 0):
+        self.plans = [MoEDecodePlan(w, tokens, hidden_dtype=hidden_dtype, top_k=top_k, eps=eps, flags=flags, residual=True)
+                      for w in layers]
+        self.tokens = tokens
+
+    @classmethod
+    def from_state_dict(cls, tensors, layer_indices: Sequence[int], tokens: int, *, spec=None, device="cuda",
+                        dtype: torch.dtype = torch.bfloat16, **kw) -> "ResidentMoELayers":
+        from .weights import pack_qwen36_moe_weights_from_state_dict
+        layers = [pack_qwen36_moe_weights_from_state_dict(tensors, i, spec=spec, device=device, dtype=dtype).weights
+                  for i in layer_indices]
+        return cls(layers, tokens, hidden_dtype=dtype, **kw)
+
+    def layer(self, index: int, hidden: torch.Tensor) -> torch.Tensor:
+        """`hidden [tokens, H]` in the plans' activation dtype -> fp32 `hidden + moe_update` (a view of the plan's
+        buffer, overwritten by the next call of the same layer)."""
+        plan = self.plans[index]
+        plan.run(hidden)
+        return plan.layer_hidden

@@ -73,6 +73,44 @@ def load_reference(path: str):
         make_synthetic_qwen36_decode_weights
 
 
+def pin_weight_packer(reference_path: str) -> None:
+    """`fastkernels_b200.weights` against the reference's packer on synthetic checkpoints: same keys chosen,
+    same tensors out, for the split, per-expert packed and grouped (both orientations) layouts."""
+    import importlib
+    rw = importlib.import_module("fastkernels.models.qwen36_weights")
+    rq = importlib.import_module("fastkernels.models.qwen36")
+    from fastkernels_b200.weights import (pack_qwen36_moe_weights_from_state_dict, resolve_qwen36_moe_weight_keys,
+                                          state_dict_from_moe_weights)
+    rspec = rq.synthetic_qwen36_spec()
+    spec = MoESpec(hidden_size=rspec.hidden_size, num_experts=rspec.num_experts, num_routed_experts=rspec.num_routed_experts,
+                   expert_intermediate_size=rspec.expert_intermediate_size)
+    full = make_moe_weights(21, spec, dtype=torch.float32)
+    variants = {"grouped": state_dict_from_moe_weights(full, 3, grouped=True),
+                "split": state_dict_from_moe_weights(full, 3, grouped=False, prefix="model.layers")}
+    flipped = dict(variants["grouped"])
+    k = "model.language_model.layers.3.mlp.experts.down_proj"
+    flipped[k] = flipped[k].transpose(1, 2).contiguous()
+    variants["grouped, down stored [E,I,H]"] = flipped
+    packed = {kk: v for kk, v in variants["split"].items() if ".experts." not in kk}
+    for e in range(spec.num_experts):
+        packed[f"model.layers.3.mlp.experts.{e}.gate_up_proj.weight"] = full.expert_gate_up_weight[e]
+        packed[f"model.layers.3.mlp.experts.{e}.down_proj.weight"] = full.expert_down_weight[e]
+    variants["per-expert packed"] = packed
+    fields = ("norm_weight", "router_weight", "expert_gate_up_weight", "expert_down_weight",
+              "shared_gate_up_weight", "shared_down_weight", "shared_expert_gate_weight")
+    for name, ckpt in variants.items():
+        ref_keys = rw.resolve_qwen36_moe_weight_keys(ckpt, 3, spec=rspec)
+        ours_keys = resolve_qwen36_moe_weight_keys(ckpt, 3, spec=spec)
+        for field in fields:
+            assert getattr(ref_keys, field) == getattr(ours_keys, field), (name, field)
+        ref = rw.pack_qwen36_moe_weights_from_state_dict(ckpt, 3, spec=rspec)
+        ours = pack_qwen36_moe_weights_from_state_dict(ckpt, 3, spec=spec).weights
+        for field in fields:
+            a, b = getattr(ref, field), getattr(ours, field)
+            assert (a is None) == (b is None) and (a is None or torch.equal(a, b)), (name, field)
+        print(f"pinned: weight packer [{name}] keys and tensors equal the reference packer's")
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", default="/root/reference")
@@ -174,6 +212,7 @@ def main() -> None:
                             **{k: layer[k].numpy() for k in ("norm_weight", "router_weight", "expert_gate_up_weight",
                                                              "expert_down_weight", "shared_gate_up_weight",
                                                              "shared_down_weight")})
+    pin_weight_packer(args.reference)
     print("all pins hold" + ("; golden vectors written" if args.write else ""))
 
 

@@ -567,3 +567,25 @@ def test_single_token_fused_kernel_first_run_on_fresh_weights():
         if bool((ref.margin > 2e-6).all()):
             assert torch.equal(outs[0][1].cpu(), ref.topk_ids)
         del plan, w
+
+
+def test_resident_layers_from_checkpoint_mapping_match_function_api():
+    """Checkpoint-style mapping -> packed bf16 layers on the GPU -> per-layer calls, against the drop-in
+    function on the same packed tensors (the caller of the reference's decode loop, MoE sublayer only)."""
+    from fastkernels_b200.stack import ResidentMoELayers
+    from fastkernels_b200.weights import pack_qwen36_moe_weights_from_state_dict, state_dict_from_moe_weights
+    spec = MoESpec(hidden_size=256, num_experts=16, num_routed_experts=4, expert_intermediate_size=256, num_layers=2)
+    ckpt = {}
+    for layer in (0, 1):
+        ckpt.update(state_dict_from_moe_weights(make_moe_weights(400 + layer, spec, dtype=torch.float32), layer,
+                                                grouped=(layer == 0)))
+    tokens = 5
+    resident = ResidentMoELayers.from_state_dict(ckpt, [0, 1], tokens, spec=spec, top_k=4)
+    hidden = make_hidden(41, tokens, spec, dtype=torch.bfloat16, device="cuda")
+    for layer in (0, 1):
+        w = pack_qwen36_moe_weights_from_state_dict(ckpt, layer, spec=spec, device="cuda", dtype=torch.bfloat16).weights
+        want = triton_qwen36_batched_moe_layer_decode(hidden, *w.tuple(), top_k=4)[0]
+        got = resident.layer(layer, hidden)
+        assert torch.equal(got, want)
+        ref = oracle_layer(hidden, w, 4)
+        check_output(got - hidden.float(), ref.output, torch.bfloat16)
