@@ -319,6 +319,14 @@ size_t fk_moe_host_staging_bytes(const fk_moe_dims* d, int hidden_dtype) {
     return align256(T * H * es) + 2 * align256(T * H * 4) + align256(T * E * 4) + align256(T * k * 8) + align256(T * k * 4);
 }
 
+// Device-side alias of a pinned (page-locked, mapped) host buffer, or null for pageable memory.
+static void* mapped_alias(void* host) {
+    if (host == nullptr) return nullptr;
+    cudaPointerAttributes attr{};
+    if (cudaPointerGetAttributes(&attr, host) != cudaSuccess) { cudaGetLastError(); return nullptr; }
+    return attr.type == cudaMemoryTypeHost ? attr.devicePointer : nullptr;
+}
+
 int fk_moe_layer_host(const fk_moe_call* c, void* staging, size_t staging_bytes, void* stream) {
     if (c == nullptr || staging == nullptr) return FK_ERR_ARG;
     size_t need = fk_moe_host_staging_bytes(&c->dims, c->hidden_dtype);
@@ -339,12 +347,18 @@ int fk_moe_layer_host(const fk_moe_call* c, void* staging, size_t staging_bytes,
     float* d_w = (float*)take(T * k * 4);
     FK_CUDA_OK(cudaMemcpyAsync(d_hidden, c->hidden, T * H * es, cudaMemcpyHostToDevice, s), "h2d hidden");
     fk_moe_call dev = *c;
-    dev.hidden = d_hidden; dev.out = d_out; dev.layer_hidden = c->layer_hidden ? d_layer : nullptr;
+    // The output rows are written once, by the last kernel, and read by none: when the caller's buffers are pinned
+    // the kernel stores them straight into host memory and the copy back (and its place in the stream) is saved.
+    float* out_alias = (float*)mapped_alias(c->out);
+    float* layer_alias = (float*)mapped_alias(c->layer_hidden);
+    dev.hidden = d_hidden; dev.out = out_alias ? out_alias : d_out;
+    dev.layer_hidden = c->layer_hidden ? (layer_alias ? layer_alias : d_layer) : nullptr;
     dev.logits = d_logits; dev.topk_ids = d_ids; dev.topk_weights = d_w;
     int st = fk_moe_layer(&dev, stream);
     if (st != FK_OK) return st;
-    FK_CUDA_OK(cudaMemcpyAsync(c->out, d_out, T * H * 4, cudaMemcpyDeviceToHost, s), "d2h out");
-    if (c->layer_hidden) FK_CUDA_OK(cudaMemcpyAsync(c->layer_hidden, d_layer, T * H * 4, cudaMemcpyDeviceToHost, s), "d2h layer");
+    if (!out_alias) FK_CUDA_OK(cudaMemcpyAsync(c->out, d_out, T * H * 4, cudaMemcpyDeviceToHost, s), "d2h out");
+    if (c->layer_hidden && !layer_alias)
+        FK_CUDA_OK(cudaMemcpyAsync(c->layer_hidden, d_layer, T * H * 4, cudaMemcpyDeviceToHost, s), "d2h layer");
     if (c->logits) FK_CUDA_OK(cudaMemcpyAsync(c->logits, d_logits, T * E * 4, cudaMemcpyDeviceToHost, s), "d2h logits");
     if (c->topk_ids) FK_CUDA_OK(cudaMemcpyAsync(c->topk_ids, d_ids, T * k * 8, cudaMemcpyDeviceToHost, s), "d2h ids");
     if (c->topk_weights) FK_CUDA_OK(cudaMemcpyAsync(c->topk_weights, d_w, T * k * 4, cudaMemcpyDeviceToHost, s), "d2h weights");

@@ -130,3 +130,34 @@ class MoEDecodePlan:
         hc.topk_weights = _ptr(weights_host)
         _lib.check(self.lib.fk_moe_layer_host(C.byref(hc), self._staging.data_ptr(), self._staging.numel(),
                                               torch.cuda.current_stream().cuda_stream), "fk_moe_layer_host")
+
+    def capture_host(self) -> None:
+        """Capture the host-buffer call (copy in, layer, copies out) into one CUDA graph over pinned buffers owned
+        by the plan.  The eager `run_host` enqueues nine stream operations from Python per call, which costs more
+        host time than the layer takes on the GPU at decode sizes; a replay is one launch."""
+        T, H, k = self.tokens, self.hidden_size, self.top_k
+        self.host_in = torch.empty((T, H), dtype=self.hidden_dtype).pin_memory()
+        self.host_out = torch.empty((T, H), dtype=torch.float32).pin_memory()
+        self.host_ids = torch.empty((T, k), dtype=torch.int64).pin_memory()
+        self.host_weights = torch.empty((T, k), dtype=torch.float32).pin_memory()
+        self.host_in.zero_()
+        s = torch.cuda.Stream(device=self.device)
+        s.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(s):
+            self.run_host(self.host_in, self.host_out, self.host_ids, self.host_weights)      # allocates the staging
+        torch.cuda.current_stream().wait_stream(s)
+        torch.cuda.synchronize(self.device)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            self.run_host(self.host_in, self.host_out, self.host_ids, self.host_weights)
+        self.host_graph = g
+
+    def run_host_graph(self, hidden_host: torch.Tensor):
+        """`hidden_host` (host, [T,H]) -> `(out, topk_ids, topk_weights)` in the plan's pinned host buffers, valid once
+        the current stream has been synchronised; overwritten by the next call."""
+        if getattr(self, "host_graph", None) is None:
+            self.capture_host()
+        self.host_in.copy_(hidden_host)
+        self.host_graph.replay()
+        return self.host_out, self.host_ids, self.host_weights
+

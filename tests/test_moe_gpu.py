@@ -589,3 +589,24 @@ def test_resident_layers_from_checkpoint_mapping_match_function_api():
         assert torch.equal(got, want)
         ref = oracle_layer(hidden, w, 4)
         check_output(got - hidden.float(), ref.output, torch.bfloat16)
+
+
+def test_host_buffer_call_eager_and_graph(real_bf16_biased):
+    """Host buffers in, host buffers out: the captured variant equals the eager one and the device-resident call."""
+    from fastkernels_b200.plan import MoEDecodePlan
+    w = real_bf16_biased
+    tokens = 7
+    plan = MoEDecodePlan(w, tokens)
+    x = make_hidden(55, tokens, REAL, dtype=torch.bfloat16)
+    out_d, _, ids_d, w_d = plan.run(x.cuda())
+    out_d, ids_d, w_d = out_d.cpu(), ids_d.cpu(), w_d.cpu()
+    out_e = torch.empty(tokens, REAL.hidden_size).pin_memory()
+    ids_e = torch.empty(tokens, 8, dtype=torch.int64).pin_memory()
+    w_e = torch.empty(tokens, 8).pin_memory()
+    plan.run_host(x.pin_memory(), out_e, ids_e, w_e)
+    torch.cuda.synchronize()
+    assert torch.equal(out_e, out_d) and torch.equal(ids_e, ids_d) and torch.equal(w_e, w_d)
+    for _ in range(2):
+        out_g, ids_g, w_g = plan.run_host_graph(x)
+        torch.cuda.synchronize()
+        assert torch.equal(out_g, out_d) and torch.equal(ids_g, ids_d) and torch.equal(w_g, w_d)
