@@ -45,6 +45,15 @@ class Call(C.Structure):
     ]
 
 
+EP_MAX_RANKS = 8
+EP_HANDLE_BYTES = 64
+
+
+class EpComm(C.Structure):          # struct fk_ep_comm
+    _fields_ = [("rank", C.c_int32), ("world", C.c_int32), ("tokens_per_rank", C.c_int32), ("reserved", C.c_int32),
+                ("base", C.c_void_p * EP_MAX_RANKS), ("bytes", C.c_size_t)]
+
+
 # name -> (restype, argtypes); every symbol include/fkmoe.h declares
 SIGNATURES = {
     "fk_version": (C.c_int, []),
@@ -68,6 +77,13 @@ SIGNATURES = {
     "fk_expert_histogram": (C.c_int, [C.c_void_p, C.c_int, C.c_int64, C.c_int, C.c_void_p, C.c_void_p]),
     "fk_moe_permute": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p,
                                  C.c_void_p, C.c_size_t, C.c_void_p]),
+    "fk_ep_buffer_bytes": (C.c_size_t, [C.c_int, C.c_int, C.c_int, C.c_int, C.c_int]),
+    "fk_ep_buffer_create": (C.c_int, [C.c_size_t, C.POINTER(C.c_void_p), C.c_void_p]),
+    "fk_ep_buffer_open": (C.c_int, [C.c_void_p, C.POINTER(C.c_void_p)]),
+    "fk_ep_buffer_close": (C.c_int, [C.c_void_p]),
+    "fk_ep_buffer_destroy": (C.c_int, [C.c_void_p]),
+    "fk_moe_layer_ep": (C.c_int, [C.POINTER(Call), C.POINTER(EpComm), C.c_void_p]),
+    "fk_ep_status": (C.c_int, [C.POINTER(EpComm), C.POINTER(C.c_int)]),
 }
 
 _lib = None

@@ -48,11 +48,13 @@ static int check_workspace(const fk_moe_call* c, Workspace& w) {
 
 // permutation + expert kernels + combine for routing already present in ids/weights
 static int run_experts(const fk_moe_call* c, const Workspace& w, const long long* ids, const float* weights,
-                       const float* shared_gate_sig, cudaStream_t stream) {
+                       const float* shared_gate_sig, cudaStream_t stream, const int* ids32 = nullptr,
+                       const EpPeers* ep_peers = nullptr) {
     const fk_moe_dims& d = c->dims;
     void* ws = c->workspace;
     PermuteParams pp{};
     pp.ids64 = ids;
+    pp.ids32 = ids32;
     pp.routes = d.tokens * d.top_k;
     pp.E = d.experts;
     pp.expert_base = c->expert_base;
@@ -116,7 +118,12 @@ static int run_experts(const fk_moe_call* c, const Workspace& w, const long long
     else
         st = launch_experts_generic(ep, c->weight_dtype, stream);
     if (st != FK_OK) return st;
-    st = launch_combine(ep, stream);
+    if (ep_peers) {
+        ep.ep = *ep_peers;
+        st = launch_combine_ep(ep, stream);
+    } else {
+        st = launch_combine(ep, stream);
+    }
     stage_mark();   // end of combine
     return st;
 }
@@ -363,6 +370,135 @@ int fk_moe_layer_host(const fk_moe_call* c, void* staging, size_t staging_bytes,
     if (c->topk_ids) FK_CUDA_OK(cudaMemcpyAsync(c->topk_ids, d_ids, T * k * 8, cudaMemcpyDeviceToHost, s), "d2h ids");
     if (c->topk_weights) FK_CUDA_OK(cudaMemcpyAsync(c->topk_weights, d_w, T * k * 4, cudaMemcpyDeviceToHost, s), "d2h weights");
     return FK_OK;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Expert parallel over peer memory
+// ---------------------------------------------------------------------------------------------
+size_t fk_ep_buffer_bytes(int world, int tokens_per_rank, int hidden, int top_k, int hidden_dtype) {
+    if (world < 1 || world > FK_EP_MAX_RANKS || tokens_per_rank < 1 || hidden < 1 || hidden > FK_MAX_HIDDEN || top_k < 1 ||
+        top_k > FK_MAX_TOP_K || !dtype_ok(hidden_dtype))
+        return 0;
+    return ep_layout(world, tokens_per_rank, hidden, top_k, hidden_dtype).total;
+}
+
+int fk_ep_buffer_create(size_t bytes, void** buffer, void* handle_out) {
+    if (bytes < 256 || buffer == nullptr || handle_out == nullptr) return FK_ERR_ARG;
+    static_assert(sizeof(cudaIpcMemHandle_t) <= FK_EP_HANDLE_BYTES, "IPC handle does not fit");
+    void* ptr = nullptr;
+    FK_CUDA_OK(cudaMalloc(&ptr, bytes), "ep buffer alloc");
+    FK_CUDA_OK(cudaMemset(ptr, 0, bytes), "ep buffer clear");
+    cudaIpcMemHandle_t h;
+    FK_CUDA_OK(cudaIpcGetMemHandle(&h, ptr), "ep buffer handle");
+    memset(handle_out, 0, FK_EP_HANDLE_BYTES);
+    memcpy(handle_out, &h, sizeof(h));
+    FK_CUDA_OK(cudaDeviceSynchronize(), "ep buffer sync");
+    *buffer = ptr;
+    return FK_OK;
+}
+
+int fk_ep_buffer_open(const void* handle, void** buffer) {
+    if (handle == nullptr || buffer == nullptr) return FK_ERR_ARG;
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle, sizeof(h));
+    void* ptr = nullptr;
+    FK_CUDA_OK(cudaIpcOpenMemHandle(&ptr, h, cudaIpcMemLazyEnablePeerAccess), "ep buffer open");
+    *buffer = ptr;
+    return FK_OK;
+}
+
+int fk_ep_buffer_close(void* buffer) {
+    if (buffer == nullptr) return FK_OK;
+    FK_CUDA_OK(cudaIpcCloseMemHandle(buffer), "ep buffer close");
+    return FK_OK;
+}
+
+int fk_ep_buffer_destroy(void* buffer) {
+    if (buffer == nullptr) return FK_OK;
+    FK_CUDA_OK(cudaFree(buffer), "ep buffer free");
+    return FK_OK;
+}
+
+int fk_ep_status(const fk_ep_comm* comm, int* error) {
+    if (comm == nullptr || error == nullptr || comm->rank < 0 || comm->rank >= FK_EP_MAX_RANKS || !comm->base[comm->rank]) return FK_ERR_ARG;
+    FK_CUDA_OK(cudaDeviceSynchronize(), "ep status sync");
+    FK_CUDA_OK(cudaMemcpy(error, reinterpret_cast<const char*>(comm->base[comm->rank]) + 20 * 4, sizeof(int), cudaMemcpyDeviceToHost),
+               "ep status read");
+    return FK_OK;
+}
+
+int fk_moe_layer_ep(const fk_moe_call* c, const fk_ep_comm* comm, void* stream) {
+    if (c == nullptr || comm == nullptr || !dims_ok(c->dims, true) || c->dims.top_k > c->dims.experts) return FK_ERR_ARG;
+    if (!dtype_ok(c->hidden_dtype) || !dtype_ok(c->weight_dtype)) return FK_ERR_UNSUPPORTED;
+    const int G = comm->world, rank = comm->rank, T = c->dims.tokens, H = c->dims.hidden, k = c->dims.top_k;
+    if (G < 1 || G > FK_EP_MAX_RANKS || rank < 0 || rank >= G || T != comm->tokens_per_rank || T < 1) return FK_ERR_ARG;
+    if (c->dims.experts % G != 0 || H % 8 != 0) return FK_ERR_ARG;
+    if (!c->hidden || !c->norm_weight || !c->router_weight || !c->expert_gate_up || !c->expert_down || !c->out || !c->logits ||
+        !c->topk_ids || !c->topk_weights)
+        return FK_ERR_ARG;
+    if ((c->shared_gate_up == nullptr) != (c->shared_down == nullptr)) return FK_ERR_ARG;
+    const EpLayout lay = ep_layout(G, T, H, k, c->hidden_dtype);
+    if (comm->bytes < lay.total) return FK_ERR_WORKSPACE;
+    for (int r = 0; r < G; ++r)
+        if (comm->base[r] == nullptr) return FK_ERR_ARG;
+    if ((reinterpret_cast<uintptr_t>(c->hidden) | reinterpret_cast<uintptr_t>(c->out) | reinterpret_cast<uintptr_t>(c->layer_hidden)) & 15)
+        return FK_ERR_ARG;
+    const int e_local = c->dims.experts / G;
+    // the gathered call: all ranks' tokens, this rank's experts
+    fk_moe_call all = *c;
+    all.dims.tokens = G * T;
+    all.dims.experts = e_local;
+    Workspace w_all;
+    int st = check_workspace(&all, w_all);
+    if (st != FK_OK) return st;
+    Workspace w_own = workspace_layout(c->dims);
+    if (c->workspace_bytes < w_own.total) return FK_ERR_WORKSPACE;
+    cudaStream_t s = (cudaStream_t)stream;
+    const bool gated = c->shared_gate_up && c->shared_gate;
+    unsigned char* mine = reinterpret_cast<unsigned char*>(comm->base[rank]);
+
+    // 1. router on the rank's own tokens; the shared gate lands where the gathered call looks for it
+    RouterParams rp{};
+    rp.hidden = c->hidden; rp.hidden_dtype = c->hidden_dtype;
+    rp.norm_weight = c->norm_weight; rp.router_weight = c->router_weight; rp.router_bias = c->router_bias;
+    rp.shared_gate_weight = gated ? c->shared_gate : nullptr;
+    rp.shared_gate_out = gated ? at<float>(c->workspace, w_all.shared_gate) + (size_t)rank * T : nullptr;
+    rp.logits = c->logits; rp.topk_ids = reinterpret_cast<long long*>(c->topk_ids); rp.topk_weights = c->topk_weights;
+    rp.ids32 = nullptr;
+    rp.tickets = at<unsigned>(c->workspace, w_all.tickets);
+    rp.T = T; rp.H = H; rp.E = c->dims.experts; rp.top_k = k;
+    rp.eps = c->eps; rp.norm_offset = c->norm_offset;
+    st = launch_router(rp, c->weight_dtype, s);
+    if (st != FK_OK) return st;
+
+    // 2. dispatch: own rows into every rank's buffer, flags, wait for everyone's rows
+    EpPeers peers{};
+    for (int r = 0; r < G; ++r) peers.header[r] = reinterpret_cast<unsigned*>(comm->base[r]);
+    peers.partial_offset = lay.partial;
+    peers.world = G; peers.rank = rank; peers.tokens = T;
+    EpDispatchParams dp{};
+    dp.peers = peers; dp.layout = lay;
+    dp.hidden = c->hidden; dp.ids = rp.topk_ids; dp.weights = c->topk_weights;
+    dp.T = T; dp.H = H; dp.top_k = k; dp.elem_bytes = c->hidden_dtype == FK_F32 ? 4 : 2;
+    st = launch_ep_dispatch(dp, s);
+    if (st != FK_OK) return st;
+
+    // 3. local experts on the gathered tokens (+ shared expert on the own ones); rows go to the home ranks
+    all.hidden = mine + lay.hidden;
+    all.flags = c->flags | FK_FLAG_SKIP_FOREIGN;
+    all.expert_base = rank * e_local;
+    all.shared_token_base = rank * T;
+    all.shared_token_count = T;
+    all.out = reinterpret_cast<float*>(mine + lay.partial);     // not written: the combine stores to the peers
+    all.layer_hidden = nullptr;
+    st = run_experts(&all, w_all, nullptr, reinterpret_cast<const float*>(mine + lay.weights),
+                     gated ? at<float>(c->workspace, w_all.shared_gate) : nullptr, s,
+                     reinterpret_cast<const int*>(mine + lay.ids), &peers);
+    if (st != FK_OK) return st;
+
+    // 4. fixed-order sum of the world partials for the own tokens
+    return launch_ep_reduce(reinterpret_cast<const float*>(mine + lay.partial), G, T, H, c->out, c->layer_hidden, c->hidden,
+                            c->hidden_dtype, s);
 }
 
 int fk_single_expert_mlp(const void* hidden, int hidden_dtype, const void* gate_up, const void* down, int weight_dtype,

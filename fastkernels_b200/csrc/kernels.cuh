@@ -45,6 +45,31 @@ struct PermuteParams {
 int launch_permute(const PermuteParams& p, cudaStream_t stream);
 int launch_histogram(const void* ids, int ids_are_int64, long long count, int E, int* counts, cudaStream_t stream);
 
+// Expert-parallel exchange over peer memory (ep_p2p.cu)
+struct EpLayout {              // byte offsets inside one rank's exchange buffer (256-byte header first)
+    size_t hidden, ids, weights, partial, total;
+};
+EpLayout ep_layout(int world, int tokens, int hidden, int top_k, int hidden_dtype);
+
+struct EpPeers {
+    unsigned* header[8];       // exchange buffer of every rank as mapped in this process
+    size_t partial_offset;     // EpLayout::partial
+    int world, rank;           // world == 0: not expert parallel
+    int tokens;                // tokens per rank
+};
+
+struct EpDispatchParams {
+    EpPeers peers;
+    EpLayout layout;
+    const void* hidden;        // this rank's [T,H]
+    const long long* ids;      // [T,k] global expert ids
+    const float* weights;      // [T,k]
+    int T, H, top_k, elem_bytes;
+};
+int launch_ep_dispatch(const EpDispatchParams& p, cudaStream_t stream);
+int launch_ep_reduce(const float* partial, int world, int T, int H, float* out, float* layer_hidden, const void* hidden,
+                     int hidden_dtype, cudaStream_t stream);
+
 struct ExpertParams {
     const void* hidden;
     int hidden_dtype;
@@ -69,7 +94,9 @@ struct ExpertParams {
     float* out;                   // [T,H]
     float* layer_hidden;          // optional [T,H]
     int* error_word;              // optional: set to non-zero when a bounded device-side wait gave up
+    EpPeers ep;                   // ep.world > 0: the combine stores every token's row into its home rank's buffer
 };
+int launch_combine_ep(const ExpertParams& p, cudaStream_t stream);
 // shape-agnostic kernels (any dtype, any H/I)
 int launch_experts_generic(const ExpertParams& p, int weight_dtype, cudaStream_t stream);
 // bf16 weight-streaming grouped GEMV (H,I in {256,512,1024,2048})

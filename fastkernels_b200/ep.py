@@ -27,10 +27,17 @@ Results do not depend on scheduling: every sum has a fixed order.
 The exchange code is backend-agnostic (gloo on CPU in the tests); the compute steps default to
 the CUDA library and can be replaced by callables for those tests.  There is no silent fallback:
 without CUDA tensors and without explicit callables the call raises.
+
+Two exchanges are implemented.  `ep_moe_layer` is the portable one (NCCL on GPUs, gloo in the CPU tests).
+`PeerEPLayer` replaces it on one NVLink node: every rank maps every other rank's exchange buffer (CUDA IPC) and
+the library's kernels store activations, routing and partial rows straight into the peers' memory and exchange
+arrival flags themselves (`fk_moe_layer_ep`, csrc/ep_p2p.cu): one C call per layer, no collective library, no
+torch glue kernels, capturable in a CUDA graph.
 """
 
 from __future__ import annotations
 
+import ctypes as C
 from dataclasses import dataclass
 from typing import Callable, Optional
 
@@ -186,3 +193,132 @@ class EPDecodePlan:
         else:
             self._call()
         return self.out, self.logits, self.topk_ids, self.topk_weights
+
+
+# --------------------------------------------------------------------------- exchange over peer memory
+class PeerExchange:
+    """This rank's exchange buffer plus the mapped buffers of all other ranks (one node, one process per GPU).
+
+    Built collectively: every rank of `group` must construct it with the same arguments.  The IPC handles travel
+    through the process group once; afterwards no collective call is made.
+    """
+
+    def __init__(self, tokens_per_rank: int, hidden_size: int, top_k: int, hidden_dtype: torch.dtype,
+                 group: Optional[dist.ProcessGroup] = None):
+        self.lib = _lib.load()
+        self.group = group
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        if self.world > _lib.EP_MAX_RANKS:
+            raise ValueError(f"at most {_lib.EP_MAX_RANKS} ranks")
+        code = {torch.float32: 0, torch.bfloat16: 1, torch.float16: 2}[hidden_dtype]
+        self.bytes = self.lib.fk_ep_buffer_bytes(self.world, tokens_per_rank, hidden_size, top_k, code)
+        if self.bytes == 0:
+            raise ValueError("exchange buffer: arguments outside the supported limits")
+        own = C.c_void_p()
+        handle = C.create_string_buffer(_lib.EP_HANDLE_BYTES)
+        _lib.check(self.lib.fk_ep_buffer_create(self.bytes, C.byref(own), handle), "fk_ep_buffer_create")
+        self.own = own.value
+        handles = [None] * self.world
+        dist.all_gather_object(handles, bytes(handle.raw), group=group)
+        self.comm = _lib.EpComm()
+        self.comm.rank, self.comm.world, self.comm.tokens_per_rank, self.comm.bytes = self.rank, self.world, tokens_per_rank, self.bytes
+        self._opened = []
+        for r in range(self.world):
+            if r == self.rank:
+                self.comm.base[r] = self.own
+            else:
+                ptr = C.c_void_p()
+                _lib.check(self.lib.fk_ep_buffer_open(C.create_string_buffer(handles[r], _lib.EP_HANDLE_BYTES), C.byref(ptr)),
+                           "fk_ep_buffer_open")
+                self.comm.base[r] = ptr.value
+                self._opened.append(ptr.value)
+        dist.barrier(group=group)          # every rank has mapped every buffer before anyone stores into one
+
+    def error(self) -> int:
+        """Synchronises the device; non-zero if a wait on a peer ever gave up (1: dispatch, 2: combine)."""
+        e = C.c_int(0)
+        _lib.check(self.lib.fk_ep_status(C.byref(self.comm), C.byref(e)), "fk_ep_status")
+        return e.value
+
+    def close(self) -> None:
+        """Collective: unmaps the peers' buffers and frees the own one once every rank has unmapped it."""
+        if self.own is None:
+            return
+        torch.cuda.synchronize()
+        for ptr in self._opened:
+            self.lib.fk_ep_buffer_close(ptr)
+        self._opened = []
+        dist.barrier(group=self.group)
+        self.lib.fk_ep_buffer_destroy(self.own)
+        self.own = None
+
+
+class PeerEPLayer:
+    """One rank's expert-parallel layer call over peer memory, shapes fixed, optionally one CUDA graph.
+
+    Same results as `ep_moe_layer` (the partial rows are summed in rank order on the home rank)."""
+
+    def __init__(self, shard: EPShard, exchange: PeerExchange, tokens: int, *, hidden_dtype=torch.bfloat16, top_k: int = 8,
+                 eps: float = 1e-6, residual: bool = False, capture: bool = True):
+        from ._lib import Call, Dims
+        from .plan import _DTYPES, _as_weight, _ptr
+        self.lib, self.exchange, self.shard = _lib.load(), exchange, shard
+        w = shard.weights
+        dev = w.expert_gate_up_weight.device
+        wdt = w.expert_gate_up_weight.dtype
+        E_local, two_i, H = w.expert_gate_up_weight.shape
+        E = shard.num_experts
+        if E_local * shard.world != E or shard.world != exchange.world or shard.rank != exchange.rank:
+            raise ValueError("shard and exchange disagree about the ranks")
+        self._keep = [_as_weight(w.norm_weight, wdt), _as_weight(w.router_weight, wdt), w.expert_gate_up_weight.contiguous(),
+                      _as_weight(w.expert_down_weight, wdt), _as_weight(w.shared_gate_up_weight, wdt),
+                      _as_weight(w.shared_down_weight, wdt), _as_weight(w.shared_expert_gate_weight, wdt),
+                      None if w.router_bias is None else w.router_bias.to(device=dev, dtype=torch.float32).contiguous()]
+        self.hidden = torch.zeros((tokens, H), dtype=hidden_dtype, device=dev)
+        self.out = torch.empty((tokens, H), dtype=torch.float32, device=dev)
+        self.layer_hidden = torch.empty_like(self.out) if residual else None
+        self.logits = torch.empty((tokens, E), dtype=torch.float32, device=dev)
+        self.topk_ids = torch.empty((tokens, top_k), dtype=torch.int64, device=dev)
+        self.topk_weights = torch.empty((tokens, top_k), dtype=torch.float32, device=dev)
+        need = max(self.lib.fk_moe_workspace_bytes(C.byref(Dims(shard.world * tokens, H, E_local, two_i // 2, top_k))),
+                   self.lib.fk_moe_workspace_bytes(C.byref(Dims(tokens, H, E, two_i // 2, top_k))))
+        if need == 0:
+            raise ValueError("MoE dims outside the supported limits")
+        self.workspace = torch.zeros(need, dtype=torch.uint8, device=dev)
+        call = Call()
+        call.dims = Dims(tokens, H, E, two_i // 2, top_k)
+        call.hidden_dtype, call.weight_dtype = _DTYPES[hidden_dtype], _DTYPES[wdt]
+        call.eps, call.norm_offset, call.flags, call.expert_base = eps, 1.0, 0, 0
+        (call.norm_weight, call.router_weight, call.expert_gate_up, call.expert_down, call.shared_gate_up,
+         call.shared_down, call.shared_gate, call.router_bias) = [_ptr(t) for t in self._keep]
+        call.hidden, call.out, call.layer_hidden = _ptr(self.hidden), _ptr(self.out), _ptr(self.layer_hidden)
+        call.logits, call.topk_ids, call.topk_weights = _ptr(self.logits), _ptr(self.topk_ids), _ptr(self.topk_weights)
+        call.workspace, call.workspace_bytes = self.workspace.data_ptr(), self.workspace.numel()
+        self.call = call
+        self.graph = None
+        side = torch.cuda.Stream(device=dev)
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            self.launch()                       # all ranks make this call: the exchange is collective
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize(dev)
+        if capture:
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                self.launch()
+            self.graph = g
+
+    def launch(self) -> None:
+        _lib.check(self.lib.fk_moe_layer_ep(C.byref(self.call), C.byref(self.exchange.comm), torch.cuda.current_stream().cuda_stream),
+                   "fk_moe_layer_ep")
+
+    def run(self, hidden: Optional[torch.Tensor] = None):
+        """Returns `(out, logits, topk_ids, topk_weights)`; `out` includes the residual when asked for at construction."""
+        if hidden is not None:
+            self.hidden.copy_(hidden, non_blocking=True)
+        if self.graph is not None:
+            self.graph.replay()
+        else:
+            self.launch()
+        return (self.layer_hidden if self.layer_hidden is not None else self.out), self.logits, self.topk_ids, self.topk_weights
+

@@ -199,6 +199,50 @@ int fk_moe_permute(const int64_t* topk_ids, int tokens, int top_k, int num_exper
                    int32_t* counts, int32_t* offsets, int32_t* order,
                    void* workspace, size_t workspace_bytes, void* stream);
 
+/* ---------------------------------------------------------------------------------------------
+ * Expert-parallel layer over peer memory (one node, one process per GPU, NVLink).
+ * The reference has no distributed code (no torch.distributed / NCCL / MPI call site anywhere; its plan
+ * lists expert-parallel dispatch as future work, docs/QWEN35_KERNEL_PLAN.md:83).  Semantics: those of
+ * triton_qwen36_batched_moe_decode (src/fastkernels/kernels/triton/qwen36_expert.py:1353) applied to the
+ * concatenation of all ranks' tokens, with rank r holding experts [r*E/world, (r+1)*E/world).
+ *
+ * Every rank owns one exchange buffer (fk_ep_buffer_create) and maps every other rank's buffer through a
+ * CUDA IPC handle (fk_ep_buffer_open).  fk_moe_layer_ep then runs the whole layer for this rank in one
+ * call: router on the rank's own tokens; a dispatch kernel that stores activations and routing of those
+ * tokens into every rank's buffer and exchanges arrival flags; the local experts on all gathered tokens;
+ * a combine kernel that stores each token's partial row straight into its home rank's buffer and
+ * exchanges flags again; a fixed-order sum of the world partials.  No collective library call and no host
+ * synchronisation are involved, so the call can be captured in a CUDA graph.  All ranks must make the
+ * same sequence of calls.  Waits on peers are bounded (about a second); a rank that gives up sets the
+ * error word read by fk_ep_status and finishes with undefined output.
+ * --------------------------------------------------------------------------------------------- */
+#define FK_EP_MAX_RANKS 8
+#define FK_EP_HANDLE_BYTES 64
+
+typedef struct fk_ep_comm {
+    int32_t rank, world;
+    int32_t tokens_per_rank;           /* fixed for the life of the buffers */
+    int32_t reserved;
+    void* base[FK_EP_MAX_RANKS];       /* exchange buffer of rank r as mapped in THIS process (own: base[rank]) */
+    size_t bytes;                      /* size of each buffer */
+} fk_ep_comm;
+
+/* Bytes of one rank's exchange buffer (0 for bad arguments). */
+size_t fk_ep_buffer_bytes(int world, int tokens_per_rank, int hidden, int top_k, int hidden_dtype);
+/* Allocates (cudaMalloc) and clears a buffer on the current device and returns its IPC handle. */
+int fk_ep_buffer_create(size_t bytes, void** buffer, void* handle_out);
+/* Maps another process's buffer from its handle / unmaps it / frees an own buffer. */
+int fk_ep_buffer_open(const void* handle, void** buffer);
+int fk_ep_buffer_close(void* buffer);
+int fk_ep_buffer_destroy(void* buffer);
+/* One expert-parallel layer call for this rank.  `c` describes the rank's own tokens (dims.tokens ==
+ * comm->tokens_per_rank, dims.experts == the GLOBAL expert count, expert_gate_up / expert_down == the rank's
+ * block of experts); outputs as for fk_moe_layer.  The workspace must hold
+ * fk_moe_workspace_bytes({world*tokens, hidden, experts/world, intermediate, top_k}). */
+int fk_moe_layer_ep(const fk_moe_call* c, const fk_ep_comm* comm, void* stream);
+/* Synchronises the device and returns the buffer's error word in *error (0: no wait ever gave up). */
+int fk_ep_status(const fk_ep_comm* comm, int* error);
+
 #ifdef __cplusplus
 }
 #endif

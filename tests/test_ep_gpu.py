@@ -64,3 +64,62 @@ def test_ep_two_gpus_matches_oracle_and_single_gpu():
         msgs.append(failures.get())
     assert not msgs, msgs
     assert all(p.exitcode == 0 for p in procs)
+
+
+def _peer_worker(rank, world, port, tokens, failures):
+    """Expert parallel over peer memory (no collective library in the layer call) against the NCCL exchange and
+    the single-GPU layer; eager and as a replayed CUDA graph, several calls with changing inputs."""
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        from fastkernels_b200.ep import PeerEPLayer, PeerExchange, ep_moe_layer, shard_weights
+        from fastkernels_b200.moe import qwen36_batched_moe_decode
+        from fastkernels_b200.spec import MoESpec
+        from fastkernels_b200.workloads import make_hidden, make_moe_weights
+        spec = MoESpec()
+        full = make_moe_weights(4, spec, dtype=torch.bfloat16, device="cuda", bias_std=0.5)
+        shard = shard_weights(full, rank, world)
+        exchange = PeerExchange(tokens, spec.hidden_size, 8, torch.bfloat16)
+        for capture in (False, True):
+            layer = PeerEPLayer(shard, exchange, tokens, capture=capture)
+            for step in range(4):
+                hidden = make_hidden(70 + rank + 10 * step, tokens, spec, dtype=torch.bfloat16, device="cuda")
+                out, logits, ids, weights = layer.run(hidden)
+                out, ids, weights = out.clone(), ids.clone(), weights.clone()
+                ref_out, _, ref_ids, ref_w = ep_moe_layer(hidden, shard, top_k=8)
+                assert torch.equal(ids, ref_ids) and torch.equal(weights, ref_w), f"routing differs (capture={capture}, step {step})"
+                # same routed sums; the shared gate's dot product is taken by another kernel there (other summation order)
+                torch.testing.assert_close(out, ref_out, atol=2e-5, rtol=1e-4)
+                single, _, ids1, _ = qwen36_batched_moe_decode(hidden, *full.tuple(), router_bias=full.router_bias)
+                assert torch.equal(ids, ids1)
+                torch.testing.assert_close(out, single, atol=2e-5, rtol=1e-4)
+            assert exchange.error() == 0
+        exchange.close()
+    except Exception as exc:  # noqa: BLE001
+        failures.put(f"rank {rank}: {exc!r}")
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("tokens", [6, 40])
+def test_ep_two_gpus_over_peer_memory(tokens):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    ctx = mp.get_context("spawn")
+    failures = ctx.Queue()
+    procs = [ctx.Process(target=_peer_worker, args=(r, 2, port, tokens, failures)) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(300)
+    msgs = []
+    while not failures.empty():
+        msgs.append(failures.get())
+    assert not msgs, msgs
+    assert all(p.exitcode == 0 for p in procs)

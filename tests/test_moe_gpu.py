@@ -610,3 +610,30 @@ def test_host_buffer_call_eager_and_graph(real_bf16_biased):
         out_g, ids_g, w_g = plan.run_host_graph(x)
         torch.cuda.synchronize()
         assert torch.equal(out_g, out_d) and torch.equal(ids_g, ids_d) and torch.equal(w_g, w_d)
+
+
+def test_peer_memory_layer_with_one_rank_equals_the_plain_layer(real_bf16_biased, tmp_path):
+    """World size 1 runs the dispatch, home-rank combine and reduce kernels of the expert-parallel call against the
+    rank's own buffer: same bits as the single-GPU layer."""
+    import torch.distributed as dist
+    from fastkernels_b200.ep import PeerEPLayer, PeerExchange, shard_weights
+    w = real_bf16_biased
+    created = not dist.is_initialized()
+    if created:
+        dist.init_process_group("gloo", init_method=f"file://{tmp_path}/pg", rank=0, world_size=1)
+    try:
+        for tokens in (1, 9, 70):
+            exchange = PeerExchange(tokens, REAL.hidden_size, 8, torch.bfloat16)
+            layer = PeerEPLayer(shard_weights(w, 0, 1), exchange, tokens)
+            for seed in (5, 6):
+                hidden = make_hidden(seed, tokens, REAL, dtype=torch.bfloat16, device="cuda")
+                out, logits, ids, weights = layer.run(hidden)
+                want, want_logits, want_ids, want_w = triton_qwen36_batched_moe_decode(
+                    hidden, *w.tuple(), router_bias=w.router_bias, flags=_lib.FLAG_NO_FUSED_DECODE)
+                assert torch.equal(ids, want_ids) and torch.equal(weights, want_w) and torch.equal(logits, want_logits)
+                assert torch.equal(out, want)
+            assert exchange.error() == 0
+            exchange.close()
+    finally:
+        if created:
+            dist.destroy_process_group()
