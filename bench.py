@@ -53,6 +53,8 @@ def parse_args():
     ap.add_argument("--stack-layers", type=int, default=0,
                     help="also time a stack of this many layers (x <- x + MoE(RMSNorm(x)), one CUDA graph) at 1 and 64 tokens")
     ap.add_argument("--ep-eager", action="store_true", help="expert-parallel leg: no CUDA-graph capture of the layer call")
+    ap.add_argument("--ep-nccl", action="store_true",
+                    help="expert-parallel leg: exchange with NCCL collectives instead of the peer-memory kernels")
     return ap.parse_args()
 
 

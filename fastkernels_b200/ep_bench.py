@@ -48,7 +48,14 @@ def run_ep(args, workload_config, measured_peak, ClockSampler, METRIC, UNIT):
     hid_host = [make_hidden(1000 + i * world + rank, B, spec, dtype=torch.bfloat16).pin_memory() for i in range(pool)]
     hid_dev = [h.to(dev) for h in hid_host]
 
-    plans = [EPDecodePlan(sh, B, capture=not args.ep_eager) for sh in shards]
+    # default: exchange over peer memory inside the library's own kernels; --ep-nccl: NCCL collectives from torch
+    exchange = None
+    if args.ep_nccl:
+        plans = [EPDecodePlan(sh, B, capture=not args.ep_eager) for sh in shards]
+    else:
+        from .ep import PeerEPLayer, PeerExchange
+        exchange = PeerExchange(B, H, 8, torch.bfloat16)
+        plans = [PeerEPLayer(sh, exchange, B, capture=not args.ep_eager) for sh in shards]
     for i, pl in enumerate(plans):              # inputs are resident before the timed region starts
         pl.hidden.copy_(hid_dev[i % pool])
 
@@ -77,7 +84,10 @@ def run_ep(args, workload_config, measured_peak, ClockSampler, METRIC, UNIT):
     ms = timed(lambda i: step(i), K)
     # graph replays bypass the library's launch counter: count what one eager call enqueues
     c0 = lib.fk_launch_count()
-    plans[0]._call()
+    if args.ep_nccl:
+        plans[0]._call()
+    else:
+        plans[0].launch()
     torch.cuda.synchronize()
     launches = (lib.fk_launch_count() - c0) * K
 
@@ -127,7 +137,13 @@ def run_ep(args, workload_config, measured_peak, ClockSampler, METRIC, UNIT):
                     "h2d_bytes_per_step": world * B * H * 2, "d2h_bytes_per_step": world * B * H * 4},
             "gpu_launches": int(launches) * world, "clocks": clocks,
         }
+        line["config"]["exchange"] = "NCCL all-gather + all-to-all" if args.ep_nccl else \
+            "peer-memory stores + flags inside the library's kernels (CUDA IPC over NVLink), no collective call"
         print(json.dumps(line), flush=True)
+    if exchange is not None:
+        err = exchange.error()
+        if err:
+            raise RuntimeError(f"rank {rank}: a wait on a peer gave up (code {err})")
     dist.barrier()
     torch.cuda.synchronize()
     # Tearing down an NCCL communicator while captured graphs that hold its kernels are alive has been
