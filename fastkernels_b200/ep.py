@@ -259,7 +259,8 @@ class PeerEPLayer:
     Same results as `ep_moe_layer` (the partial rows are summed in rank order on the home rank)."""
 
     def __init__(self, shard: EPShard, exchange: PeerExchange, tokens: int, *, hidden_dtype=torch.bfloat16, top_k: int = 8,
-                 eps: float = 1e-6, residual: bool = False, capture: bool = True):
+                 eps: float = 1e-6, residual: bool = False, capture: bool = True, hidden_buffer: Optional[torch.Tensor] = None,
+                 out_buffer: Optional[torch.Tensor] = None, warmup: bool = True):
         from ._lib import Call, Dims
         from .plan import _DTYPES, _as_weight, _ptr
         self.lib, self.exchange, self.shard = _lib.load(), exchange, shard
@@ -274,8 +275,9 @@ class PeerEPLayer:
                       _as_weight(w.expert_down_weight, wdt), _as_weight(w.shared_gate_up_weight, wdt),
                       _as_weight(w.shared_down_weight, wdt), _as_weight(w.shared_expert_gate_weight, wdt),
                       None if w.router_bias is None else w.router_bias.to(device=dev, dtype=torch.float32).contiguous()]
-        self.hidden = torch.zeros((tokens, H), dtype=hidden_dtype, device=dev)
-        self.out = torch.empty((tokens, H), dtype=torch.float32, device=dev)
+        # buffers may be shared between the layers of a stack
+        self.hidden = hidden_buffer if hidden_buffer is not None else torch.zeros((tokens, H), dtype=hidden_dtype, device=dev)
+        self.out = out_buffer if out_buffer is not None else torch.empty((tokens, H), dtype=torch.float32, device=dev)
         self.layer_hidden = torch.empty_like(self.out) if residual else None
         self.logits = torch.empty((tokens, E), dtype=torch.float32, device=dev)
         self.topk_ids = torch.empty((tokens, top_k), dtype=torch.int64, device=dev)
@@ -296,6 +298,8 @@ class PeerEPLayer:
         call.workspace, call.workspace_bytes = self.workspace.data_ptr(), self.workspace.numel()
         self.call = call
         self.graph = None
+        if not warmup:
+            return
         side = torch.cuda.Stream(device=dev)
         side.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(side):

@@ -19,7 +19,7 @@ import torch.distributed as dist
 
 def run_ep(args, workload_config, measured_peak, ClockSampler, METRIC, UNIT):
     from . import _lib
-    from .ep import EPDecodePlan, ep_payload_bytes, EPShard
+    from .ep import EPDecodePlan, ep_payload_bytes, EPShard, PeerEPLayer, PeerExchange
     from .spec import MoESpec
     from .workloads import make_hidden, make_moe_weights
 
@@ -53,7 +53,6 @@ def run_ep(args, workload_config, measured_peak, ClockSampler, METRIC, UNIT):
     if args.ep_nccl:
         plans = [EPDecodePlan(sh, B, capture=not args.ep_eager) for sh in shards]
     else:
-        from .ep import PeerEPLayer, PeerExchange
         exchange = PeerExchange(B, H, 8, torch.bfloat16)
         plans = [PeerEPLayer(sh, exchange, B, capture=not args.ep_eager) for sh in shards]
     for i, pl in enumerate(plans):              # inputs are resident before the timed region starts
@@ -120,6 +119,35 @@ def run_ep(args, workload_config, measured_peak, ClockSampler, METRIC, UNIT):
     per_expert = 3 * H * I * 2
     rank_bytes = (u_local + 1) * per_expert + E * H * 2 + 2 * H * 2 + B * H * 2 + B * H * 4 + B * E * 4 + B * 8 * 12
     payload = ep_payload_bytes(B, H, 8, world)
+    # optional: the layer stack (x <- x + MoE_l(RMSNorm(x))) expert parallel over the same peer-memory exchange
+    stack = None
+    if args.stack_layers > 0 and not args.ep_nccl:
+        from .stack import MoEStackPlan
+        del plans
+        if exchange is not None:
+            if exchange.error():
+                raise RuntimeError("exchange error before the stack leg")
+            exchange.close()
+        torch.cuda.empty_cache()
+        for layer in range(len(shards), args.stack_layers):
+            w = make_moe_weights(layer, spec, dtype=torch.bfloat16, device=dev, bias_std=0.5,
+                                 expert_range=(rank * per, (rank + 1) * per))
+            shards.append(EPShard(w, rank, world, E))
+        stack = {"layers": args.stack_layers, "runs": []}
+        for tok in (1, 64):
+            ex = PeerExchange(tok, H, 8, torch.bfloat16)
+            sp = MoEStackPlan(shards[:args.stack_layers], tok, exchange=ex)
+            x0 = make_hidden(3000 + tok + rank, tok, spec, dtype=torch.float32, device=dev)
+            for _ in range(3):
+                sp.run(x0)
+            t_ms = timed(lambda i: sp.run(x0), 10)
+            stack["runs"].append({"tokens_per_gpu": tok, "ms_per_stack_pass": t_ms, "us_per_layer": t_ms * 1e3 / args.stack_layers,
+                                  "tokens_per_s": world * tok / (t_ms * 1e-3)})
+            if ex.error():
+                raise RuntimeError("exchange error in the stack leg")
+            del sp
+            ex.close()
+        exchange = None
     if rank == 0:
         achieved = rank_bytes / (ms * 1e-3) / 1e9
         line = {
@@ -137,6 +165,8 @@ def run_ep(args, workload_config, measured_peak, ClockSampler, METRIC, UNIT):
                     "h2d_bytes_per_step": world * B * H * 2, "d2h_bytes_per_step": world * B * H * 4},
             "gpu_launches": int(launches) * world, "clocks": clocks,
         }
+        if stack is not None:
+            line["stack"] = stack
         line["config"]["exchange"] = "NCCL all-gather + all-to-all" if args.ep_nccl else \
             "peer-memory stores + flags inside the library's kernels (CUDA IPC over NVLink), no collective call"
         print(json.dumps(line), flush=True)

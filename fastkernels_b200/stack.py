@@ -24,7 +24,7 @@ from .plan import MoEDecodePlan
 
 class MoEStackPlan:
     def __init__(self, layers: Sequence, tokens: int, *, top_k: int = 8, eps: float = 1e-6, norm_eps: float = 1e-6,
-                 act_dtype: torch.dtype = torch.bfloat16, group=None, capture: bool = True, flags: int = 0):
+                 act_dtype: torch.dtype = torch.bfloat16, group=None, capture: bool = True, flags: int = 0, exchange=None):
         from .ep import EPShard
         self.lib = _lib.load()
         self.layers = list(layers)
@@ -39,10 +39,17 @@ class MoEStackPlan:
         self.xin = torch.zeros((tokens, H), device=dev, dtype=act_dtype)          # normed activations of the current layer
         self.topk_ids = []
         self.graph = None
+        self.exchange = exchange
         if not self.ep:
             self.update = torch.zeros((tokens, H), device=dev, dtype=torch.float32)
             self.plans = [MoEDecodePlan(w, tokens, hidden_dtype=act_dtype, top_k=top_k, eps=eps, flags=flags,
                                         hidden_buffer=self.xin, out_buffer=self.update) for w in self.layers]
+        elif exchange is not None:
+            # expert parallel over peer memory: every layer's call uses the same exchange buffers, one after the other
+            from .ep import PeerEPLayer
+            self.update = torch.zeros((tokens, H), device=dev, dtype=torch.float32)
+            self.plans = [PeerEPLayer(sh, exchange, tokens, hidden_dtype=act_dtype, top_k=top_k, eps=eps, capture=False,
+                                      hidden_buffer=self.xin, out_buffer=self.update, warmup=False) for sh in self.layers]
         side = torch.cuda.Stream(device=dev)
         side.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(side):
@@ -67,7 +74,7 @@ class MoEStackPlan:
         self.topk_ids = []
         for i, layer in enumerate(self.layers):
             self._norm(update)                       # x += previous update; xin = RMSNorm(x)
-            if self.ep:
+            if self.ep and self.exchange is None:
                 update, _, ids, _ = ep_moe_layer(self.xin, layer, top_k=self.top_k, eps=self.eps, group=self.group)
             else:
                 self.plans[i].launch()

@@ -97,6 +97,21 @@ def _peer_worker(rank, world, port, tokens, failures):
                 assert torch.equal(ids, ids1)
                 torch.testing.assert_close(out, single, atol=2e-5, rtol=1e-4)
             assert exchange.error() == 0
+        if tokens <= 8:
+            # two-layer stack over the same exchange buffers against the single-GPU stack on the full weights
+            from fastkernels_b200.stack import MoEStackPlan
+            fulls = [full, make_moe_weights(5, spec, dtype=torch.bfloat16, device="cuda", bias_std=0.5)]
+            x0 = make_hidden(90, tokens, spec, dtype=torch.float32, device="cuda")      # same tokens on every rank
+            ep_stack = MoEStackPlan([shard_weights(f, rank, world) for f in fulls], tokens, exchange=exchange)
+            got = ep_stack.run(x0).clone()
+            got2 = ep_stack.run(x0).clone()
+            assert torch.equal(got, got2), "stack over peer memory is not repeatable"
+            one = MoEStackPlan(fulls, tokens)
+            want = one.run(x0).clone()
+            for a, b in zip(ep_stack.topk_ids, one.topk_ids):
+                assert torch.equal(a, b)
+            torch.testing.assert_close(got, want, atol=1e-4, rtol=1e-4)
+            assert exchange.error() == 0
         exchange.close()
     except Exception as exc:  # noqa: BLE001
         failures.put(f"rank {rank}: {exc!r}")
