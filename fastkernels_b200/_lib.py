@@ -20,6 +20,7 @@ FLAG_NO_FUSED_DECODE = 8
 FLAG_SKIP_FOREIGN = 16
 FLAG_REGISTER_GEMV = 32
 FLAG_TRACE = 64
+FLAG_WIDE_PASSES = 128
 
 
 class Dims(C.Structure):

@@ -49,7 +49,7 @@ static int check_workspace(const fk_moe_call* c, Workspace& w) {
 // permutation + expert kernels + combine for routing already present in ids/weights
 static int run_experts(const fk_moe_call* c, const Workspace& w, const long long* ids, const float* weights,
                        const float* shared_gate_sig, cudaStream_t stream, const int* ids32 = nullptr,
-                       const EpPeers* ep_peers = nullptr) {
+                       const EpPeers* ep_peers = nullptr, int avg_rows_per_expert = 0) {
     const fk_moe_dims& d = c->dims;
     void* ws = c->workspace;
     PermuteParams pp{};
@@ -94,7 +94,11 @@ static int run_experts(const fk_moe_call* c, const Workspace& w, const long long
                          ((c->flags & FK_FLAG_FORCE_TENSOR) || d.tokens > stream_max_tokens || !stream_ok);
     const bool use_tc = want_tc && (d.tokens >= 64 || (c->flags & FK_FLAG_FORCE_TENSOR)) && tc_path_supported(ep, c->weight_dtype);
     const bool use_stream = !use_tc && stream_ok;
-    pp.pass_rows = use_tc ? 64 : (use_stream ? stream_rows : 4);
+    // 128-token passes are an option (FK_FLAG_WIDE_PASSES), not a default: at 64 tokens per expert (8 ranks x 256
+    // tokens) they halve the passes but leave room for 4 ring stages instead of 7, and measured slower (153 vs 144 us)
+    (void)avg_rows_per_expert;
+    const int tc_rows = (c->flags & FK_FLAG_WIDE_PASSES) ? 128 : 64;
+    pp.pass_rows = use_tc ? tc_rows : (use_stream ? stream_rows : 4);
     int st = launch_permute(pp, stream);
     if (st != FK_OK) return st;
     stage_mark();   // end of permute
@@ -110,7 +114,7 @@ static int run_experts(const fk_moe_call* c, const Workspace& w, const long long
 
     ep.error_word = at<int>(ws, w.meta) + 2;
     if (use_tc)
-        st = launch_experts_tc(ep, at<__nv_bfloat16>(ws, w.xg), at<__nv_bfloat16>(ws, w.actb), stream);
+        st = launch_experts_tc(ep, at<__nv_bfloat16>(ws, w.xg), at<__nv_bfloat16>(ws, w.actb), tc_rows, stream);
     else if (use_stream)
         st = launch_experts_stream(ep, stream);
     else if (!generic && sh_n == d.tokens && gemv_path_supported(ep, c->weight_dtype))
@@ -493,7 +497,7 @@ int fk_moe_layer_ep(const fk_moe_call* c, const fk_ep_comm* comm, void* stream) 
     all.layer_hidden = nullptr;
     st = run_experts(&all, w_all, nullptr, reinterpret_cast<const float*>(mine + lay.weights),
                      gated ? at<float>(c->workspace, w_all.shared_gate) : nullptr, s,
-                     reinterpret_cast<const int*>(mine + lay.ids), &peers);
+                     reinterpret_cast<const int*>(mine + lay.ids), &peers, (int)((long long)G * T * k / c->dims.experts));
     if (st != FK_OK) return st;
 
     // 4. fixed-order sum of the world partials for the own tokens

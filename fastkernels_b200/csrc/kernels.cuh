@@ -108,7 +108,7 @@ int launch_experts_stream(const ExpertParams& p, cudaStream_t stream);
 int stream_pass_rows(const ExpertParams& p);    // 8 when both streaming kernels run their tensor-core consumers, else 4
 // tcgen05 grouped GEMM (bf16, H and I multiples of 128); needs a pass list of <= 64-row passes
 bool tc_path_supported(const ExpertParams& p, int weight_dtype);
-int launch_experts_tc(const ExpertParams& p, __nv_bfloat16* xg, __nv_bfloat16* actb, cudaStream_t stream);
+int launch_experts_tc(const ExpertParams& p, __nv_bfloat16* xg, __nv_bfloat16* actb, int pass_rows, cudaStream_t stream);   // pass_rows 64 or 128
 // ordered weighted combine of the per-row outputs (+ shared expert, + residual)
 int launch_combine(const ExpertParams& p, cudaStream_t stream);
 

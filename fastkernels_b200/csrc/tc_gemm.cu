@@ -27,15 +27,15 @@
 
 namespace fk {
 
-constexpr int kTcStages = 8;              // down: 8 x 24 KB; enough bytes in flight per SM to cover the HBM latency
-constexpr int kTcStagesGU = 7;            // gate_up: 7 x 24 KB beside the 33 KB up-value exchange buffer
-constexpr int kTcStagesMax = kTcStages > kTcStagesGU ? kTcStages : kTcStagesGU;
-constexpr int kTcN = 64;                 // tokens per pass (MMA N, rounded up to 16)
+// NMAX = tokens per pass (MMA N, rounded up to 16): 64 while experts see few tokens (more ring stages, the kernel is
+// a weight stream), 128 when an expert sees dozens of tokens (expert parallel at 8 x 256 tokens: 64 per expert on
+// average, and every pass beyond the first streams the expert's weights again).
+constexpr int kTcStagesMax = 8;
 constexpr int kTcThreads = 192;
 constexpr int kTcTileBytes = 128 * 64 * 2;          // one 128-row x 64-column bf16 operand tile
-constexpr int kTcBBytes = kTcN * 64 * 2;
-constexpr int kTcTmemCols = 128;         // 2 accumulator buffers x 64 columns
-constexpr int kTcUStride = kTcN + 1;     // row stride (floats) of the up-value exchange buffer
+__host__ __device__ constexpr int tc_stages(bool gu, int nmax) { return nmax == 64 ? (gu ? 7 : 8) : (gu ? 4 : 6); }
+__host__ __device__ constexpr int tc_b_bytes(int nmax) { return nmax * 64 * 2; }
+__host__ __device__ constexpr int tc_ustride(int nmax) { return nmax + 1; }   // row stride (floats) of the up-value buffer
 
 struct TcBarriers {
     uint64_t full[kTcStagesMax];
@@ -56,14 +56,17 @@ struct TcParams {
     int H, I;
 };
 
-template <bool GU>
+template <bool GU, int NMAX>
 __global__ void __launch_bounds__(kTcThreads, 1)
 tc_grouped_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ CUtensorMap smap,
                   const __grid_constant__ CUtensorMap amap, TcParams p) {
     extern __shared__ unsigned char smem_dyn[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~uintptr_t(1023));
+    constexpr int kTcBBytes = tc_b_bytes(NMAX);
+    constexpr int kTcUStride = tc_ustride(NMAX);
+    constexpr int kTcTmemCols = 2 * NMAX;                 // two accumulator buffers
     constexpr int kStageBytes = kTcTileBytes + kTcBBytes;
-    constexpr int kNumStages = GU ? kTcStagesGU : kTcStages;
+    constexpr int kNumStages = tc_stages(GU, NMAX);
     TcBarriers& bar = *reinterpret_cast<TcBarriers*>(smem + kNumStages * kStageBytes);
     float* ubuf = reinterpret_cast<float*>(smem + kNumStages * kStageBytes + 1024);   // GU: [2][64][kTcUStride]
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -132,7 +135,7 @@ tc_grouped_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constan
                 const uint32_t acc = ui & 1u;
                 mbar_wait(&bar.tempty[acc], ((ui >> 1) & 1u) ^ 1u, &bar.abort_flag);
                 tc_fence_after_sync();
-                const uint32_t d0 = tmem_base + acc * 64u;
+                const uint32_t d0 = tmem_base + acc * (uint32_t)NMAX;
                 for (int c = 0; c < chunks; ++c, ++it) {
                     const int stage = it % kNumStages;
                     const uint32_t par = (it / kNumStages) & 1u;
@@ -162,7 +165,7 @@ tc_grouped_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constan
             const uint32_t acc = ui & 1u;
             mbar_wait(&bar.tfull[acc], (ui >> 1) & 1u, &bar.abort_flag);
             tc_fence_after_sync();
-            const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + acc * 64u;
+            const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + acc * (uint32_t)NMAX;
             if (GU) {
                 // lanes 64..127 hold the up rows: hand them to the warps that hold the gate rows of the same pairs
                 float* ub = ubuf + (size_t)acc * 64 * kTcUStride;
@@ -309,8 +312,9 @@ bool tc_path_supported(const ExpertParams& p, int weight_dtype) {
     return encode_fn() != nullptr;
 }
 
-// gather -> gate_up GEMM (+SwiGLU) -> down GEMM; the pass list in p.passes must hold passes of <= 64 rows
-int launch_experts_tc(const ExpertParams& p, __nv_bfloat16* xg, __nv_bfloat16* actb, cudaStream_t stream) {
+// gather -> gate_up GEMM (+SwiGLU) -> down GEMM; the pass list in p.passes must hold passes of <= NMAX rows
+template <int NMAX>
+static int launch_experts_tc_t(const ExpertParams& p, __nv_bfloat16* xg, __nv_bfloat16* actb, cudaStream_t stream) {
     if (p.T <= 0) return FK_OK;
     const uint64_t rows = (uint64_t)p.routes + (p.shared_gate_up ? p.shared_n : 0);
     CUtensorMap w_gu, s_gu, a_x, w_dn, s_dn, a_act;
@@ -335,22 +339,26 @@ int launch_experts_tc(const ExpertParams& p, __nv_bfloat16* xg, __nv_bfloat16* a
     TcParams tp{};
     tp.passes = p.passes; tp.meta = p.meta; tp.actb = actb; tp.y = p.y; tp.error_word = p.error_word; tp.H = p.H; tp.I = p.I;
     {
-        auto kern = tc_grouped_kernel<true>;
-        const int smem = kTcStagesGU * (kTcTileBytes + kTcBBytes) + 1024 + 2 * 64 * kTcUStride * (int)sizeof(float) + 1024;
+        auto kern = tc_grouped_kernel<true, NMAX>;
+        const int smem = tc_stages(true, NMAX) * (kTcTileBytes + tc_b_bytes(NMAX)) + 1024 + 2 * 64 * tc_ustride(NMAX) * (int)sizeof(float) + 1024;
         FK_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem), "tc gate_up attr");
         FK_CUDA_OK(launch_pdl(kern, dim3(sm_count()), dim3(kTcThreads), (size_t)smem, stream, w_gu, s_gu, a_x, tp), "tc gate_up launch");
         FK_LAUNCH_OK("tc gate_up launch");
     }
     stage_mark();   // end of gate_up
     {
-        auto kern = tc_grouped_kernel<false>;
-        const int smem = kTcStages * (kTcTileBytes + kTcBBytes) + 1024 + 1024;
+        auto kern = tc_grouped_kernel<false, NMAX>;
+        const int smem = tc_stages(false, NMAX) * (kTcTileBytes + tc_b_bytes(NMAX)) + 1024 + 1024;
         FK_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem), "tc down attr");
         FK_CUDA_OK(launch_pdl(kern, dim3(sm_count()), dim3(kTcThreads), (size_t)smem, stream, w_dn, s_dn, a_act, tp), "tc down launch");
         FK_LAUNCH_OK("tc down launch");
     }
     stage_mark();   // end of down
     return FK_OK;
+}
+
+int launch_experts_tc(const ExpertParams& p, __nv_bfloat16* xg, __nv_bfloat16* actb, int pass_rows, cudaStream_t stream) {
+    return pass_rows > 64 ? launch_experts_tc_t<128>(p, xg, actb, stream) : launch_experts_tc_t<64>(p, xg, actb, stream);
 }
 
 }  // namespace fk

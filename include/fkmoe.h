@@ -62,6 +62,7 @@ typedef struct fk_moe_dims {
 #define FK_FLAG_TRACE 64u          /* T==1 fused kernel: write per-block phase timestamps (ns) at the start of the
                                       workspace's y region: u64 [blocks][8]; fk_moe_trace_offset() gives the offset */
 #define FK_FLAG_SKIP_FOREIGN 16u   /* ids outside [expert_base, expert_base+E) are skipped instead of clamped */
+#define FK_FLAG_WIDE_PASSES 128u   /* tcgen05 path: 128 tokens per pass instead of 64 (experts that see dozens of tokens) */
 
 typedef struct fk_moe_call {
     fk_moe_dims dims;

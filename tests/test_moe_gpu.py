@@ -634,6 +634,28 @@ def test_peer_memory_layer_with_one_rank_equals_the_plain_layer(real_bf16_biased
                 assert torch.equal(out, want)
             assert exchange.error() == 0
             exchange.close()
+        # many tokens per expert (32 experts, 600 tokens: 150 each) through the tcgen05 kernels, and the same with
+        # 128-token passes: the rows must not depend on how an expert's tokens are split into passes
+        spec32 = MoESpec(num_experts=32)
+        w32 = make_moe_weights(9, spec32, dtype=torch.bfloat16, device="cuda", bias_std=0.5)
+        tokens = 600
+        exchange = PeerExchange(tokens, spec32.hidden_size, 8, torch.bfloat16)
+        layer = PeerEPLayer(shard_weights(w32, 0, 1), exchange, tokens)
+        hidden = make_hidden(12, tokens, spec32, dtype=torch.bfloat16, device="cuda")
+        out, logits, ids, weights = layer.run(hidden)
+        want, _, want_ids, _ = triton_qwen36_batched_moe_decode(hidden, *w32.tuple(), router_bias=w32.router_bias)
+        assert torch.equal(ids, want_ids) and torch.equal(out, want)
+        wide, _, wide_ids, _ = triton_qwen36_batched_moe_decode(hidden, *w32.tuple(), router_bias=w32.router_bias,
+                                                                flags=_lib.FLAG_WIDE_PASSES)
+        assert torch.equal(wide_ids, want_ids) and torch.equal(wide, want)
+        sample = torch.arange(0, tokens, 75)
+        ref = oracle_layer(hidden[sample.cuda()], w32, 8)
+        clear = ref.margin > 2e-6
+        assert torch.equal(ids.cpu()[sample][clear], ref.topk_ids[clear])
+        if bool(clear.all()):
+            check_output(out[sample.cuda()], ref.output, torch.bfloat16)
+        assert exchange.error() == 0
+        exchange.close()
     finally:
         if created:
             dist.destroy_process_group()
