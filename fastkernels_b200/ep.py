@@ -223,16 +223,32 @@ class PeerExchange:
         self.comm = _lib.EpComm()
         self.comm.rank, self.comm.world, self.comm.tokens_per_rank, self.comm.bytes = self.rank, self.world, tokens_per_rank, self.bytes
         self._opened = []
+        failure = None
         for r in range(self.world):
             if r == self.rank:
                 self.comm.base[r] = self.own
-            else:
-                ptr = C.c_void_p()
+                continue
+            ptr = C.c_void_p()
+            try:
                 _lib.check(self.lib.fk_ep_buffer_open(C.create_string_buffer(handles[r], _lib.EP_HANDLE_BYTES), C.byref(ptr)),
                            "fk_ep_buffer_open")
-                self.comm.base[r] = ptr.value
-                self._opened.append(ptr.value)
-        dist.barrier(group=group)          # every rank has mapped every buffer before anyone stores into one
+            except RuntimeError as exc:          # e.g. no peer access between the two GPUs
+                failure = str(exc)
+                break
+            self.comm.base[r] = ptr.value
+            self._opened.append(ptr.value)
+        # every rank learns whether every rank has mapped every buffer, before anyone stores into one (and so that a
+        # failure on one rank does not leave the others waiting)
+        outcomes = [None] * self.world
+        dist.all_gather_object(outcomes, failure, group=group)
+        if any(o is not None for o in outcomes):
+            for ptr in self._opened:
+                self.lib.fk_ep_buffer_close(ptr)
+            self._opened = []
+            dist.barrier(group=group)
+            self.lib.fk_ep_buffer_destroy(self.own)
+            self.own = None
+            raise RuntimeError("peer memory exchange unavailable: " + "; ".join(f"rank {i}: {o}" for i, o in enumerate(outcomes) if o))
 
     def error(self) -> int:
         """Synchronises the device; non-zero if a wait on a peer ever gave up (1: dispatch, 2: combine)."""

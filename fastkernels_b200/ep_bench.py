@@ -50,10 +50,16 @@ def run_ep(args, workload_config, measured_peak, ClockSampler, METRIC, UNIT):
 
     # default: exchange over peer memory inside the library's own kernels; --ep-nccl: NCCL collectives from torch
     exchange = None
+    exchange_note = None
+    if not args.ep_nccl:
+        try:
+            exchange = PeerExchange(B, H, 8, torch.bfloat16)
+        except RuntimeError as exc:              # raised on every rank together: fall back to the collective library
+            exchange_note = str(exc)
+            args.ep_nccl = True
     if args.ep_nccl:
         plans = [EPDecodePlan(sh, B, capture=not args.ep_eager) for sh in shards]
     else:
-        exchange = PeerExchange(B, H, 8, torch.bfloat16)
         plans = [PeerEPLayer(sh, exchange, B, capture=not args.ep_eager) for sh in shards]
     for i, pl in enumerate(plans):              # inputs are resident before the timed region starts
         pl.hidden.copy_(hid_dev[i % pool])
@@ -167,6 +173,8 @@ def run_ep(args, workload_config, measured_peak, ClockSampler, METRIC, UNIT):
         }
         if stack is not None:
             line["stack"] = stack
+        if exchange_note:
+            line["config"]["exchange_note"] = exchange_note
         line["config"]["exchange"] = "NCCL all-gather + all-to-all" if args.ep_nccl else \
             "peer-memory stores + flags inside the library's kernels (CUDA IPC over NVLink), no collective call"
         print(json.dumps(line), flush=True)
