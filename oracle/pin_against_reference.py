@@ -113,7 +113,7 @@ def pin_weight_packer(reference_path: str) -> None:
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="path of the reference checkout")
     ap.add_argument("--write", action="store_true")
     args = ap.parse_args()
     R, ref_rms, RefWeights, ref_real_spec, ref_tiny_spec, ref_make_tiny = load_reference(args.reference)
