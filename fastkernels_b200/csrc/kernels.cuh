@@ -41,6 +41,7 @@ struct PermuteParams {
     int shared_tokens;        // tokens the shared expert sees (0: no shared expert)
     int shared_tok0;          // first of them
     int pass_rows;            // rows per pass: 4 or 8 for the GEMV kernels, 64 for the tensor-core GEMM
+    int cache_routes;         // set by the launcher: routes whose local expert ids fit in shared memory (0: none)
 };
 int launch_permute(const PermuteParams& p, cudaStream_t stream);
 int launch_histogram(const void* ids, int ids_are_int64, long long count, int E, int* counts, cudaStream_t stream);

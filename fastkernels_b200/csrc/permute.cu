@@ -39,11 +39,21 @@ __global__ void __launch_bounds__(kPermWarps * 32) permute_kernel(PermuteParams 
 
     const int seg = (R + NW - 1) / NW;
     const int seg_lo = min(R, warp * seg), seg_hi = min(R, seg_lo + seg);
-    for (int base = seg_lo; base < seg_hi; base += 32) {
-        int r = base + lane;
-        if (r < seg_hi) {
-            int lid = local_expert(p, r);
-            if (lid >= 0) atomicAdd(&whist[warp * E + lid], 1);
+    // The local expert of every route is kept in shared memory for the placement pass (when it fits), and the ids are
+    // fetched four groups at a time: with thousands of routes the kernel was two serial chains of global loads.
+    short* lid_cache = p.cache_routes >= R ? reinterpret_cast<short*>(offs + E + 2) : nullptr;
+    for (int base = seg_lo; base < seg_hi; base += 128) {
+        int lid[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int r = base + j * 32 + lane;
+            lid[j] = r < seg_hi ? local_expert(p, r) : -1;
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int r = base + j * 32 + lane;
+            if (lid[j] >= 0) atomicAdd(&whist[warp * E + lid[j]], 1);
+            if (lid_cache && r < seg_hi) lid_cache[r] = (short)lid[j];
         }
     }
     __syncthreads();
@@ -114,7 +124,8 @@ __global__ void __launch_bounds__(kPermWarps * 32) permute_kernel(PermuteParams 
     // stable placement
     for (int base = seg_lo; base < seg_hi; base += 32) {
         int r = base + lane;
-        int lid = (r < seg_hi) ? local_expert(p, r) : -1;
+        int lid = -1;
+        if (r < seg_hi) lid = lid_cache ? (int)lid_cache[r] : local_expert(p, r);
         unsigned peers = __match_any_sync(kFull, lid);
         int pos = -1;
         if (lid >= 0) {
@@ -136,9 +147,15 @@ int launch_permute(const PermuteParams& p, cudaStream_t stream) {
     // a short dependency chain matters more than width while there are few routes; E must fit the block
     const int warps = (p.routes <= 768 && p.E <= 256) ? 8 : kPermWarps;
     size_t smem = sizeof(int) * ((size_t)warps * p.E + p.E + 2);
-    FK_CUDA_OK(cudaFuncSetAttribute(permute_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                    (int)(sizeof(int) * ((size_t)kPermWarps * p.E + p.E + 2))), "permute attr");
-    FK_CUDA_OK(launch_pdl(permute_kernel, dim3(1), dim3(warps * 32), smem, stream, p), "permute launch");
+    PermuteParams q = p;
+    q.cache_routes = 0;
+    const size_t cache = ((size_t)p.routes * sizeof(short) + 15) & ~size_t(15);
+    if (p.E < 32767 && smem + cache <= 200 * 1024) {      // local expert ids of all routes next to the histograms
+        q.cache_routes = p.routes;
+        smem += cache;
+    }
+    FK_CUDA_OK(cudaFuncSetAttribute(permute_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), "permute attr");
+    FK_CUDA_OK(launch_pdl(permute_kernel, dim3(1), dim3(warps * 32), smem, stream, q), "permute launch");
     FK_LAUNCH_OK("permute launch");
     return FK_OK;
 }
