@@ -501,8 +501,8 @@ int fk_moe_layer_ep(const fk_moe_call* c, const fk_ep_comm* comm, void* stream) 
     if (st != FK_OK) return st;
 
     // 4. fixed-order sum of the world partials for the own tokens
-    return launch_ep_reduce(reinterpret_cast<const float*>(mine + lay.partial), G, T, H, c->out, c->layer_hidden, c->hidden,
-                            c->hidden_dtype, s);
+    return launch_ep_reduce(reinterpret_cast<const float*>(mine + lay.partial), G, rank, T, H, rp.topk_ids, k, e_local,
+                            c->shared_gate_up != nullptr ? 1 : 0, c->out, c->layer_hidden, c->hidden, c->hidden_dtype, s);
 }
 
 int fk_single_expert_mlp(const void* hidden, int hidden_dtype, const void* gate_up, const void* down, int weight_dtype,

@@ -8,7 +8,9 @@
 //   hidden   [world*T, H]   activations of every rank's tokens, rank-major
 //   ids      [world*T, k]   i32 global expert ids
 //   weights  [world*T, k]   f32 routing weights
-//   partial  [world, T, H]  f32: slice g holds rank g's partial rows for THIS rank's tokens
+//   partial  [world, T, H]  f32: slice g holds rank g's partial rows for THIS rank's tokens; a row is written only
+//                           if rank g holds one of the token's experts (or is the home rank running the shared
+//                           expert): the home rank derives the same set from the token's ids and reads nothing else
 //
 // Dispatch: each rank stores its own rows into slot `rank` of every buffer (plain 16-byte stores to peer
 // memory), fences at system scope, and the last block to finish publishes the rank's new epoch in every
@@ -163,6 +165,12 @@ __global__ void __launch_bounds__(256) combine_ep_kernel(ExpertParams p) {
             }
         }
         if (shared) { acc.x += gate * sh.x; acc.y += gate * sh.y; acc.z += gate * sh.z; acc.w += gate * sh.w; }
+        // a token none of whose experts live here (and that is not one of this rank's own, shared-expert tokens)
+        // gets no row from this rank: its home rank knows from the token's ids and skips the slot
+        bool any = shared;
+#pragma unroll
+        for (int s = 0; s < FK_MAX_TOP_K; ++s) any = any || pos[s] >= 0;
+        if (!any) continue;
         const int home = t / ep.tokens, tl = t - home * ep.tokens;
         float* dst = reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(ep.header[home]) + ep.partial_offset) +
                      ((size_t)ep.rank * ep.tokens + tl) * p.H + h;
@@ -171,17 +179,26 @@ __global__ void __launch_bounds__(256) combine_ep_kernel(ExpertParams p) {
     if (ep_last_block(ep.header[ep.rank] + 19)) ep_signal_and_wait(ep, 8, 17);
 }
 
-// out[t] = sum over ranks g (ascending) of partial[g][t]  (+ hidden[t] into layer_hidden)
-__global__ void __launch_bounds__(256) ep_reduce_kernel(const float* partial, int world, int T, int H, float* out, float* layer_hidden,
-                                                        const void* hidden, int hidden_dtype) {
+// out[t] = sum over the ranks g (ascending) that hold one of token t's experts, plus this rank when it ran the shared
+// expert for t, of partial[g][t]  (+ hidden[t] into layer_hidden).  Slots of other ranks were not written.
+__global__ void __launch_bounds__(256) ep_reduce_kernel(const float* partial, int world, int rank, int T, int H, const long long* ids,
+                                                        int top_k, int experts_per_rank, int own_always, float* out,
+                                                        float* layer_hidden, const void* hidden, int hidden_dtype) {
     pdl_trigger();
     pdl_wait();
     const int H4 = H >> 2;
     const long long total = (long long)T * H4;
     for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
         const size_t o = (size_t)i * 4;
-        float4 acc = *reinterpret_cast<const float4*>(partial + o);
-        for (int g = 1; g < world; ++g) {
+        const int t = (int)(i / H4);
+        unsigned mask = own_always ? (1u << rank) : 0u;
+        for (int s = 0; s < top_k; ++s) {
+            const long long e = ids[(size_t)t * top_k + s];
+            if (e >= 0 && e < (long long)experts_per_rank * world) mask |= 1u << (int)(e / experts_per_rank);
+        }
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int g = 0; g < world; ++g) {
+            if (!((mask >> g) & 1u)) continue;
             const float4 v = *reinterpret_cast<const float4*>(partial + (size_t)g * T * H + o);
             acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
         }
@@ -215,14 +232,14 @@ int launch_combine_ep(const ExpertParams& p, cudaStream_t stream) {
     return FK_OK;
 }
 
-int launch_ep_reduce(const float* partial, int world, int T, int H, float* out, float* layer_hidden, const void* hidden,
-                     int hidden_dtype, cudaStream_t stream) {
+int launch_ep_reduce(const float* partial, int world, int rank, int T, int H, const long long* ids, int top_k, int experts_per_rank,
+                     int own_always, float* out, float* layer_hidden, const void* hidden, int hidden_dtype, cudaStream_t stream) {
     const long long total = (long long)T * (H / 4);
     int blocks = (int)((total + 255) / 256);
     if (blocks > 148 * 8) blocks = 148 * 8;
     if (blocks < 1) blocks = 1;
-    FK_CUDA_OK(launch_pdl(ep_reduce_kernel, dim3(blocks), dim3(256), 0, stream, partial, world, T, H, out, layer_hidden, hidden,
-                          hidden_dtype), "ep reduce launch");
+    FK_CUDA_OK(launch_pdl(ep_reduce_kernel, dim3(blocks), dim3(256), 0, stream, partial, world, rank, T, H, ids, top_k,
+                          experts_per_rank, own_always, out, layer_hidden, hidden, hidden_dtype), "ep reduce launch");
     FK_LAUNCH_OK("ep reduce launch");
     return FK_OK;
 }

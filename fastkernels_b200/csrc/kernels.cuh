@@ -68,8 +68,8 @@ struct EpDispatchParams {
     int T, H, top_k, elem_bytes;
 };
 int launch_ep_dispatch(const EpDispatchParams& p, cudaStream_t stream);
-int launch_ep_reduce(const float* partial, int world, int T, int H, float* out, float* layer_hidden, const void* hidden,
-                     int hidden_dtype, cudaStream_t stream);
+int launch_ep_reduce(const float* partial, int world, int rank, int T, int H, const long long* ids, int top_k, int experts_per_rank,
+                     int own_always, float* out, float* layer_hidden, const void* hidden, int hidden_dtype, cudaStream_t stream);
 
 struct ExpertParams {
     const void* hidden;

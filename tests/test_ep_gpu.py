@@ -97,6 +97,24 @@ def _peer_worker(rank, world, port, tokens, failures):
                 assert torch.equal(ids, ids1)
                 torch.testing.assert_close(out, single, atol=2e-5, rtol=1e-4)
             assert exchange.error() == 0
+        # top-2 routing: half of the tokens have both experts on one rank, so the other rank sends no row for them
+        # and the home rank must leave that slot out of its sum
+        ex2 = PeerExchange(tokens, spec.hidden_size, 2, torch.bfloat16)
+        layer2 = PeerEPLayer(shard, ex2, tokens, top_k=2)
+        lonely = 0
+        for step in range(3):
+            hidden = make_hidden(170 + rank + 10 * step, tokens, spec, dtype=torch.bfloat16, device="cuda")
+            out, _, ids, weights = layer2.run(hidden)
+            out, ids = out.clone(), ids.clone()
+            ref_out, _, ref_ids, _ = ep_moe_layer(hidden, shard, top_k=2)
+            assert torch.equal(ids, ref_ids)
+            torch.testing.assert_close(out, ref_out, atol=2e-5, rtol=1e-4)
+            lonely += int(((ids // (spec.num_experts // world)).min(dim=1).values ==
+                           (ids // (spec.num_experts // world)).max(dim=1).values).sum())
+        assert ex2.error() == 0
+        assert tokens < 16 or lonely > 0, "no token was routed to a single rank: the case was not exercised"
+        del layer2
+        ex2.close()
         if tokens <= 8:
             # two-layer stack over the same exchange buffers against the single-GPU stack on the full weights
             from fastkernels_b200.stack import MoEStackPlan
