@@ -270,6 +270,10 @@ int fk_moe_experts(const fk_moe_call* c, void* stream) {
     return run_experts(c, w, reinterpret_cast<const long long*>(c->topk_ids_in), c->topk_weights_in, gate_sig, s);
 }
 
+// fk_moe_layer_host hands the caller's pinned ids / weights buffers to the routing kernels through these
+static thread_local long long* t_ids_mirror = nullptr;
+static thread_local float* t_weights_mirror = nullptr;
+
 int fk_moe_layer(const fk_moe_call* c, void* stream) {
     if (c == nullptr || !dims_ok(c->dims, true) || c->dims.top_k > c->dims.experts) return FK_ERR_ARG;
     if (!dtype_ok(c->hidden_dtype) || !dtype_ok(c->weight_dtype)) return FK_ERR_UNSUPPORTED;
@@ -290,6 +294,7 @@ int fk_moe_layer(const fk_moe_call* c, void* stream) {
     rp.shared_gate_out = gated ? at<float>(c->workspace, w.shared_gate) : nullptr;
     rp.logits = c->logits; rp.topk_ids = reinterpret_cast<long long*>(c->topk_ids); rp.topk_weights = c->topk_weights;
     rp.ids32 = nullptr;
+    rp.ids_mirror = t_ids_mirror; rp.weights_mirror = t_weights_mirror;
     rp.tickets = at<unsigned>(c->workspace, w.tickets);
     rp.T = c->dims.tokens; rp.H = c->dims.hidden; rp.E = c->dims.experts; rp.top_k = c->dims.top_k;
     rp.eps = c->eps; rp.norm_offset = c->norm_offset;
@@ -303,6 +308,7 @@ int fk_moe_layer(const fk_moe_call* c, void* stream) {
         dp.shared_gate = gated ? c->shared_gate : nullptr;
         dp.logits = c->logits; dp.topk_ids = reinterpret_cast<long long*>(c->topk_ids); dp.topk_weights = c->topk_weights;
         dp.out = c->out; dp.layer_hidden = c->layer_hidden;
+        dp.ids_mirror = t_ids_mirror; dp.weights_mirror = t_weights_mirror;
         dp.ract = at<float>(c->workspace, w.act);
         dp.sact = dp.ract + (size_t)c->dims.top_k * c->dims.intermediate;
         dp.sgate = at<float>(c->workspace, w.shared_gate);
@@ -365,14 +371,22 @@ int fk_moe_layer_host(const fk_moe_call* c, void* staging, size_t staging_bytes,
     dev.hidden = d_hidden; dev.out = out_alias ? out_alias : d_out;
     dev.layer_hidden = c->layer_hidden ? (layer_alias ? layer_alias : d_layer) : nullptr;
     dev.logits = d_logits; dev.topk_ids = d_ids; dev.topk_weights = d_w;
+    // ids and weights are small: when the caller's buffers are pinned, the routing kernel writes a second copy there
+    long long* ids_alias = (long long*)mapped_alias(c->topk_ids);
+    float* w_alias = (float*)mapped_alias(c->topk_weights);
+    t_ids_mirror = ids_alias;
+    t_weights_mirror = w_alias;
     int st = fk_moe_layer(&dev, stream);
+    t_ids_mirror = nullptr;
+    t_weights_mirror = nullptr;
     if (st != FK_OK) return st;
     if (!out_alias) FK_CUDA_OK(cudaMemcpyAsync(c->out, d_out, T * H * 4, cudaMemcpyDeviceToHost, s), "d2h out");
     if (c->layer_hidden && !layer_alias)
         FK_CUDA_OK(cudaMemcpyAsync(c->layer_hidden, d_layer, T * H * 4, cudaMemcpyDeviceToHost, s), "d2h layer");
     if (c->logits) FK_CUDA_OK(cudaMemcpyAsync(c->logits, d_logits, T * E * 4, cudaMemcpyDeviceToHost, s), "d2h logits");
-    if (c->topk_ids) FK_CUDA_OK(cudaMemcpyAsync(c->topk_ids, d_ids, T * k * 8, cudaMemcpyDeviceToHost, s), "d2h ids");
-    if (c->topk_weights) FK_CUDA_OK(cudaMemcpyAsync(c->topk_weights, d_w, T * k * 4, cudaMemcpyDeviceToHost, s), "d2h weights");
+    if (c->topk_ids && !ids_alias) FK_CUDA_OK(cudaMemcpyAsync(c->topk_ids, d_ids, T * k * 8, cudaMemcpyDeviceToHost, s), "d2h ids");
+    if (c->topk_weights && !w_alias)
+        FK_CUDA_OK(cudaMemcpyAsync(c->topk_weights, d_w, T * k * 4, cudaMemcpyDeviceToHost, s), "d2h weights");
     return FK_OK;
 }
 

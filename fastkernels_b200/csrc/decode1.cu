@@ -303,6 +303,8 @@ __device__ __forceinline__ void block_topk(const DecodeParams& p, D1Smem& s, flo
         if (write_global) {
             p.topk_ids[ctid] = s.ids[ctid];
             p.topk_weights[ctid] = wgt;
+            if (p.ids_mirror) p.ids_mirror[ctid] = s.ids[ctid];
+            if (p.weights_mirror) p.weights_mirror[ctid] = wgt;
         }
         s.wnorm[ctid] = wgt;
     }

@@ -17,6 +17,8 @@ struct RouterParams {
     float* topk_weights;
     int* ids32;                        // optional int32 copy of the ids (workspace)
     float* shared_gate_out;            // optional f32 [T]
+    long long* ids_mirror;             // optional second copy of ids / weights (e.g. the caller's pinned host buffers)
+    float* weights_mirror;
     unsigned* tickets;
     int T, H, E, top_k;
     float eps, norm_offset;
@@ -128,6 +130,8 @@ struct DecodeParams {
     float* logits;                // [E]
     long long* topk_ids;          // [k]
     float* topk_weights;          // [k]
+    long long* ids_mirror;        // optional second copy of ids / weights (the caller's pinned host buffers)
+    float* weights_mirror;
     float* out;                   // [H]
     float* layer_hidden;          // optional [H]
     float* ract;                  // workspace [k, I]

@@ -204,8 +204,10 @@ router_kernel(RouterParams p) {
         long long* ids = p.topk_ids + (size_t)token * p.top_k;
         int* ids32 = p.ids32 ? p.ids32 + (size_t)token * p.top_k : nullptr;
         float* wts = p.topk_weights + (size_t)token * p.top_k;
-        if (E <= 256) topk_warp<8>(row, E, p.top_k, ids, ids32, wts);
-        else topk_warp<32>(row, E, p.top_k, ids, ids32, wts);
+        long long* ids2 = p.ids_mirror ? p.ids_mirror + (size_t)token * p.top_k : nullptr;
+        float* wts2 = p.weights_mirror ? p.weights_mirror + (size_t)token * p.top_k : nullptr;
+        if (E <= 256) topk_warp<8>(row, E, p.top_k, ids, ids32, wts, wts2, ids2);
+        else topk_warp<32>(row, E, p.top_k, ids, ids32, wts, wts2, ids2);
     }
 }
 
@@ -389,8 +391,10 @@ __global__ void __launch_bounds__(kRouterWarps * 32) router_fast_kernel(RouterPa
         long long* ids = p.topk_ids + (size_t)token * p.top_k;
         int* ids32 = p.ids32 ? p.ids32 + (size_t)token * p.top_k : nullptr;
         float* wts = p.topk_weights + (size_t)token * p.top_k;
-        if (E <= 256) topk_warp<8>(row, E, p.top_k, ids, ids32, wts);
-        else topk_warp<32>(row, E, p.top_k, ids, ids32, wts);
+        long long* ids2 = p.ids_mirror ? p.ids_mirror + (size_t)token * p.top_k : nullptr;
+        float* wts2 = p.weights_mirror ? p.weights_mirror + (size_t)token * p.top_k : nullptr;
+        if (E <= 256) topk_warp<8>(row, E, p.top_k, ids, ids32, wts, wts2, ids2);
+        else topk_warp<32>(row, E, p.top_k, ids, ids32, wts, wts2, ids2);
     }
 }
 
@@ -603,8 +607,10 @@ __global__ void __launch_bounds__(kRmWarps * 32, 1) router_mma_kernel(RouterPara
         long long* ids = p.topk_ids + (size_t)token * p.top_k;
         int* ids32 = p.ids32 ? p.ids32 + (size_t)token * p.top_k : nullptr;
         float* wts = p.topk_weights + (size_t)token * p.top_k;
-        if (E <= 256) topk_warp<8>(row, E, p.top_k, ids, ids32, wts);
-        else topk_warp<32>(row, E, p.top_k, ids, ids32, wts);
+        long long* ids2 = p.ids_mirror ? p.ids_mirror + (size_t)token * p.top_k : nullptr;
+        float* wts2 = p.weights_mirror ? p.weights_mirror + (size_t)token * p.top_k : nullptr;
+        if (E <= 256) topk_warp<8>(row, E, p.top_k, ids, ids32, wts, wts2, ids2);
+        else topk_warp<32>(row, E, p.top_k, ids, ids32, wts, wts2, ids2);
     }
 }
 

@@ -9,7 +9,7 @@ namespace fk {
 // softmax + top-k of one token's logits by one warp.  EPL = experts per lane (E <= 32*EPL).
 template <int EPL>
 __device__ void topk_warp(const float* __restrict__ logits_row, int E, int top_k, long long* ids_out,
-                          int* ids32_out, float* weights_out, float* weights_out2 = nullptr) {
+                          int* ids32_out, float* weights_out, float* weights_out2 = nullptr, long long* ids_out2 = nullptr) {
     const int lane = threadIdx.x & 31;
     float v[EPL];
     float m = -INFINITY;
@@ -61,6 +61,7 @@ __device__ void topk_warp(const float* __restrict__ logits_row, int E, int top_k
     if (lane < top_k) {
         const float w = my_v / total;
         if (ids_out) ids_out[lane] = my_i;
+        if (ids_out2) ids_out2[lane] = my_i;
         if (ids32_out) ids32_out[lane] = my_i;
         if (weights_out) weights_out[lane] = w;
         if (weights_out2) weights_out2[lane] = w;
