@@ -216,10 +216,20 @@ class PeerExchange:
             raise ValueError("exchange buffer: arguments outside the supported limits")
         own = C.c_void_p()
         handle = C.create_string_buffer(_lib.EP_HANDLE_BYTES)
-        _lib.check(self.lib.fk_ep_buffer_create(self.bytes, C.byref(own), handle), "fk_ep_buffer_create")
+        created = None
+        try:
+            _lib.check(self.lib.fk_ep_buffer_create(self.bytes, C.byref(own), handle), "fk_ep_buffer_create")
+        except RuntimeError as exc:              # reported to every rank below, so that nobody waits for this one
+            created = str(exc)
         self.own = own.value
         handles = [None] * self.world
-        dist.all_gather_object(handles, bytes(handle.raw), group=group)
+        dist.all_gather_object(handles, created if created is not None else bytes(handle.raw), group=group)
+        if any(isinstance(h, str) for h in handles):
+            if self.own:
+                self.lib.fk_ep_buffer_destroy(self.own)
+            self.own = None
+            raise RuntimeError("peer memory exchange unavailable: " +
+                               "; ".join(f"rank {i}: {h}" for i, h in enumerate(handles) if isinstance(h, str)))
         self.comm = _lib.EpComm()
         self.comm.rank, self.comm.world, self.comm.tokens_per_rank, self.comm.bytes = self.rank, self.world, tokens_per_rank, self.bytes
         self._opened = []
