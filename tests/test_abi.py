@@ -65,3 +65,26 @@ def test_calls_reject_null_pointers_without_a_gpu():
     assert lib.fk_moe_layer(None, None) == 1
     with pytest.raises(RuntimeError, match="invalid argument"):
         _lib.check(1, "probe")
+
+
+def test_expert_parallel_entry_points_check_arguments_without_a_gpu():
+    lib = _lib.load()
+    b2 = lib.fk_ep_buffer_bytes(2, 32, 2048, 8, _lib.FK_BF16)
+    b8 = lib.fk_ep_buffer_bytes(8, 32, 2048, 8, _lib.FK_BF16)
+    # header + gathered activations (bf16) + routing (ids, weights) + partial rows (fp32), each 256-byte aligned
+    assert b2 == 256 + 2 * 32 * 2048 * 2 + 2 * (2 * 32 * 8 * 4) + 2 * 32 * 2048 * 4
+    assert b8 > b2 and b8 % 256 == 0
+    assert lib.fk_ep_buffer_bytes(9, 32, 2048, 8, _lib.FK_BF16) == 0         # more ranks than one node has GPUs
+    assert lib.fk_ep_buffer_bytes(2, 0, 2048, 8, _lib.FK_BF16) == 0
+    assert lib.fk_ep_buffer_bytes(2, 32, 2048, 9, _lib.FK_BF16) == 0
+    call = Call()
+    call.dims = Dims(32, 2048, 256, 512, 8)
+    call.hidden_dtype = call.weight_dtype = _lib.FK_BF16
+    comm = _lib.EpComm()
+    comm.rank, comm.world, comm.tokens_per_rank = 0, 2, 32
+    assert lib.fk_moe_layer_ep(C.byref(call), C.byref(comm), None) == 1      # FK_ERR_ARG: null tensors
+    assert lib.fk_moe_layer_ep(C.byref(call), None, None) == 1
+    comm.tokens_per_rank = 16
+    assert lib.fk_moe_layer_ep(C.byref(call), C.byref(comm), None) == 1      # token count differs from the buffers'
+    assert lib.fk_ep_buffer_open(None, None) == 1
+    assert lib.fk_ep_buffer_close(None) == 0 and lib.fk_ep_buffer_destroy(None) == 0
