@@ -78,6 +78,7 @@ SIGNATURES = {
     "fk_expert_histogram": (C.c_int, [C.c_void_p, C.c_int, C.c_int64, C.c_int, C.c_void_p, C.c_void_p]),
     "fk_moe_permute": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p,
                                  C.c_void_p, C.c_size_t, C.c_void_p]),
+    "fk_moe_layer_residual": (C.c_int, [C.POINTER(Call), C.c_void_p, C.c_void_p, C.c_void_p, C.c_float, C.c_void_p]),
     "fk_ep_buffer_bytes": (C.c_size_t, [C.c_int, C.c_int, C.c_int, C.c_int, C.c_int]),
     "fk_ep_buffer_create": (C.c_int, [C.c_size_t, C.POINTER(C.c_void_p), C.c_void_p]),
     "fk_ep_buffer_open": (C.c_int, [C.c_void_p, C.POINTER(C.c_void_p)]),

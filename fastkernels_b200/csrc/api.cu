@@ -273,6 +273,11 @@ int fk_moe_experts(const fk_moe_call* c, void* stream) {
 // fk_moe_layer_host hands the caller's pinned ids / weights buffers to the routing kernels through these
 static thread_local long long* t_ids_mirror = nullptr;
 static thread_local float* t_weights_mirror = nullptr;
+// fk_moe_layer_residual hands the residual stream to the single-token kernel through these
+static thread_local const float* t_resid_in = nullptr;
+static thread_local const float* t_update_in = nullptr;
+static thread_local float* t_resid_out = nullptr;
+static thread_local float t_resid_eps = 0.f;
 
 int fk_moe_layer(const fk_moe_call* c, void* stream) {
     if (c == nullptr || !dims_ok(c->dims, true) || c->dims.top_k > c->dims.experts) return FK_ERR_ARG;
@@ -309,6 +314,7 @@ int fk_moe_layer(const fk_moe_call* c, void* stream) {
         dp.logits = c->logits; dp.topk_ids = reinterpret_cast<long long*>(c->topk_ids); dp.topk_weights = c->topk_weights;
         dp.out = c->out; dp.layer_hidden = c->layer_hidden;
         dp.ids_mirror = t_ids_mirror; dp.weights_mirror = t_weights_mirror;
+        dp.resid_in = t_resid_in; dp.update_in = t_update_in; dp.resid_out = t_resid_out; dp.resid_eps = t_resid_eps;
         dp.ract = at<float>(c->workspace, w.act);
         dp.sact = dp.ract + (size_t)c->dims.top_k * c->dims.intermediate;
         dp.sgate = at<float>(c->workspace, w.shared_gate);
@@ -323,10 +329,24 @@ int fk_moe_layer(const fk_moe_call* c, void* stream) {
             return st;
         }
     }
+    if (t_resid_in) return FK_ERR_UNSUPPORTED;      // the residual form exists for the single-token kernel only
     st = launch_router(rp, c->weight_dtype, s);
     if (st != FK_OK) return st;
     stage_mark();   // end of router
     return run_experts(c, w, rp.topk_ids, c->topk_weights, rp.shared_gate_out, s);
+}
+
+int fk_moe_layer_residual(const fk_moe_call* c, const float* resid_in, const float* update_in, float* resid_out,
+                          float norm_eps, void* stream) {
+    if (c == nullptr || resid_in == nullptr || resid_out == nullptr || resid_out == resid_in) return FK_ERR_ARG;
+    if (c->dims.tokens != 1) return FK_ERR_UNSUPPORTED;
+    t_resid_in = resid_in; t_update_in = update_in; t_resid_out = resid_out; t_resid_eps = norm_eps;
+    fk_moe_call call = *c;
+    if (call.hidden == nullptr) call.hidden = resid_in;       // not read in this form; keeps the argument check simple
+    call.layer_hidden = nullptr;
+    const int st = fk_moe_layer(&call, stream);
+    t_resid_in = nullptr; t_update_in = nullptr; t_resid_out = nullptr;
+    return st;
 }
 
 size_t fk_moe_host_staging_bytes(const fk_moe_dims* d, int hidden_dtype) {

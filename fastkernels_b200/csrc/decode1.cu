@@ -319,6 +319,7 @@ __global__ void __launch_bounds__(kD1Threads, 1) decode1_kernel(DecodeParams p) 
     float* xg_s = sact_s + p.I;                                                   // [H]  x * (offset + norm_weight)
     unsigned char* xraw_s = reinterpret_cast<unsigned char*>(xg_s + p.H);         // [H] activations as stored (<= 4 bytes each)
     unsigned char* nw_s = xraw_s + (size_t)p.H * 4;                               // [H] bf16 norm weights
+    unsigned char* uraw_s = nw_s + (size_t)p.H * 2;                               // [H] fp32 previous update (stack mode)
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int G = gridDim.x, blk = blockIdx.x;
     const int H = p.H, I = p.I;
@@ -344,9 +345,16 @@ __global__ void __launch_bounds__(kD1Threads, 1) decode1_kernel(DecodeParams p) 
         // One copy of the token and of the norm weights per block.  (Plain loads by every consumer warp of
         // every block all hit the same few L2 lines and took 4 us to come back.)
         if (lane == 0) {
-            const uint32_t xb = (uint32_t)H * (p.hidden_dtype == FK_F32 ? 4u : 2u);
-            mbar_expect_tx(&s.xready, xb + (uint32_t)H * 2u);
-            bulk_load(xraw_s, p.hidden, xb, &s.xready);
+            if (p.resid_in) {
+                const uint32_t rb = (uint32_t)H * 4u;
+                mbar_expect_tx(&s.xready, rb + (p.update_in ? rb : 0u) + (uint32_t)H * 2u);
+                bulk_load(xraw_s, p.resid_in, rb, &s.xready);
+                if (p.update_in) bulk_load(uraw_s, p.update_in, rb, &s.xready);
+            } else {
+                const uint32_t xb = (uint32_t)H * (p.hidden_dtype == FK_F32 ? 4u : 2u);
+                mbar_expect_tx(&s.xready, xb + (uint32_t)H * 2u);
+                bulk_load(xraw_s, p.hidden, xb, &s.xready);
+            }
             bulk_load(nw_s, p.norm_weight, (uint32_t)H * 2u, &s.xready);
         }
     }
@@ -416,7 +424,16 @@ __global__ void __launch_bounds__(kD1Threads, 1) decode1_kernel(DecodeParams p) 
         for (int j = 0; j < 8; ++j) {
             if (j < nchH) {
                 const size_t el = (size_t)j * 256 + lane * 8;
-                if (p.hidden_dtype == FK_BF16) {
+                if (p.resid_in) {
+                    const uint4 a = lds128(xraw_s + el * 4), b = lds128(xraw_s + el * 4 + 16);
+                    x[j][0] = __uint_as_float(a.x); x[j][1] = __uint_as_float(a.y); x[j][2] = __uint_as_float(a.z); x[j][3] = __uint_as_float(a.w);
+                    x[j][4] = __uint_as_float(b.x); x[j][5] = __uint_as_float(b.y); x[j][6] = __uint_as_float(b.z); x[j][7] = __uint_as_float(b.w);
+                    if (p.update_in) {
+                        const uint4 c = lds128(uraw_s + el * 4), d = lds128(uraw_s + el * 4 + 16);
+                        x[j][0] += __uint_as_float(c.x); x[j][1] += __uint_as_float(c.y); x[j][2] += __uint_as_float(c.z); x[j][3] += __uint_as_float(c.w);
+                        x[j][4] += __uint_as_float(d.x); x[j][5] += __uint_as_float(d.y); x[j][6] += __uint_as_float(d.z); x[j][7] += __uint_as_float(d.w);
+                    }
+                } else if (p.hidden_dtype == FK_BF16) {
                     const uint4 v = lds128(xraw_s + el * 2);
                     x[j][0] = bf16lo(v.x); x[j][1] = bf16hi(v.x); x[j][2] = bf16lo(v.y); x[j][3] = bf16hi(v.y);
                     x[j][4] = bf16lo(v.z); x[j][5] = bf16hi(v.z); x[j][6] = bf16lo(v.w); x[j][7] = bf16hi(v.w);
@@ -439,6 +456,37 @@ __global__ void __launch_bounds__(kD1Threads, 1) decode1_kernel(DecodeParams p) 
             }
         }
 
+        if (p.resid_in) {
+            // layer-stack mode: x holds the new residual stream.  This block stores its slice of it, then the token
+            // is its unit-gain RMS norm rounded to the activation dtype, exactly what a separate norm kernel would
+            // have handed over.
+            if (warp == 1) {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        const int col = j * 256 + lane * 8 + i;
+                        if (j < nchH && col >= pl.h0 && col < pl.h0 + pl.nh) p.resid_out[col] = x[j][i];
+                    }
+                }
+            }
+            float so = 0.f;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) so = fmaf(x[j][i], x[j][i], so);
+            }
+            const float inv = rsqrtf(warp_sum(so) / (float)H + p.resid_eps);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const float v = x[j][i] * inv;
+                    x[j][i] = p.hidden_dtype == FK_BF16 ? __bfloat162float(__float2bfloat16_rn(v))
+                            : (p.hidden_dtype == FK_F16 ? __half2float(__float2half_rn(v)) : v);
+                }
+            }
+        }
         float ss = 0.f;
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
@@ -574,7 +622,7 @@ __global__ void __launch_bounds__(kD1Threads, 1) decode1_kernel(DecodeParams p) 
                 acc += p.shared_gate ? __ldcg(p.sgate) * sh : sh;
             }
             p.out[pl.h0 + tid] = acc;
-            if (p.layer_hidden) p.layer_hidden[pl.h0 + tid] = load_any(p.hidden, p.hidden_dtype, (size_t)(pl.h0 + tid)) + acc;
+            if (p.layer_hidden && !p.resid_in) p.layer_hidden[pl.h0 + tid] = load_any(p.hidden, p.hidden_dtype, (size_t)(pl.h0 + tid)) + acc;
         }
     }
 
@@ -605,11 +653,12 @@ bool decode1_supported(const DecodeParams& p, int weight_dtype) {
                      reinterpret_cast<uintptr_t>(p.shared_down) | reinterpret_cast<uintptr_t>(p.shared_gate) |
                      reinterpret_cast<uintptr_t>(p.logits);
     if (p.E % 4 != 0) return false;            // the logits travel as one bulk copy
+    bits |= reinterpret_cast<uintptr_t>(p.resid_in) | reinterpret_cast<uintptr_t>(p.update_in) | reinterpret_cast<uintptr_t>(p.resid_out);
     return (bits & 15) == 0;
 }
 
 int launch_decode1(const DecodeParams& p, cudaStream_t stream) {
-    const int smem = (int)(sizeof(D1Smem) + sizeof(float) * ((size_t)(FK_MAX_TOP_K + 1) * p.I + p.H) + (size_t)p.H * 6 + 128);
+    const int smem = (int)(sizeof(D1Smem) + sizeof(float) * ((size_t)(FK_MAX_TOP_K + 1) * p.I + p.H) + (size_t)p.H * 10 + 128);
     FK_CUDA_OK(cudaFuncSetAttribute(decode1_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem), "decode1 attr");
     DecodeParams copy = p;
     void* args[] = {&copy};

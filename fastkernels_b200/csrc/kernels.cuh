@@ -142,6 +142,12 @@ struct DecodeParams {
     unsigned long long* trace;    // optional [blocks][8] nanosecond timestamps of the phase boundaries
     int H, E, I, top_k;
     float eps, norm_offset;
+    // layer-stack mode (resid_in != null): the token is RMSNorm(resid_in + update_in) with unit gain, rounded to the
+    // activation dtype of `hidden_dtype`; `hidden` is not read; resid_out receives resid_in + update_in
+    const float* resid_in;        // [H] fp32 residual stream
+    const float* update_in;       // [H] fp32 update of the previous layer, or null
+    float* resid_out;             // [H] (a different buffer than resid_in: other blocks still read that one)
+    float resid_eps;
 };
 bool decode1_supported(const DecodeParams& p, int weight_dtype);
 int launch_decode1(const DecodeParams& p, cudaStream_t stream);

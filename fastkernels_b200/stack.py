@@ -24,7 +24,8 @@ from .plan import MoEDecodePlan
 
 class MoEStackPlan:
     def __init__(self, layers: Sequence, tokens: int, *, top_k: int = 8, eps: float = 1e-6, norm_eps: float = 1e-6,
-                 act_dtype: torch.dtype = torch.bfloat16, group=None, capture: bool = True, flags: int = 0, exchange=None):
+                 act_dtype: torch.dtype = torch.bfloat16, group=None, capture: bool = True, flags: int = 0, exchange=None,
+                 fused_residual: bool = True):
         from .ep import EPShard
         self.lib = _lib.load()
         self.layers = list(layers)
@@ -40,10 +41,25 @@ class MoEStackPlan:
         self.topk_ids = []
         self.graph = None
         self.exchange = exchange
+        self.result = self.x
+        self.fused_residual = False
         if not self.ep:
             self.update = torch.zeros((tokens, H), device=dev, dtype=torch.float32)
             self.plans = [MoEDecodePlan(w, tokens, hidden_dtype=act_dtype, top_k=top_k, eps=eps, flags=flags,
                                         hidden_buffer=self.xin, out_buffer=self.update) for w in self.layers]
+            if tokens == 1 and fused_residual:
+                # one token: the residual add and the norm move into the layer's own kernel (one launch per layer); the
+                # residual stream then alternates between two buffers, because a block of that kernel stores its slice
+                # of the new stream while other blocks still read the old one
+                self.x_alt = torch.zeros_like(self.x)
+                st = self.lib.fk_moe_layer_residual(C.byref(self.plans[0].call), self.x.data_ptr(), None, self.x_alt.data_ptr(),
+                                                    self.norm_eps, torch.cuda.current_stream().cuda_stream)
+                torch.cuda.synchronize(dev)
+                if st == 0:
+                    self.fused_residual = True
+                    self.result = self.x if len(self.layers) % 2 == 0 else self.x_alt
+                elif st != 2:                        # 2 = unsupported shape: keep the two-kernel form
+                    _lib.check(st, "fk_moe_layer_residual")
         elif exchange is not None:
             # expert parallel over peer memory: every layer's call uses the same exchange buffers, one after the other
             from .ep import PeerEPLayer
@@ -72,6 +88,19 @@ class MoEStackPlan:
         from .ep import ep_moe_layer
         update = None
         self.topk_ids = []
+        if self.fused_residual:
+            bufs = (self.x, self.x_alt)
+            stream = torch.cuda.current_stream().cuda_stream
+            for i, plan in enumerate(self.plans):
+                st = self.lib.fk_moe_layer_residual(C.byref(plan.call), bufs[i % 2].data_ptr(),
+                                                    None if i == 0 else self.update.data_ptr(), bufs[(i + 1) % 2].data_ptr(),
+                                                    self.norm_eps, stream)
+                _lib.check(st, "fk_moe_layer_residual")
+                self.topk_ids.append(plan.topk_ids)
+            st = self.lib.fk_residual_rmsnorm(self.result.data_ptr(), self.update.data_ptr(), self.xin.data_ptr(), self.act_code,
+                                              self.tokens, self.hidden_size, self.norm_eps, stream)
+            _lib.check(st, "fk_residual_rmsnorm")           # the last update joins the stream
+            return
         for i, layer in enumerate(self.layers):
             self._norm(update)                       # x += previous update; xin = RMSNorm(x)
             if self.ep and self.exchange is None:
@@ -83,14 +112,15 @@ class MoEStackPlan:
         self._norm(update)                           # x += last update (xin then holds the norm of the result)
 
     def run(self, x: Optional[torch.Tensor] = None) -> torch.Tensor:
-        """Runs the stack in place on `self.x` (copying `x` in first if given) and returns `self.x`."""
+        """Runs the stack on `self.x` (copying `x` in first if given) and returns the residual stream after the last
+        layer: `self.x` itself, or the plan's second buffer in the single-token form with an odd number of layers."""
         if x is not None:
             self.x.copy_(x, non_blocking=True)
         if self.graph is not None:
             self.graph.replay()
         else:
             self._forward()
-        return self.x
+        return self.result
 
 
 class ResidentMoELayers:

@@ -200,6 +200,17 @@ int fk_moe_permute(const int64_t* topk_ids, int tokens, int top_k, int num_exper
                    int32_t* counts, int32_t* offsets, int32_t* order,
                    void* workspace, size_t workspace_bytes, void* stream);
 
+/* One token through one layer of a stack, x_next = x + MoE(RMSNorm(x)) with the previous layer's update still
+ * to be added: resid_out = resid_in + update_in (update_in may be NULL), the layer runs on the unit-gain RMS norm
+ * (norm_eps) of resid_out rounded to c->hidden_dtype, and c->out receives this layer's update (to be passed as
+ * update_in of the next call).  c->hidden is not read.  resid_out must not be resid_in.  The residual add and the
+ * norm happen inside the single-token kernel, so a stack needs one launch per layer.  dims.tokens must be 1 and the
+ * shapes those of the fused kernel, else FK_ERR_UNSUPPORTED (use fk_residual_rmsnorm + fk_moe_layer then).
+ * Counterpart in the reference: the per-layer residual add of its decode loop
+ * (src/fastkernels/kernels/triton/qwen36_layer.py:94-105) and the norm feeding the MoE block (:167-190). */
+int fk_moe_layer_residual(const fk_moe_call* c, const float* resid_in, const float* update_in, float* resid_out,
+                          float norm_eps, void* stream);
+
 /* ---------------------------------------------------------------------------------------------
  * Expert-parallel layer over peer memory (one node, one process per GPU, NVLink).
  * The reference has no distributed code (no torch.distributed / NCCL / MPI call site anywhere; its plan
