@@ -86,6 +86,10 @@ SIGNATURES = {
     "fk_ep_buffer_destroy": (C.c_int, [C.c_void_p]),
     "fk_moe_layer_ep": (C.c_int, [C.POINTER(Call), C.POINTER(EpComm), C.c_void_p]),
     "fk_ep_status": (C.c_int, [C.POINTER(EpComm), C.POINTER(C.c_int)]),
+    "fk_ep_buffer_reset": (C.c_int, [C.c_void_p]),
+    "fk_moe_layer_ep_timed": (C.c_int, [C.POINTER(Call), C.POINTER(EpComm), C.c_void_p, C.POINTER(C.c_float), C.POINTER(C.c_int)]),
+    "fk_set_wait_limit_cycles": (C.c_int, [C.c_longlong]),
+    "fk_moe_status": (C.c_int, [C.c_void_p, C.c_size_t, C.POINTER(C.c_int)]),
 }
 
 _lib = None

@@ -6,6 +6,7 @@
 
 #include "common.cuh"
 #include "kernels.cuh"
+#include "tma.cuh"
 
 namespace fk {
 
@@ -19,6 +20,9 @@ bool pdl_enabled() {
 }
 
 void note_launch() { __atomic_fetch_add(&g_launches, 1ull, __ATOMIC_RELAXED); }
+
+static long long g_wait_cycles = kWaitCycles;
+long long wait_limit_cycles() { return __atomic_load_n(&g_wait_cycles, __ATOMIC_RELAXED); }
 
 void note_cuda_error(cudaError_t e, const char* where) {
     snprintf(g_last_error, sizeof(g_last_error), "%s: %s", where, cudaGetErrorString(e));
@@ -145,6 +149,25 @@ __global__ void shared_gate_kernel(const void* hidden, int hidden_dtype, const v
     if (lane == 0) out[t] = sigmoidf_(acc);
 }
 
+template <typename F>
+static int run_timed(void* stream, float* stage_ms, int* stages, F&& call) {
+    if (!stage_ms || !stages) return FK_ERR_ARG;
+    StageTimer t{};
+    t.stream = (cudaStream_t)stream;
+    for (int i = 0; i < 12; ++i) FK_CUDA_OK(cudaEventCreate(&t.ev[i]), "event create");
+    g_stage_timer = &t;
+    int st = call();
+    g_stage_timer = nullptr;
+    *stages = 0;
+    if (st == FK_OK && t.used >= 2) {
+        FK_CUDA_OK(cudaEventSynchronize(t.ev[t.used - 1]), "event sync");
+        for (int i = 1; i < t.used; ++i) cudaEventElapsedTime(&stage_ms[i - 1], t.ev[i - 1], t.ev[i]);
+        *stages = t.used - 1;
+    }
+    for (int i = 0; i < 12; ++i) cudaEventDestroy(t.ev[i]);
+    return st;
+}
+
 }  // namespace fk
 
 using namespace fk;
@@ -170,21 +193,30 @@ const char* fk_last_cuda_error(void) { return g_last_error; }
 uint64_t fk_launch_count(void) { return __atomic_load_n(&g_launches, __ATOMIC_RELAXED); }
 
 int fk_moe_layer_timed(const fk_moe_call* c, void* stream, float* stage_ms, int* stages) {
-    if (!stage_ms || !stages) return FK_ERR_ARG;
-    StageTimer t{};
-    t.stream = (cudaStream_t)stream;
-    for (int i = 0; i < 12; ++i) FK_CUDA_OK(cudaEventCreate(&t.ev[i]), "event create");
-    g_stage_timer = &t;
-    int st = fk_moe_layer(c, stream);
-    g_stage_timer = nullptr;
-    *stages = 0;
-    if (st == FK_OK && t.used >= 2) {
-        FK_CUDA_OK(cudaEventSynchronize(t.ev[t.used - 1]), "event sync");
-        for (int i = 1; i < t.used; ++i) cudaEventElapsedTime(&stage_ms[i - 1], t.ev[i - 1], t.ev[i]);
-        *stages = t.used - 1;
-    }
-    for (int i = 0; i < 12; ++i) cudaEventDestroy(t.ev[i]);
-    return st;
+    return run_timed(stream, stage_ms, stages, [&] { return fk_moe_layer(c, stream); });
+}
+
+int fk_moe_layer_ep_timed(const fk_moe_call* c, const fk_ep_comm* comm, void* stream, float* stage_ms, int* stages) {
+    return run_timed(stream, stage_ms, stages, [&] { return fk_moe_layer_ep(c, comm, stream); });
+}
+
+int fk_set_wait_limit_cycles(long long cycles) {
+    if (cycles < 0) return FK_ERR_ARG;
+    __atomic_store_n(&g_wait_cycles, cycles == 0 ? kWaitCycles : cycles, __ATOMIC_RELAXED);
+    return FK_OK;
+}
+
+int fk_moe_status(void* workspace, size_t workspace_bytes, int* code) {
+    Workspace w = workspace_layout(fk_moe_dims{0, 1, 1, 1, 0});
+    if (workspace == nullptr || workspace_bytes < w.meta + 16 * sizeof(int)) return FK_ERR_ARG;
+    int* word = at<int>(workspace, w.meta) + 2;
+    int v = 0;
+    FK_CUDA_OK(cudaDeviceSynchronize(), "status sync");
+    FK_CUDA_OK(cudaMemcpy(&v, word, sizeof(int), cudaMemcpyDeviceToHost), "status read");
+    if (code) *code = v;
+    if (v == 0) return FK_OK;
+    FK_CUDA_OK(cudaMemset(word, 0, sizeof(int)), "status clear");
+    return FK_ERR_TIMEOUT;
 }
 
 size_t fk_moe_trace_offset(const fk_moe_dims* dims) {
@@ -270,16 +302,21 @@ int fk_moe_experts(const fk_moe_call* c, void* stream) {
     return run_experts(c, w, reinterpret_cast<const long long*>(c->topk_ids_in), c->topk_weights_in, gate_sig, s);
 }
 
-// fk_moe_layer_host hands the caller's pinned ids / weights buffers to the routing kernels through these
-static thread_local long long* t_ids_mirror = nullptr;
-static thread_local float* t_weights_mirror = nullptr;
-// fk_moe_layer_residual hands the residual stream to the single-token kernel through these
-static thread_local const float* t_resid_in = nullptr;
-static thread_local const float* t_update_in = nullptr;
-static thread_local float* t_resid_out = nullptr;
-static thread_local float t_resid_eps = 0.f;
+// What the public layer entry points add to a plain fk_moe_layer call.
+struct LayerExtras {
+    long long* ids_mirror = nullptr;       // fk_moe_layer_host: the caller's pinned ids / weights buffers, written by the
+    float* weights_mirror = nullptr;       // routing kernels as a second copy
+    const float* resid_in = nullptr;       // fk_moe_layer_residual: the residual stream handed to the single-token kernel
+    const float* update_in = nullptr;
+    float* resid_out = nullptr;
+    float resid_eps = 0.f;
+};
 
-int fk_moe_layer(const fk_moe_call* c, void* stream) {
+static int moe_layer_impl(const fk_moe_call* c, void* stream, const LayerExtras& x);
+
+int fk_moe_layer(const fk_moe_call* c, void* stream) { return moe_layer_impl(c, stream, LayerExtras{}); }
+
+static int moe_layer_impl(const fk_moe_call* c, void* stream, const LayerExtras& x) {
     if (c == nullptr || !dims_ok(c->dims, true) || c->dims.top_k > c->dims.experts) return FK_ERR_ARG;
     if (!dtype_ok(c->hidden_dtype) || !dtype_ok(c->weight_dtype)) return FK_ERR_UNSUPPORTED;
     if (c->dims.tokens == 0) return FK_OK;
@@ -299,7 +336,7 @@ int fk_moe_layer(const fk_moe_call* c, void* stream) {
     rp.shared_gate_out = gated ? at<float>(c->workspace, w.shared_gate) : nullptr;
     rp.logits = c->logits; rp.topk_ids = reinterpret_cast<long long*>(c->topk_ids); rp.topk_weights = c->topk_weights;
     rp.ids32 = nullptr;
-    rp.ids_mirror = t_ids_mirror; rp.weights_mirror = t_weights_mirror;
+    rp.ids_mirror = x.ids_mirror; rp.weights_mirror = x.weights_mirror;
     rp.tickets = at<unsigned>(c->workspace, w.tickets);
     rp.T = c->dims.tokens; rp.H = c->dims.hidden; rp.E = c->dims.experts; rp.top_k = c->dims.top_k;
     rp.eps = c->eps; rp.norm_offset = c->norm_offset;
@@ -313,14 +350,18 @@ int fk_moe_layer(const fk_moe_call* c, void* stream) {
         dp.shared_gate = gated ? c->shared_gate : nullptr;
         dp.logits = c->logits; dp.topk_ids = reinterpret_cast<long long*>(c->topk_ids); dp.topk_weights = c->topk_weights;
         dp.out = c->out; dp.layer_hidden = c->layer_hidden;
-        dp.ids_mirror = t_ids_mirror; dp.weights_mirror = t_weights_mirror;
-        dp.resid_in = t_resid_in; dp.update_in = t_update_in; dp.resid_out = t_resid_out; dp.resid_eps = t_resid_eps;
-        dp.ract = at<float>(c->workspace, w.act);
-        dp.sact = dp.ract + (size_t)c->dims.top_k * c->dims.intermediate;
+        dp.ids_mirror = x.ids_mirror; dp.weights_mirror = x.weights_mirror;
+        dp.resid_in = x.resid_in; dp.update_in = x.update_in; dp.resid_out = x.resid_out; dp.resid_eps = x.resid_eps;
+        dp.act_hi = at<__nv_bfloat16>(c->workspace, w.act);
+        dp.act_lo = at<__nv_bfloat16>(c->workspace, w.act) + (size_t)(c->dims.top_k + 1) * c->dims.intermediate;
         dp.sgate = at<float>(c->workspace, w.shared_gate);
         dp.bar = at<unsigned>(c->workspace, w.counters);
+        dp.tagged = at<unsigned long long>(c->workspace, w.tagged);
+        dp.wait_cycles = wait_limit_cycles();
         dp.error_word = at<int>(c->workspace, w.meta) + 2;
-        dp.trace = (c->flags & FK_FLAG_TRACE) ? at<unsigned long long>(c->workspace, w.y) : nullptr;
+        // the trace record is 256 bytes per block at the start of the y region: dropped when it does not fit there
+        const bool trace_fits = (size_t)sm_count() * 256 <= w.xg - w.y;
+        dp.trace = ((c->flags & FK_FLAG_TRACE) && trace_fits) ? at<unsigned long long>(c->workspace, w.y) : nullptr;
         dp.H = c->dims.hidden; dp.E = c->dims.experts; dp.I = c->dims.intermediate; dp.top_k = c->dims.top_k;
         dp.eps = c->eps; dp.norm_offset = c->norm_offset;
         if (decode1_supported(dp, c->weight_dtype)) {
@@ -329,7 +370,7 @@ int fk_moe_layer(const fk_moe_call* c, void* stream) {
             return st;
         }
     }
-    if (t_resid_in) return FK_ERR_UNSUPPORTED;      // the residual form exists for the single-token kernel only
+    if (x.resid_in) return FK_ERR_UNSUPPORTED;      // the residual form exists for the single-token kernel only
     st = launch_router(rp, c->weight_dtype, s);
     if (st != FK_OK) return st;
     stage_mark();   // end of router
@@ -340,13 +381,12 @@ int fk_moe_layer_residual(const fk_moe_call* c, const float* resid_in, const flo
                           float norm_eps, void* stream) {
     if (c == nullptr || resid_in == nullptr || resid_out == nullptr || resid_out == resid_in) return FK_ERR_ARG;
     if (c->dims.tokens != 1) return FK_ERR_UNSUPPORTED;
-    t_resid_in = resid_in; t_update_in = update_in; t_resid_out = resid_out; t_resid_eps = norm_eps;
+    LayerExtras x;
+    x.resid_in = resid_in; x.update_in = update_in; x.resid_out = resid_out; x.resid_eps = norm_eps;
     fk_moe_call call = *c;
     if (call.hidden == nullptr) call.hidden = resid_in;       // not read in this form; keeps the argument check simple
     call.layer_hidden = nullptr;
-    const int st = fk_moe_layer(&call, stream);
-    t_resid_in = nullptr; t_update_in = nullptr; t_resid_out = nullptr;
-    return st;
+    return moe_layer_impl(&call, stream, x);
 }
 
 size_t fk_moe_host_staging_bytes(const fk_moe_dims* d, int hidden_dtype) {
@@ -394,11 +434,10 @@ int fk_moe_layer_host(const fk_moe_call* c, void* staging, size_t staging_bytes,
     // ids and weights are small: when the caller's buffers are pinned, the routing kernel writes a second copy there
     long long* ids_alias = (long long*)mapped_alias(c->topk_ids);
     float* w_alias = (float*)mapped_alias(c->topk_weights);
-    t_ids_mirror = ids_alias;
-    t_weights_mirror = w_alias;
-    int st = fk_moe_layer(&dev, stream);
-    t_ids_mirror = nullptr;
-    t_weights_mirror = nullptr;
+    LayerExtras x;
+    x.ids_mirror = ids_alias;
+    x.weights_mirror = w_alias;
+    int st = moe_layer_impl(&dev, stream, x);
     if (st != FK_OK) return st;
     if (!out_alias) FK_CUDA_OK(cudaMemcpyAsync(c->out, d_out, T * H * 4, cudaMemcpyDeviceToHost, s), "d2h out");
     if (c->layer_hidden && !layer_alias)
@@ -457,6 +496,14 @@ int fk_ep_buffer_destroy(void* buffer) {
     return FK_OK;
 }
 
+int fk_ep_buffer_reset(void* buffer) {
+    if (buffer == nullptr) return FK_ERR_ARG;
+    FK_CUDA_OK(cudaDeviceSynchronize(), "ep buffer reset sync");
+    FK_CUDA_OK(cudaMemset(buffer, 0, 256), "ep buffer reset");     // the header: epochs, tickets, error word
+    FK_CUDA_OK(cudaDeviceSynchronize(), "ep buffer reset sync");
+    return FK_OK;
+}
+
 int fk_ep_status(const fk_ep_comm* comm, int* error) {
     if (comm == nullptr || error == nullptr || comm->rank < 0 || comm->rank >= FK_EP_MAX_RANKS || !comm->base[comm->rank]) return FK_ERR_ARG;
     FK_CUDA_OK(cudaDeviceSynchronize(), "ep status sync");
@@ -506,20 +553,24 @@ int fk_moe_layer_ep(const fk_moe_call* c, const fk_ep_comm* comm, void* stream) 
     rp.tickets = at<unsigned>(c->workspace, w_all.tickets);
     rp.T = T; rp.H = H; rp.E = c->dims.experts; rp.top_k = k;
     rp.eps = c->eps; rp.norm_offset = c->norm_offset;
+    stage_mark();   // start
     st = launch_router(rp, c->weight_dtype, s);
     if (st != FK_OK) return st;
+    stage_mark();   // end of router
 
     // 2. dispatch: own rows into every rank's buffer, flags, wait for everyone's rows
     EpPeers peers{};
     for (int r = 0; r < G; ++r) peers.header[r] = reinterpret_cast<unsigned*>(comm->base[r]);
     peers.partial_offset = lay.partial;
     peers.world = G; peers.rank = rank; peers.tokens = T;
+    peers.wait_cycles = wait_limit_cycles();
     EpDispatchParams dp{};
     dp.peers = peers; dp.layout = lay;
     dp.hidden = c->hidden; dp.ids = rp.topk_ids; dp.weights = c->topk_weights;
     dp.T = T; dp.H = H; dp.top_k = k; dp.elem_bytes = c->hidden_dtype == FK_F32 ? 4 : 2;
     st = launch_ep_dispatch(dp, s);
     if (st != FK_OK) return st;
+    stage_mark();   // end of dispatch (stores, flags, wait for every rank's rows)
 
     // 3. local experts on the gathered tokens (+ shared expert on the own ones); rows go to the home ranks
     all.hidden = mine + lay.hidden;
@@ -535,8 +586,10 @@ int fk_moe_layer_ep(const fk_moe_call* c, const fk_ep_comm* comm, void* stream) 
     if (st != FK_OK) return st;
 
     // 4. fixed-order sum of the world partials for the own tokens
-    return launch_ep_reduce(reinterpret_cast<const float*>(mine + lay.partial), G, rank, T, H, rp.topk_ids, k, e_local,
-                            c->shared_gate_up != nullptr ? 1 : 0, c->out, c->layer_hidden, c->hidden, c->hidden_dtype, s);
+    st = launch_ep_reduce(reinterpret_cast<const float*>(mine + lay.partial), G, rank, T, H, rp.topk_ids, k, e_local,
+                          c->shared_gate_up != nullptr ? 1 : 0, c->out, c->layer_hidden, c->hidden, c->hidden_dtype, s);
+    stage_mark();   // end of reduce
+    return st;
 }
 
 int fk_single_expert_mlp(const void* hidden, int hidden_dtype, const void* gate_up, const void* down, int weight_dtype,

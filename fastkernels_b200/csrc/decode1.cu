@@ -1,36 +1,55 @@
-// Whole MoE layer for ONE token in one cooperative launch (bf16 weights).
+// Whole MoE layer for ONE token in one launch (bf16 weights and activations, H = 2048, I = 512), one block per SM.
 //
-// One block per SM.  The layer has three dependent phases; the blocks meet at two grid-wide
-// barriers (bounded spins on counters in the workspace, co-residency guaranteed by the cooperative
-// launch):
-//   A  router rows -> logits, shared-expert gate_up pairs -> shared activations, gate dot   (static)
-//   -- barrier 1 --  every block runs softmax + top-k (by rank) on the 256 logits itself
-//   B  the 8 selected experts' gate_up pairs -> activations; shared-expert down rows
-//   -- barrier 2 --
-//   C  the 8 selected experts' down rows for this block's slice of the output, summed in slot order
-//      with the routing weights, plus the gated shared expert (and the residual)
-// Work is split evenly by bytes: every block streams the same share of every matrix.
+// The layer has three dependent steps (router -> gate_up of the selected experts -> down), and at this size
+// every dependent step costs about as much as streaming its weights.  The kernel is laid out around the
+// dependences and around the instruction count of the warps that consume the stream:
 //
-// A producer warp issues bulk copies (one weight row or gate/up pair per 8 KB stage) into a
-// 16-stage shared-memory ring and runs ahead across the barriers: phase C addresses depend only on
-// the expert ids, so those rows are already in flight while the blocks wait at barrier 2.  Eight
-// consumer warps take the stages round-robin; a stage is handled by one warp (16-byte shared loads,
-// the token's activations in registers, shuffle reduction), so consumers never synchronise with
-// each other inside a phase.  Code that runs once per launch (router rows, top-k, down rows) is
-// written as short rolled loops: at this size the kernel is bound by instruction fetch and memory
-// latency, not by issue rate.
+//   start   every block issues ALL of its routing-independent copies at once: its router rows, its gate_up tiles
+//           of the shared expert (ring stages) and the shared expert's down tile (a buffer of its own), before it
+//           even has the token.  Weights are constants, so with programmatic dependent launch these copies run
+//           while the kernel before this one in the stream drains.
+//   logits  each router row's logit is published as one 64-bit word (launch tag << 32 | logit bits).  A select
+//           warp in every block polls the E words until all carry this launch's tag: arrival and data are one
+//           load, no fence, no counter, no second round trip.  The same warp then runs softmax + top-k on the
+//           values it already holds in registers, and the producer warp starts the experts' copies at once.
+//   B       the selected experts' gate and up tiles stream through the 16-stage ring; the down tiles follow in
+//           the same queue as ring slots free up (their addresses depend on the ids only), so HBM stays busy
+//           across the second grid-wide dependence.
+//   sync    one counter barrier (bounded spin): every block has published its SwiGLU activations; each block
+//           stages all of them in shared memory with two bulk copies.
+//   C       down tiles of the block's 16 output rows, summed in slot order with the routing weights, plus the
+//           gated shared expert (and the residual).
+//
+// Consumers.  Warp w owns columns [256 w, 256 w + 256) of the hidden dimension (phase B) and [64 w, 64 w + 64) of
+// the intermediate dimension (phase C).  A stage is one [16 rows x 256 columns] weight tile (four 128-byte-swizzled
+// TMA boxes), read with ldmatrix and multiplied on the tensor cores (mma.sync m16n8k16, bf16 in, fp32 accumulate):
+// the sixteen weight rows are the M rows, the token is column 0 of N.  Seven of the eight N columns are wasted, and
+// it is still five times fewer instructions than unpacking bf16 pairs and issuing one FMA per weight, which is what
+// bounded this kernel before (each warp issued ~4300 instructions at ~6 stall cycles each).  Products of bf16
+// values are exact in fp32, so the sums differ from a CUDA-core dot product only in their order.  The fp32 SwiGLU
+// activations enter the down MMAs as a bf16 head plus a bf16 remainder (relative error 2^-17).  The eight K-slices
+// of a tile meet in shared memory.  The router rows (at most three per block) stay on the CUDA cores, one K-slice
+// per warp, because their operand x * (offset + norm_weight) is an fp32 value.
+//
+// The launch is not cooperative: 148 blocks of one block per SM become resident together as soon as the SMs are
+// free, and every wait on another block is bounded (it gives up, raises the error word and lets the kernel
+// finish).  That allows the programmatic-dependent-launch attribute, which a cooperative launch does not take.
+// FKMOE_D1_COOPERATIVE=1 selects a cooperative launch without the overlap.
 //
 // Reference math: src/fastkernels/reference/qwen36_real.py:329-354.
 
-#include <cooperative_groups.h>
+#include <cuda.h>
+
+#include <cstdlib>
 
 #include "common.cuh"
 #include "kernels.cuh"
-#include "tma.cuh"
+#include "tcgen05.cuh"
 #include "topk.cuh"
 
 namespace fk {
 
+constexpr int kD1H = 2048, kD1I = 512;           // the shape this kernel is built for
 constexpr int kD1Stages = 16;
 constexpr int kD1StageBytes = 8192;
 constexpr int kD1Consumers = 8;                  // warps
@@ -40,86 +59,74 @@ constexpr int kD1Consumers = 8;                  // warps
 // out of order, e.g. after a TLB miss), and a one-bit phase parity cannot tell "lap k landed" from "lap k-1 has
 // not landed yet": the warp would read the slot early and release it twice.
 static_assert(kD1Stages % kD1Consumers == 0, "every ring slot must belong to one consumer warp");
-constexpr int kD1Threads = (kD1Consumers + 1) * 32;
-constexpr int kD1MaxRows = 64;                   // output rows per block (H / #blocks rounded up)
+static_assert(kD1H == kD1Consumers * 256 && kD1I == kD1Consumers * 64, "one K-slice per consumer warp");
+constexpr int kD1Threads = (kD1Consumers + 2) * 32;   // consumers + producer warp + select warp
+constexpr int kD1Tile = 16;                      // MMA M: gate (or up) rows per stage, output rows per block
+constexpr int kD1MaxRouterRows = 4;              // router rows of a block, the shared-expert gate vector included
+constexpr int kD1MaxAtoms = 4;                   // gate_up atoms (16 gate/up pairs of one expert) per block
+constexpr int kD1ActElems = (FK_MAX_TOP_K + 1) * kD1I;
 
 struct D1Smem {
-    unsigned char stage[kD1Stages][kD1StageBytes];
+    unsigned char stage[kD1Stages][kD1StageBytes];                // 1 KB aligned: the swizzle is a function of the address
+    unsigned char sdown[kD1Consumers][2048];                      // the shared expert's down tile, one [16 x 64] box per warp
+    unsigned char rrow[kD1MaxRouterRows][kD1H * 2];               // router rows as stored
+    unsigned char xraw[kD1H * 4];                                 // the token as stored (bf16), or the fp32 residual stream
+    unsigned char uraw[kD1H * 4];                                 // fp32 update of the previous layer (stack mode)
+    unsigned char nw[kD1H * 2];                                   // bf16 norm weights
+    unsigned char xb[kD1H * 2];                                   // stack mode: the normed token in bf16
+    unsigned char act_hi[kD1ActElems * 2];                        // all blocks' activations, bf16 head ...
+    unsigned char act_lo[kD1ActElems * 2];                        // ... and bf16 remainder
+    float bpart[2 * kD1MaxAtoms][kD1Consumers][kD1Tile];          // phase B: K-slice sums per stage
+    float cpart[FK_MAX_TOP_K + 1][kD1Consumers][kD1Tile];         // phase C: K-slice sums per slot (slot top_k = shared expert)
+    float rpart[kD1MaxRouterRows + 1][kD1Consumers];              // router rows: K-slice sums; last row: sum of squares
+    float sopart[kD1Consumers];                                   // stack mode: K-slice sums of squares of the residual
     uint64_t full[kD1Stages];
     uint64_t empty[kD1Stages];
-    uint64_t ids_ready;
-    uint64_t xready;                              // the token's activations and the norm weights are in shared memory
-    uint64_t staged_a;                            // logits and shared activations of all blocks are in shared memory
-    uint64_t staged_b;                            // routed activations of all blocks are in shared memory
-    int4 desc[kD1Stages];                         // what each stage holds (written by the producer)
-    float dpart[FK_MAX_TOP_K][kD1MaxRows];       // un-weighted down outputs per slot
-    float ysh[kD1MaxRows];                       // shared-expert down outputs
-    float weights[FK_MAX_TOP_K];                 // selected probabilities, descending
-    float wnorm[FK_MAX_TOP_K];                   // renormalised routing weights
-    float red[2 * kD1Consumers];                 // block reductions of the softmax
+    uint64_t xready;                              // the token, the norm weights and the launch tag are in shared memory
+    uint64_t rrfull;                              // the router rows have landed
+    uint64_t sdfull;                              // sdown has landed
+    uint64_t rdone;                               // every warp has written its router K-slice sums
+    uint64_t staged_b;                            // the activations of all blocks are in shared memory
+    uint64_t ids_ready;                           // ids / wnorm written by the select warp
+    float wnorm[FK_MAX_TOP_K];                    // renormalised routing weights
     int ids[FK_MAX_TOP_K];
+    unsigned tag;                                 // this launch's tag for the published logits
     int abort_flag;
 };
 
-enum D1Kind { kRouterRow = 0, kGateRow = 1, kSharedPair = 2, kRoutedPair = 3, kSharedDown = 4, kRoutedDown = 5, kNone = 6 };
-
+// Static split of the work among the G blocks.
+//   router   block b takes rows b, b + G, ...; the last block also takes the shared-expert gate vector.
+//   gate_up  "atoms" of 16 gate/up pairs of one expert: first the shared expert's (I/16), then slot by slot the
+//            routed experts' (top_k * I/16), dealt evenly.  (The blocks meet between gate_up and down, so each of
+//            the two phases has to be balanced by itself: giving the blocks without an output tile more atoms
+//            made everybody wait for them.)
+//   down     block b < H/16 owns output rows [16 b, 16 b + 16); the other blocks leave after gate_up.
 struct D1Plan {
-    // static split of the work of block b among G blocks
-    int nA_router, nA_gate, nA_pair, nB_pair, nB_down, nC;   // stages per kind
-    int pair0, q0, h0, nh;                                    // first shared pair, first routed pair, output slice
-    int rows_per_stage;                                       // down rows per stage (8 KB / row bytes)
-};
-
-struct D1Stage {
-    int kind, a, b, c;   // see decode_stage
+    int nrr;            // router rows of this block (gate vector included)
+    int gate_row;       // index of the gate vector among them, or -1
+    int atom0, atoms;   // first global atom, number of atoms
+    int shared_atoms;   // global atoms [0, shared_atoms) belong to the shared expert
+    int tile;           // output tile, or -1
+    int nB;             // ring stages of phase B per warp (2 per atom)
+    int nC;             // ring stages of phase C per warp (4 slots per stage)
 };
 
 __device__ __forceinline__ D1Plan make_plan(const DecodeParams& p, int b, int G) {
     D1Plan pl;
-    pl.nA_router = (p.E - b + G - 1) / G;
-    if (b >= p.E) pl.nA_router = 0;
-    pl.nA_gate = (p.shared_gate != nullptr && b == G - 1) ? 1 : 0;
-    const int has_shared = p.shared_gate_up != nullptr;
-    const unsigned ub = (unsigned)b, uG = (unsigned)G;
-    pl.pair0 = (int)(ub * (unsigned)p.I / uG);
-    const int pair1 = (int)((ub + 1u) * (unsigned)p.I / uG);
-    pl.nA_pair = has_shared ? pair1 - pl.pair0 : 0;
-    pl.q0 = (int)(ub * (unsigned)(p.top_k * p.I) / uG);
-    const int q1 = (int)((ub + 1u) * (unsigned)(p.top_k * p.I) / uG);
-    pl.nB_pair = q1 - pl.q0;
-    pl.h0 = (int)(ub * (unsigned)p.H / uG);
-    pl.nh = (int)((ub + 1u) * (unsigned)p.H / uG) - pl.h0;
-    pl.rows_per_stage = min(8, kD1StageBytes / (p.I * 2));
-    const int down_stages = (pl.nh + pl.rows_per_stage - 1) / pl.rows_per_stage;
-    pl.nB_down = has_shared ? down_stages : 0;
-    pl.nC = down_stages * p.top_k;
+    pl.nrr = b < p.E ? (p.E - b + G - 1) / G : 0;
+    pl.gate_row = (p.shared_gate != nullptr && b == G - 1) ? pl.nrr : -1;
+    if (pl.gate_row >= 0) pl.nrr += 1;
+    const int per_expert = kD1I / kD1Tile;
+    pl.shared_atoms = p.shared_gate_up ? per_expert : 0;
+    const int total = pl.shared_atoms + p.top_k * per_expert;
+    const int tiles = kD1H / kD1Tile;                      // G >= tiles is checked on the host
+    const int q = total / G, r = total - q * G;
+    pl.tile = b < tiles ? b : -1;
+    pl.atom0 = b * q + min(b, r);
+    pl.atoms = q + (b < r ? 1 : 0);
+    pl.nB = 2 * pl.atoms;
+    pl.nC = pl.tile >= 0 ? (p.top_k + 3) / 4 : 0;
     return pl;
-}
-
-// Stage number `it` of a block -> what it holds.
-//   kRouterRow : a = expert row            kGateRow : -
-//   kSharedPair: a = pair index            kRoutedPair: a = slot, b = pair index
-//   kSharedDown: a = first local row, b = rows      kRoutedDown: a = slot, b = first local row, c = rows
-__device__ __forceinline__ D1Stage decode_stage(const D1Plan& pl, const DecodeParams& p, int it, int blk, int G) {
-    D1Stage s{kNone, 0, 0, 0};
-    if (it < pl.nA_router) { s.kind = kRouterRow; s.a = blk + it * G; return s; }
-    it -= pl.nA_router;
-    if (it < pl.nA_gate) { s.kind = kGateRow; return s; }
-    it -= pl.nA_gate;
-    if (it < pl.nA_pair) { s.kind = kSharedPair; s.a = pl.pair0 + it; return s; }
-    it -= pl.nA_pair;
-    if (it < pl.nB_pair) { const int q = pl.q0 + it; s.kind = kRoutedPair; s.a = q / p.I; s.b = q - s.a * p.I; return s; }
-    it -= pl.nB_pair;
-    if (it < pl.nB_down) {
-        s.kind = kSharedDown; s.a = it * pl.rows_per_stage; s.b = min(pl.rows_per_stage, pl.nh - s.a); return s;
-    }
-    it -= pl.nB_down;
-    if (it < pl.nC) {
-        const int per_slot = pl.nC / p.top_k;
-        s.kind = kRoutedDown; s.a = it / per_slot;
-        s.b = (it - s.a * per_slot) * pl.rows_per_stage; s.c = min(pl.rows_per_stage, pl.nh - s.b); return s;
-    }
-    return s;
 }
 
 __device__ __forceinline__ unsigned long long global_ns() {
@@ -127,13 +134,23 @@ __device__ __forceinline__ unsigned long long global_ns() {
     asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
     return t;
 }
-// optional trace: p.trace[block][slot] = nanosecond timestamp of a phase boundary (16 words per block;
-// words 8 and 9 hold the SM cycle counter at start and exit)
-#define D1_TRACE(slot) do { if (p.trace) p.trace[(size_t)blk * 16 + (slot)] = global_ns(); } while (0)
+// optional trace: p.trace[block][slot] = nanosecond timestamp of a phase boundary (32 words per block;
+// words 8 and 9 hold the SM cycle counter at start and exit); the slots are listed in include/fkmoe.h
+#define D1_TRACE(slot) do { if (p.trace) p.trace[(size_t)blockIdx.x * 32 + (slot)] = global_ns(); } while (0)
 
 __device__ __forceinline__ unsigned ld_acquire_u32(const unsigned* p) {
     unsigned v;
     asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ unsigned ld_relaxed_u32(const unsigned* p) {
+    unsigned v;
+    asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ unsigned long long ld_relaxed_u64(const unsigned long long* p) {
+    unsigned long long v;
+    asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
     return v;
 }
 
@@ -141,529 +158,593 @@ __device__ __forceinline__ unsigned ld_acquire_u32(const unsigned* p) {
 // later bulk copies, which read and write memory through the async proxy.
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async;" ::: "memory"); }
 
-// Bounded spin until *word >= target; false on time-out.
-__device__ __forceinline__ bool spin_until(const unsigned* word, unsigned target, volatile int* abort_flag) {
-    if (ld_acquire_u32(word) >= target) return true;
-    const long long limit = *abort_flag ? kWaitCyclesAfterAbort : kWaitCycles;
+// Bounded spin until the counter *word has reached target (a count that only grows and may wrap); false on time-out.
+__device__ __forceinline__ bool spin_until(const unsigned* word, unsigned target, long long wait_cycles, volatile int* abort_flag) {
+    if ((int)(ld_acquire_u32(word) - target) >= 0) return true;
+    const long long limit = *abort_flag ? min(wait_cycles, kWaitCyclesAfterAbort) : wait_cycles;
     const long long t0 = clock64();
-    while (ld_acquire_u32(word) < target) {
+    while ((int)(ld_acquire_u32(word) - target) < 0) {
         if (clock64() - t0 > limit) { *abort_flag = 1; return false; }
     }
     return true;
 }
 
-// gate and up row of one pair against the token's activations held in registers (hot loop, unrolled)
-__device__ __forceinline__ void pair_dot(const unsigned char* grow, const unsigned char* urow, const float (&x)[8][8],
-                                         int lane, int nch, float& g, float& u) {
-    float g0 = 0.f, g1 = 0.f, u0 = 0.f, u1 = 0.f;
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-        if (j < nch) {
-            const uint4 a = lds128(grow + (size_t)(j * 256 + lane * 8) * 2);
-            const uint4 b = lds128(urow + (size_t)(j * 256 + lane * 8) * 2);
-            g0 = fmaf(bf16lo(a.x), x[j][0], g0); g1 = fmaf(bf16hi(a.x), x[j][1], g1);
-            g0 = fmaf(bf16lo(a.y), x[j][2], g0); g1 = fmaf(bf16hi(a.y), x[j][3], g1);
-            g0 = fmaf(bf16lo(a.z), x[j][4], g0); g1 = fmaf(bf16hi(a.z), x[j][5], g1);
-            g0 = fmaf(bf16lo(a.w), x[j][6], g0); g1 = fmaf(bf16hi(a.w), x[j][7], g1);
-            u0 = fmaf(bf16lo(b.x), x[j][0], u0); u1 = fmaf(bf16hi(b.x), x[j][1], u1);
-            u0 = fmaf(bf16lo(b.y), x[j][2], u0); u1 = fmaf(bf16hi(b.y), x[j][3], u1);
-            u0 = fmaf(bf16lo(b.z), x[j][4], u0); u1 = fmaf(bf16hi(b.z), x[j][5], u1);
-            u0 = fmaf(bf16lo(b.w), x[j][6], u0); u1 = fmaf(bf16hi(b.w), x[j][7], u1);
-        }
+// "The mbarriers are initialised": the producer warp arrives on named barrier 2 without waiting, every other warp
+// waits there once before its first use of an mbarrier.
+__device__ __forceinline__ void barriers_ready_arrive() { asm volatile("bar.arrive 2, %0;" ::"r"(kD1Threads) : "memory"); }
+__device__ __forceinline__ void barriers_ready_wait() { asm volatile("bar.sync 2, %0;" ::"r"(kD1Threads) : "memory"); }
+
+// tight wait on a latency-critical barrier (no back-off)
+__device__ __forceinline__ bool mbar_wait_spin(uint64_t* bar, uint32_t parity, long long limit, volatile int* abort_flag) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if (*abort_flag) limit = min(limit, kWaitCyclesAfterAbort);
+    const long long t0 = clock64();
+    while (!mbar_try_wait(bar, parity)) {
+        if (clock64() - t0 > limit) { *abort_flag = 1; return false; }
     }
-    g = warp_sum(g0 + g1);
-    u = warp_sum(u0 + u1);
+    return true;
 }
 
-// one bf16 row of nch*256 columns against a vector in shared memory (rolled on purpose: this code
-// runs a handful of times per launch, and a short loop costs far fewer instruction fetches)
-__device__ __forceinline__ float row_dot_smem(const unsigned char* row, const float* vec, int lane, int nch) {
-    float a0 = 0.f, a1 = 0.f;
-#pragma unroll 2
-    for (int j = 0; j < nch; ++j) {
-        const int c = j * 256 + lane * 8;
-        const uint4 w = lds128(row + (size_t)c * 2);
-        const float4 v0 = *reinterpret_cast<const float4*>(vec + c);
-        const float4 v1 = *reinterpret_cast<const float4*>(vec + c + 4);
-        a0 = fmaf(bf16lo(w.x), v0.x, a0); a1 = fmaf(bf16hi(w.x), v0.y, a1);
-        a0 = fmaf(bf16lo(w.y), v0.z, a0); a1 = fmaf(bf16hi(w.y), v0.w, a1);
-        a0 = fmaf(bf16lo(w.z), v1.x, a0); a1 = fmaf(bf16hi(w.z), v1.y, a1);
-        a0 = fmaf(bf16lo(w.w), v1.z, a0); a1 = fmaf(bf16hi(w.w), v1.w, a1);
-    }
-    return warp_sum(a0 + a1);
+__device__ __forceinline__ uint32_t d1_lds32(const void* smem_ptr) {
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(smem_u32(smem_ptr)));
+    return v;
+}
+__device__ __forceinline__ void d1_ldmatrix_x4(uint32_t (&r)[4], uint32_t smem_addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_addr));
+}
+__device__ __forceinline__ void d1_mma(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+// mbarrier arrive that cannot be scheduled before `dep` has been computed
+__device__ __forceinline__ void d1_release(uint64_t* bar, float dep) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)), "f"(dep) : "memory");
 }
 
-// up to 8 rows of nch*256 columns (row stride = row_bytes) against one vector in shared memory, all
-// rows at once: 8 independent sums per lane, folded with a transposing shuffle reduction.
-// Returns in every lane the sum of the row (lane >> 2), i.e. lanes 4r..4r+3 hold row r.
-__device__ __forceinline__ float rows8_dot_smem(const unsigned char* base, int row_bytes, int nrows, const float* vec,
-                                                int lane, int nch) {
-    float acc[8];
+// One [16 rows x 64 columns] box (128-byte swizzle, 2 KB, base 1 KB aligned) against 64 values of the token in
+// column 0 of B: four k-steps of ldmatrix.x4 + MMA.  bfrag[kk] holds {b0, b1} of k-step kk (zero outside lanes 0..3).
+// ldmatrix row address of a lane: matrices 0..3 = (rows 0-7, k 0-7), (rows 8-15, k 0-7), (rows 0-7, k 8-15),
+// (rows 8-15, k 8-15); the 16-byte chunk c of row r sits at chunk c ^ (r & 7).
+__device__ __forceinline__ void box_mma(float (&c)[4], uint32_t box_addr, const uint32_t (*bfrag)[2], int lane) {
+    const int row = (lane & 7) + ((lane >> 3) & 1) * 8;
+    const uint32_t rbase = box_addr + row * 128;
+    const int sel = lane >> 4, sw = row & 7;
 #pragma unroll
-    for (int r = 0; r < 8; ++r) acc[r] = 0.f;
-#pragma unroll 1
-    for (int j = 0; j < nch; ++j) {
-        const int c = j * 256 + lane * 8;
-        const float4 v0 = *reinterpret_cast<const float4*>(vec + c);
-        const float4 v1 = *reinterpret_cast<const float4*>(vec + c + 4);
-#pragma unroll
-        for (int r = 0; r < 8; ++r) {
-            if (r < nrows) {
-                const uint4 w = lds128(base + (size_t)r * row_bytes + (size_t)c * 2);
-                float a = acc[r];
-                a = fmaf(bf16lo(w.x), v0.x, a); a = fmaf(bf16hi(w.x), v0.y, a);
-                a = fmaf(bf16lo(w.y), v0.z, a); a = fmaf(bf16hi(w.y), v0.w, a);
-                a = fmaf(bf16lo(w.z), v1.x, a); a = fmaf(bf16hi(w.z), v1.y, a);
-                a = fmaf(bf16lo(w.w), v1.z, a); a = fmaf(bf16hi(w.w), v1.w, a);
-                acc[r] = a;
-            }
-        }
+    for (int kk = 0; kk < 4; ++kk) {
+        uint32_t a[4];
+        d1_ldmatrix_x4(a, rbase + (((2 * kk + sel) ^ sw) << 4));
+        d1_mma(c, a, bfrag[kk][0], bfrag[kk][1]);
     }
-    // transposing reduction: 4 + 2 + 1 exchanges, then two plain steps
-#pragma unroll
-    for (int st = 0; st < 3; ++st) {
-        const int half = 4 >> st, off = 16 >> st;
-        const bool upper = (lane & off) != 0;
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            if (i < half) {
-                const float send = upper ? acc[i] : acc[i + half];
-                const float keep = upper ? acc[i + half] : acc[i];
-                acc[i] = keep + __shfl_xor_sync(kFull, send, off);
-            }
-        }
-    }
-    acc[0] += __shfl_xor_sync(kFull, acc[0], 2);
-    acc[0] += __shfl_xor_sync(kFull, acc[0], 1);
-    return acc[0];
 }
 
-// k rounds of warp arg-max over probabilities in shared memory (ties to the lower index); lane r
-// writes the r-th winner.  Non-negative floats order like their bit patterns: key = bits + 1, 0 = taken.
+// Select warp: wait until every expert's logit of this launch has been published, then softmax + top-k on the
+// values the lanes already hold (lane L owns experts j*32 + L).  Writes ids / renormalised weights to shared memory
+// (and to the outputs from block 0).
 template <int EPL>
-__device__ __forceinline__ void select_warp(const float* probs, int E, int top_k, int* ids, float* vals, int lane) {
-    unsigned key[EPL];
+__device__ __forceinline__ void poll_and_select(const DecodeParams& p, D1Smem& s, int lane, bool write_global) {
+    const unsigned tag = s.tag;
+    float v[EPL];
+    const long long t0 = clock64();
+    bool complete = true;
+    for (;;) {
+        unsigned long long w[EPL];
 #pragma unroll
-    for (int j = 0; j < EPL; ++j) key[j] = (j * 32 + lane < E) ? __float_as_uint(probs[j * 32 + lane]) + 1u : 0u;
-#pragma unroll 1
-    for (int r = 0; r < top_k; ++r) {
-        unsigned best = 0u;
-#pragma unroll
-        for (int j = 0; j < EPL; ++j) best = max(best, key[j]);
-        const unsigned m = __reduce_max_sync(kFull, best);
-        unsigned cand = 0x7fffffffu;
-#pragma unroll
-        for (int j = EPL - 1; j >= 0; --j) cand = (key[j] == m) ? (unsigned)(j * 32 + lane) : cand;
-        const unsigned bi = __reduce_min_sync(kFull, cand);
-#pragma unroll
-        for (int j = 0; j < EPL; ++j) key[j] = ((unsigned)(j * 32 + lane) == bi) ? 0u : key[j];
-        if (lane == r) { ids[r] = (int)bi; vals[r] = __uint_as_float(m - 1u); }
-    }
-}
-
-// Block-wide softmax over the logits in `probs` (shared memory), then top-k by one warp (threads = cthreads
-// consumer threads, E <= 1024).
-// Every thread owns the experts e = ctid, ctid + cthreads, ... for the softmax.
-// Writes ids/weights to shared memory (and to global memory from block 0).
-__device__ __forceinline__ void block_topk(const DecodeParams& p, D1Smem& s, float* probs, int ctid, int cthreads, bool write_global) {
-    const int E = p.E, lane = ctid & 31, w = ctid >> 5;
-    float m = -INFINITY;
-    for (int e = ctid; e < E; e += cthreads) {
-        const float l = probs[e];                 // the logits were bulk-copied here
-        m = fmaxf(m, l);
-    }
-    m = warp_max(m);
-    if (lane == 0) s.red[w] = m;
-    named_bar_sync(1, cthreads);
-    m = s.red[0];
-    for (int i = 1; i < kD1Consumers; ++i) m = fmaxf(m, s.red[i]);
-    float sum = 0.f;
-    for (int e = ctid; e < E; e += cthreads) {
-        const float ex = expf(probs[e] - m);
-        probs[e] = ex;
-        sum += ex;
-    }
-    sum = warp_sum(sum);
-    if (lane == 0) s.red[kD1Consumers + w] = sum;
-    named_bar_sync(1, cthreads);
-    sum = 0.f;
-    for (int i = 0; i < kD1Consumers; ++i) sum += s.red[kD1Consumers + i];
-    for (int e = ctid; e < E; e += cthreads) probs[e] = probs[e] / sum;
-    named_bar_sync(1, cthreads);
-    // selection by one warp: k rounds of two hardware warp reductions over keys held 8 (or 32) per lane
-    if (w == 0) {
-        if (E <= 256) select_warp<8>(probs, E, p.top_k, s.ids, s.weights, lane);
-        else select_warp<32>(probs, E, p.top_k, s.ids, s.weights, lane);
-    }
-    named_bar_sync(1, cthreads);
-    if (ctid < p.top_k) {
-        float total = 0.f;
-        for (int r = 0; r < p.top_k; ++r) total += s.weights[r];
-        const float wgt = s.weights[ctid] / total;
-        if (write_global) {
-            p.topk_ids[ctid] = s.ids[ctid];
-            p.topk_weights[ctid] = wgt;
-            if (p.ids_mirror) p.ids_mirror[ctid] = s.ids[ctid];
-            if (p.weights_mirror) p.weights_mirror[ctid] = wgt;
+        for (int j = 0; j < EPL; ++j) {               // all loads in flight together: one round trip per poll
+            const int e = j * 32 + lane;
+            w[j] = e < p.E ? ld_relaxed_u64(p.tagged + e) : 0ull;
         }
-        s.wnorm[ctid] = wgt;
+        bool ok = true;
+#pragma unroll
+        for (int j = 0; j < EPL; ++j) {
+            const int e = j * 32 + lane;
+            ok = ok & (e >= p.E || (unsigned)(w[j] >> 32) == tag);
+            v[j] = e < p.E ? __uint_as_float((unsigned)w[j]) : -INFINITY;
+        }
+        if (__all_sync(kFull, ok)) break;
+        if (clock64() - t0 > p.wait_cycles) { complete = false; break; }
+        __nanosleep(64);       // 148 warps polling without a pause keep the publishing stores waiting for microseconds
     }
-    named_bar_sync(1, cthreads);
+    complete = __all_sync(kFull, complete);
+    if (lane == 0) D1_TRACE(18);
+    if (!complete && lane == 0) s.abort_flag = 1;
+    int my_i;
+    float my_w;
+    topk_warp_regs<EPL>(v, p.E, p.top_k, lane, my_i, my_w);
+    if (lane < p.top_k) {
+        s.ids[lane] = my_i;
+        s.wnorm[lane] = my_w;
+        if (write_global) {
+            p.topk_ids[lane] = my_i;
+            p.topk_weights[lane] = my_w;
+            if (p.ids_mirror) p.ids_mirror[lane] = my_i;
+            if (p.weights_mirror) p.weights_mirror[lane] = my_w;
+        }
+    }
+    __syncwarp();
 }
 
-__global__ void __launch_bounds__(kD1Threads, 1) decode1_kernel(DecodeParams p) {
-    extern __shared__ __align__(128) unsigned char smem_raw[];
-    D1Smem& s = *reinterpret_cast<D1Smem*>(smem_raw);
-    float* ract_s = reinterpret_cast<float*>(smem_raw + sizeof(D1Smem));          // [top_k][I]; softmax scratch before
-    float* sact_s = ract_s + (size_t)FK_MAX_TOP_K * p.I;                          // [I]
-    float* xg_s = sact_s + p.I;                                                   // [H]  x * (offset + norm_weight)
-    unsigned char* xraw_s = reinterpret_cast<unsigned char*>(xg_s + p.H);         // [H] activations as stored (<= 4 bytes each)
-    unsigned char* nw_s = xraw_s + (size_t)p.H * 4;                               // [H] bf16 norm weights
-    unsigned char* uraw_s = nw_s + (size_t)p.H * 2;                               // [H] fp32 previous update (stack mode)
+__global__ void __launch_bounds__(kD1Threads, 1)
+decode1_kernel(const __grid_constant__ CUtensorMap gu_map, const __grid_constant__ CUtensorMap sgu_map,
+               const __grid_constant__ CUtensorMap dn_map, const __grid_constant__ CUtensorMap sdn_map, DecodeParams p) {
+    extern __shared__ unsigned char smem_raw[];
+    D1Smem& s = *reinterpret_cast<D1Smem*>(smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u));
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int G = gridDim.x, blk = blockIdx.x;
-    const int H = p.H, I = p.I;
-    const int nchH = H / 256, nchI = I / 256;
-    if (tid == 0) { D1_TRACE(0); if (p.trace) p.trace[(size_t)blk * 16 + 8] = (unsigned long long)clock64(); }
+    constexpr int H = kD1H, I = kD1I;
+    pdl_trigger();            // the next kernel in the stream may start its own constant loads as SMs free up
+    if (tid == 0) { D1_TRACE(0); if (p.trace) p.trace[(size_t)blk * 32 + 8] = (unsigned long long)clock64(); }
 
-    // The producer warp prepares the ring itself (one slot per lane) and starts phase A before the block
-    // meets: the first copies are then in flight while the consumers still wait for their activations.
+    const D1Plan pl = make_plan(p, blk, G);
+    const bool has_shared = p.shared_gate_up != nullptr;
+    const int shared_slot = p.top_k;                       // index of the shared expert in the activation arrays
+    __nv_bfloat16* act_hi_g = reinterpret_cast<__nv_bfloat16*>(p.act_hi);
+    __nv_bfloat16* act_lo_g = reinterpret_cast<__nv_bfloat16*>(p.act_lo);
+
     if (warp == kD1Consumers) {
+        // ------------------------------------------------------------------ producer warp
         if (lane < kD1Stages) {
             mbar_init(&s.full[lane], 1);
             mbar_init(&s.empty[lane], 1);
         }
         if (lane == 0) {
-            mbar_init(&s.ids_ready, 1);
-            mbar_init(&s.xready, 1);
-            mbar_init(&s.staged_a, 1);
+            mbar_init(&s.xready, 2);              // the copies' transaction count + the tag
+            mbar_init(&s.rrfull, 1);
+            mbar_init(&s.sdfull, 1);
+            mbar_init(&s.rdone, kD1Consumers);
             mbar_init(&s.staged_b, 1);
+            mbar_init(&s.ids_ready, 1);
             s.abort_flag = 0;
+            prefetch_tensormap(&gu_map);
+            prefetch_tensormap(&dn_map);
         }
         mbar_init_fence();
         __syncwarp();
-        // One copy of the token and of the norm weights per block.  (Plain loads by every consumer warp of
-        // every block all hit the same few L2 lines and took 4 us to come back.)
-        if (lane == 0) {
-            if (p.resid_in) {
-                const uint32_t rb = (uint32_t)H * 4u;
-                mbar_expect_tx(&s.xready, rb + (p.update_in ? rb : 0u) + (uint32_t)H * 2u);
-                bulk_load(xraw_s, p.resid_in, rb, &s.xready);
-                if (p.update_in) bulk_load(uraw_s, p.update_in, rb, &s.xready);
-            } else {
-                const uint32_t xb = (uint32_t)H * (p.hidden_dtype == FK_F32 ? 4u : 2u);
-                mbar_expect_tx(&s.xready, xb + (uint32_t)H * 2u);
-                bulk_load(xraw_s, p.hidden, xb, &s.xready);
-            }
-            bulk_load(nw_s, p.norm_weight, (uint32_t)H * 2u, &s.xready);
-        }
-    }
-
-    const D1Plan pl = make_plan(p, blk, G);
-    const int nA = pl.nA_router + pl.nA_gate + pl.nA_pair;
-    const int nB = pl.nB_pair + pl.nB_down;
-    const int total = nA + nB + pl.nC;
-    const __nv_bfloat16* router_w = reinterpret_cast<const __nv_bfloat16*>(p.router_weight);
-    const __nv_bfloat16* gate_up = reinterpret_cast<const __nv_bfloat16*>(p.gate_up);
-    const __nv_bfloat16* down = reinterpret_cast<const __nv_bfloat16*>(p.down);
-    const __nv_bfloat16* sgu = reinterpret_cast<const __nv_bfloat16*>(p.shared_gate_up);
-    const __nv_bfloat16* sdn = reinterpret_cast<const __nv_bfloat16*>(p.shared_down);
-
-    if (warp == kD1Consumers) {
-        // ------------------------------------------------------------------ producer warp
-        // Lane l owns ring slot l: the lanes decode and issue up to kD1Stages stages side by side, so the
-        // issue rate does not depend on one thread's instruction latency.
-        auto issue = [&](int it, bool wait) {
-            const D1Stage st = decode_stage(pl, p, it, blk, G);
-            const int slot = it % kD1Stages;
-            const uint32_t par = (it / kD1Stages) & 1u;
-            const __nv_bfloat16 *src0 = nullptr, *src1 = nullptr;
-            uint32_t bytes0 = 0, bytes1 = 0;
-            switch (st.kind) {
-                case kRouterRow: src0 = router_w + (size_t)st.a * H; bytes0 = H * 2; break;
-                case kGateRow: src0 = reinterpret_cast<const __nv_bfloat16*>(p.shared_gate); bytes0 = H * 2; break;
-                case kSharedPair:
-                    src0 = sgu + (size_t)st.a * H; src1 = sgu + (size_t)(I + st.a) * H; bytes0 = bytes1 = H * 2; break;
-                case kRoutedPair: {
-                    const __nv_bfloat16* w = gate_up + (size_t)s.ids[st.a] * 2 * I * H;
-                    src0 = w + (size_t)st.b * H; src1 = w + (size_t)(I + st.b) * H; bytes0 = bytes1 = H * 2; break;
-                }
-                case kSharedDown: src0 = sdn + (size_t)(pl.h0 + st.a) * I; bytes0 = st.b * I * 2; break;
-                case kRoutedDown:
-                    src0 = down + ((size_t)s.ids[st.a] * H + pl.h0 + st.b) * I; bytes0 = st.c * I * 2; break;
-                default: break;
-            }
-            if (wait) mbar_wait(&s.empty[slot], par ^ 1u, &s.abort_flag);
-            s.desc[slot] = make_int4(st.kind, st.a, st.b, st.c);
-            mbar_expect_tx(&s.full[slot], bytes0 + bytes1);
-            bulk_load(s.stage[slot], src0, bytes0, &s.full[slot]);
-            if (bytes1) bulk_load(s.stage[slot] + bytes0, src1, bytes1, &s.full[slot]);
-        };
-        for (int base = 0; base < nA; base += kD1Stages) {            // phase A: static addresses
-            const int it = base + lane;
-            if (lane < kD1Stages && it < nA) issue(it, true);
-        }
+        barriers_ready_arrive();                  // does not wait
+        // routing-independent copies that do not go through the ring: the block's router rows ...
+        if (lane == 0) mbar_expect_tx(&s.rrfull, (uint32_t)(pl.nrr * H * 2));
         __syncwarp();
-        __syncthreads();                                               // the consumers may use the barriers from here on
-        if (lane == 0) D1_TRACE(2);
-        mbar_wait(&s.ids_ready, 0, &s.abort_flag);                     // the consumers select the experts
-        if (lane == 0) D1_TRACE(4);
-        // phases B and C: addresses depend on the ids only, so C is issued as soon as ring slots free up
-        for (int base = (nA / kD1Stages) * kD1Stages; base < total; base += kD1Stages) {
-            const int it = base + lane;
-            if (lane < kD1Stages && it >= nA && it < total) issue(it, true);
+        if (lane < pl.nrr) {
+            const void* src = lane == pl.gate_row ? p.shared_gate
+                                                  : (const void*)(reinterpret_cast<const __nv_bfloat16*>(p.router_weight) + (size_t)(blk + lane * G) * H);
+            bulk_load(s.rrow[lane], src, (uint32_t)H * 2, &s.rrfull);
         }
+        // ... and the shared expert's down tile of the block's output rows
+        if (has_shared && pl.tile >= 0) {
+            if (lane == 16) mbar_expect_tx(&s.sdfull, kD1Consumers * 2048);
+            __syncwarp();
+            if (lane >= 16 && lane < 16 + kD1Consumers)
+                tma_load_2d(s.sdown[lane - 16], &sdn_map, (lane - 16) * 64, pl.tile * kD1Tile, &s.sdfull);
+        }
+        // Lane l owns ring slot l: the lanes issue up to kD1Stages stages side by side.  One loop (one copy of the
+        // issue code) serves all phases.  Its first lap issues the stages that depend neither on the routing nor
+        // on the kernel before this one (the shared expert's gate_up tiles); the token follows as soon as that
+        // kernel has completed; stages whose addresses depend on the ids wait for the select warp; the down tiles
+        // are issued as ring slots free up.
+        const int nstatic = 2 * max(0, min(pl.atoms, pl.shared_atoms - pl.atom0)) * kD1Consumers;   // stages of shared atoms
+        const int total = (pl.nB + pl.nC) * kD1Consumers;
+        bool token_issued = false, have_ids = false;
+#pragma unroll 1
+        for (int base = 0; base < total || !token_issued; base += kD1Stages) {
+#pragma unroll 1
+            for (int half = 0; half < 2; ++half) {
+                const int it = base + lane;
+                if (half == 1) {
+                    if (!token_issued) {
+                        token_issued = true;
+                        if (lane == 0) D1_TRACE(1);
+                        pdl_wait();                               // the token (and the barrier words) may come from the kernel before
+                        if (lane == 0) D1_TRACE(20);
+                        if (lane == 0) {
+                            // One copy of the token and of the norm weights per block.  (Plain loads by every consumer
+                            // warp of every block all hit the same few L2 lines and took 4 us to come back.)
+                            if (p.resid_in) {
+                                const uint32_t rb = (uint32_t)H * 4u;
+                                mbar_expect_tx(&s.xready, rb + (p.update_in ? rb : 0u) + (uint32_t)H * 2u);
+                                bulk_load(s.xraw, p.resid_in, rb, &s.xready);
+                                if (p.update_in) bulk_load(s.uraw, p.update_in, rb, &s.xready);
+                            } else {
+                                mbar_expect_tx(&s.xready, (uint32_t)H * 4u);
+                                bulk_load(s.xraw, p.hidden, (uint32_t)H * 2u, &s.xready);
+                            }
+                            bulk_load(s.nw, p.norm_weight, (uint32_t)H * 2u, &s.xready);
+                            // this launch's tag: one load per block, handed to the other warps with the token
+                            s.tag = ld_relaxed_u32(p.bar + 3) + 1u;
+                            mbar_arrive(&s.xready);
+                        }
+                        __syncwarp();
+                    }
+                    if (!have_ids && base + kD1Stages > nstatic && base < total) {
+                        have_ids = true;
+                        if (lane == 0) {
+                            // a short pause between polls: this warp shares its scheduler with the warp that publishes the logits
+                            const long long t0 = clock64();
+                            while (!mbar_try_wait(&s.ids_ready, 0)) {
+                                __nanosleep(32);
+                                if (clock64() - t0 > kWaitCycles) { s.abort_flag = 1; break; }
+                            }
+                            D1_TRACE(4);
+                        }
+                        __syncwarp();
+                    }
+                }
+                if (lane < kD1Stages && it < total && ((it < nstatic) == (half == 0))) {
+                    const int n = it >> 3, w = it & 7;            // stage n of warp w
+                    const int slot = it % kD1Stages;
+                    const uint32_t par = (it / kD1Stages) & 1u;
+                    mbar_wait(&s.empty[slot], par ^ 1u, &s.abort_flag);      // passes at once on a slot's first lap
+                    unsigned char* dst = s.stage[slot];
+                    if (n < pl.nB) {
+                        // gate (even n) or up (odd n) tile of atom n / 2, columns [256 w, 256 w + 256)
+                        const int g = pl.atom0 + (n >> 1);
+                        const CUtensorMap* map;
+                        int y;
+                        if (g < pl.shared_atoms) {
+                            map = &sgu_map;
+                            y = g * kD1Tile;
+                        } else {
+                            const int q = g - pl.shared_atoms;
+                            map = &gu_map;
+                            y = s.ids[q / (I / kD1Tile)] * 2 * I + (q % (I / kD1Tile)) * kD1Tile;
+                        }
+                        if (n & 1) y += I;
+                        mbar_expect_tx(&s.full[slot], kD1StageBytes);
+#pragma unroll
+                        for (int sl = 0; sl < 4; ++sl) tma_load_2d(dst + sl * 2048, map, w * 256 + sl * 64, y, &s.full[slot]);
+                    } else {
+                        // down tiles of four slots, columns [64 w, 64 w + 64) of the block's 16 output rows
+                        const int c = n - pl.nB;
+                        const int nu = min(4, p.top_k - c * 4);
+                        mbar_expect_tx(&s.full[slot], (uint32_t)nu * 2048u);
+                        for (int u = 0; u < nu; ++u)
+                            tma_load_2d(dst + u * 2048, &dn_map, w * 64, s.ids[c * 4 + u] * H + pl.tile * kD1Tile, &s.full[slot]);
+                    }
+                }
+                __syncwarp();
+            }
+        }
+        if (lane == 0) D1_TRACE(14);
+    } else if (warp == kD1Consumers + 1) {
+        // ------------------------------------------------------------------ select warp
+        barriers_ready_wait();
+        pdl_wait();
+        mbar_wait_spin(&s.xready, 0, kWaitCycles, &s.abort_flag);      // the tag travels with the token
+        if (p.E <= 256) poll_and_select<8>(p, s, lane, blk == 0);
+        else poll_and_select<32>(p, s, lane, blk == 0);
+        if (lane == 0) { mbar_arrive(&s.ids_ready); D1_TRACE(19); }
     } else {
         // ------------------------------------------------------------------ consumer warps
-        __syncthreads();                                               // ring barriers initialised by the producer warp
         const int cthreads = kD1Consumers * 32;
-        mbar_wait(&s.xready, 0, &s.abort_flag);
-        // the token's activations, 8 consecutive columns of every 256-column chunk per lane
-        float x[8][8];
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            if (j < nchH) {
-                const size_t el = (size_t)j * 256 + lane * 8;
-                if (p.resid_in) {
-                    const uint4 a = lds128(xraw_s + el * 4), b = lds128(xraw_s + el * 4 + 16);
-                    x[j][0] = __uint_as_float(a.x); x[j][1] = __uint_as_float(a.y); x[j][2] = __uint_as_float(a.z); x[j][3] = __uint_as_float(a.w);
-                    x[j][4] = __uint_as_float(b.x); x[j][5] = __uint_as_float(b.y); x[j][6] = __uint_as_float(b.z); x[j][7] = __uint_as_float(b.w);
-                    if (p.update_in) {
-                        const uint4 c = lds128(uraw_s + el * 4), d = lds128(uraw_s + el * 4 + 16);
-                        x[j][0] += __uint_as_float(c.x); x[j][1] += __uint_as_float(c.y); x[j][2] += __uint_as_float(c.z); x[j][3] += __uint_as_float(c.w);
-                        x[j][4] += __uint_as_float(d.x); x[j][5] += __uint_as_float(d.y); x[j][6] += __uint_as_float(d.z); x[j][7] += __uint_as_float(d.w);
-                    }
-                } else if (p.hidden_dtype == FK_BF16) {
-                    const uint4 v = lds128(xraw_s + el * 2);
-                    x[j][0] = bf16lo(v.x); x[j][1] = bf16hi(v.x); x[j][2] = bf16lo(v.y); x[j][3] = bf16hi(v.y);
-                    x[j][4] = bf16lo(v.z); x[j][5] = bf16hi(v.z); x[j][6] = bf16lo(v.w); x[j][7] = bf16hi(v.w);
-                } else if (p.hidden_dtype == FK_F32) {
-                    const uint4 a = lds128(xraw_s + el * 4), b = lds128(xraw_s + el * 4 + 16);
-                    x[j][0] = __uint_as_float(a.x); x[j][1] = __uint_as_float(a.y); x[j][2] = __uint_as_float(a.z); x[j][3] = __uint_as_float(a.w);
-                    x[j][4] = __uint_as_float(b.x); x[j][5] = __uint_as_float(b.y); x[j][6] = __uint_as_float(b.z); x[j][7] = __uint_as_float(b.w);
-                } else {
-                    const uint4 v = lds128(xraw_s + el * 2);
-                    const __half2* h = reinterpret_cast<const __half2*>(&v);
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        const float2 f = __half22float2(h[i]);
-                        x[j][2 * i] = f.x; x[j][2 * i + 1] = f.y;
-                    }
-                }
-            } else {
-#pragma unroll
-                for (int i = 0; i < 8; ++i) x[j][i] = 0.f;
-            }
-        }
+        const int gid = lane >> 2, tig = lane & 3;
+        barriers_ready_wait();
+        pdl_wait();
+        mbar_wait_spin(&s.xready, 0, kWaitCycles, &s.abort_flag);
+        if (tid == 0) D1_TRACE(2);
 
+        // ---- the token: this lane's 8 columns of the warp's K-slice
+        const int c0 = warp * 256 + lane * 8;
+        float xv[8];
+        const unsigned char* xsrc = s.xraw;                    // bf16 source of the MMA B operand
         if (p.resid_in) {
-            // layer-stack mode: x holds the new residual stream.  This block stores its slice of it, then the token
-            // is its unit-gain RMS norm rounded to the activation dtype, exactly what a separate norm kernel would
-            // have handed over.
-            if (warp == 1) {
-#pragma unroll
-                for (int j = 0; j < 8; ++j) {
-#pragma unroll
-                    for (int i = 0; i < 8; ++i) {
-                        const int col = j * 256 + lane * 8 + i;
-                        if (j < nchH && col >= pl.h0 && col < pl.h0 + pl.nh) p.resid_out[col] = x[j][i];
-                    }
-                }
+            // layer-stack mode: the new residual stream is resid_in + update_in; the block stores its 16 columns of
+            // it, and the token is its unit-gain RMS norm rounded to bf16, exactly what a separate norm kernel
+            // would have handed over
+            const uint4 a = lds128(s.xraw + (size_t)c0 * 4), b = lds128(s.xraw + (size_t)c0 * 4 + 16);
+            xv[0] = __uint_as_float(a.x); xv[1] = __uint_as_float(a.y); xv[2] = __uint_as_float(a.z); xv[3] = __uint_as_float(a.w);
+            xv[4] = __uint_as_float(b.x); xv[5] = __uint_as_float(b.y); xv[6] = __uint_as_float(b.z); xv[7] = __uint_as_float(b.w);
+            if (p.update_in) {
+                const uint4 c = lds128(s.uraw + (size_t)c0 * 4), d = lds128(s.uraw + (size_t)c0 * 4 + 16);
+                xv[0] += __uint_as_float(c.x); xv[1] += __uint_as_float(c.y); xv[2] += __uint_as_float(c.z); xv[3] += __uint_as_float(c.w);
+                xv[4] += __uint_as_float(d.x); xv[5] += __uint_as_float(d.y); xv[6] += __uint_as_float(d.z); xv[7] += __uint_as_float(d.w);
+            }
+            if (pl.tile >= 0 && c0 >= pl.tile * kD1Tile && c0 < (pl.tile + 1) * kD1Tile) {
+                *reinterpret_cast<float4*>(p.resid_out + c0) = make_float4(xv[0], xv[1], xv[2], xv[3]);
+                *reinterpret_cast<float4*>(p.resid_out + c0 + 4) = make_float4(xv[4], xv[5], xv[6], xv[7]);
             }
             float so = 0.f;
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
+            for (int i = 0; i < 8; ++i) so = fmaf(xv[i], xv[i], so);
+            so = warp_sum(so);
+            if (lane == 0) s.sopart[warp] = so;
+            named_bar_sync(1, cthreads);
+            float tot = 0.f;
 #pragma unroll
-                for (int i = 0; i < 8; ++i) so = fmaf(x[j][i], x[j][i], so);
+            for (int w = 0; w < kD1Consumers; ++w) tot += s.sopart[w];
+            const float inv = rsqrtf(tot / (float)H + p.resid_eps);
+            __nv_bfloat162 packed[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                packed[i] = __floats2bfloat162_rn(xv[2 * i] * inv, xv[2 * i + 1] * inv);
+                const float2 f = __bfloat1622float2(packed[i]);
+                xv[2 * i] = f.x; xv[2 * i + 1] = f.y;
             }
-            const float inv = rsqrtf(warp_sum(so) / (float)H + p.resid_eps);
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-#pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    const float v = x[j][i] * inv;
-                    x[j][i] = p.hidden_dtype == FK_BF16 ? __bfloat162float(__float2bfloat16_rn(v))
-                            : (p.hidden_dtype == FK_F16 ? __half2float(__float2half_rn(v)) : v);
-                }
-            }
+            *reinterpret_cast<uint4*>(s.xb + (size_t)c0 * 2) = *reinterpret_cast<const uint4*>(packed);
+            __syncwarp();                                      // the warp reads back only its own K-slice
+            xsrc = s.xb;
+        } else {
+            const uint4 v = lds128(s.xraw + (size_t)c0 * 2);
+            xv[0] = bf16lo(v.x); xv[1] = bf16hi(v.x); xv[2] = bf16lo(v.y); xv[3] = bf16hi(v.y);
+            xv[4] = bf16lo(v.z); xv[5] = bf16hi(v.z); xv[6] = bf16lo(v.w); xv[7] = bf16hi(v.w);
         }
-        float ss = 0.f;
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-#pragma unroll
-            for (int i = 0; i < 8; ++i) ss = fmaf(x[j][i], x[j][i], ss);
-        }
-        const float rstd = rsqrtf(warp_sum(ss) / (float)H + p.eps);
-        if (tid == 0) D1_TRACE(10);
-        // warp 0 publishes x * gain for the router rows (rows are spread over the warps)
-        if (warp == 0) {
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                if (j < nchH) {
-                    const int c = j * 256 + lane * 8;
-                    const uint4 g = lds128(nw_s + (size_t)c * 2);
-                    const float o = p.norm_offset;
-                    float4 lo = make_float4(x[j][0] * (o + bf16lo(g.x)), x[j][1] * (o + bf16hi(g.x)),
-                                            x[j][2] * (o + bf16lo(g.y)), x[j][3] * (o + bf16hi(g.y)));
-                    float4 hi = make_float4(x[j][4] * (o + bf16lo(g.z)), x[j][5] * (o + bf16hi(g.z)),
-                                            x[j][6] * (o + bf16lo(g.w)), x[j][7] * (o + bf16hi(g.w)));
-                    *reinterpret_cast<float4*>(xg_s + c) = lo;
-                    *reinterpret_cast<float4*>(xg_s + c + 4) = hi;
-                }
-            }
-        }
-        named_bar_sync(1, cthreads);
 
-        int phase = 0;
-        for (int it = warp;;) {
-            const int limit = phase == 0 ? nA : (phase == 1 ? nA + nB : total);
-            if (it >= limit) {
-                // phase boundary: every consumer warp passes here exactly once per phase
-                if (phase == 0) {
-                    // publish phase A (logits, shared activations, gate); when every block has, select the experts
-                    if (tid == 0) D1_TRACE(13);
-                    __threadfence();
-                    if (tid == 0) D1_TRACE(14);
-                    named_bar_sync(1, cthreads);
-                    if (tid == 0) {
-                        atomicAdd(p.bar + 0, 1u);
-                        D1_TRACE(1);
-                        spin_until(p.bar + 0, (unsigned)G, &s.abort_flag);
-                        D1_TRACE(3);
-                        // What the other blocks published is fetched by ONE bulk copy per block.  (Plain loads by
-                        // every thread of every block pile thousands of requests onto a handful of L2 lines.)
-                        fence_proxy_async();
-                        const uint32_t sb = p.shared_gate_up ? (uint32_t)I * 4u : 0u;
-                        mbar_expect_tx(&s.staged_a, (uint32_t)p.E * 4u + sb);
-                        bulk_load(ract_s, p.logits, (uint32_t)p.E * 4u, &s.staged_a);
-                        if (sb) bulk_load(sact_s, p.sact, sb, &s.staged_a);
-                    }
-                    if (!p.shared_gate_up && tid < I / 4) reinterpret_cast<float4*>(sact_s)[tid] = make_float4(0.f, 0.f, 0.f, 0.f);
-                    named_bar_sync(1, cthreads);
-                    mbar_wait(&s.staged_a, 0, &s.abort_flag);
-                    block_topk(p, s, ract_s, tid, cthreads, blk == 0);
-                    if (tid == 0) mbar_arrive(&s.ids_ready);
-                    fence_proxy_async();              // the softmax scratch is overwritten by a bulk copy later
-                    named_bar_sync(1, cthreads);
-                } else if (phase == 1) {
-                    // publish the routed activations, wait for every block's, stage them in shared memory
-                    __threadfence();
-                    named_bar_sync(1, cthreads);
-                    if (tid == 0) {
-                        atomicAdd(p.bar + 1, 1u);
-                        D1_TRACE(5);
-                        spin_until(p.bar + 1, (unsigned)G, &s.abort_flag);
-                        D1_TRACE(6);
-                        fence_proxy_async();
-                        const uint32_t rb = (uint32_t)(p.top_k * I) * 4u;
-                        mbar_expect_tx(&s.staged_b, rb);
-                        bulk_load(ract_s, p.ract, rb, &s.staged_b);
-                    }
-                    named_bar_sync(1, cthreads);
-                    mbar_wait(&s.staged_b, 0, &s.abort_flag);
-                } else {
-                    break;
+        // ---- router rows (and the shared-expert gate vector): K-slice sums on the CUDA cores
+        {
+            float ss = 0.f;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) ss = fmaf(xv[i], xv[i], ss);
+            const uint4 g = lds128(s.nw + (size_t)c0 * 2);
+            const float o = p.norm_offset;
+            float xg[8];
+            xg[0] = xv[0] * (o + bf16lo(g.x)); xg[1] = xv[1] * (o + bf16hi(g.x)); xg[2] = xv[2] * (o + bf16lo(g.y)); xg[3] = xv[3] * (o + bf16hi(g.y));
+            xg[4] = xv[4] * (o + bf16lo(g.z)); xg[5] = xv[5] * (o + bf16hi(g.z)); xg[6] = xv[6] * (o + bf16lo(g.w)); xg[7] = xv[7] * (o + bf16hi(g.w));
+            mbar_wait(&s.rrfull, 0, &s.abort_flag);
+            // all rows' K-slice sums are reduced together (independent shuffle chains), then lane r keeps row r
+            float racc[kD1MaxRouterRows + 1];
+#pragma unroll
+            for (int r = 0; r < kD1MaxRouterRows; ++r) {
+                racc[r] = 0.f;
+                if (r < pl.nrr) {
+                    const uint4 w = lds128(s.rrow[r] + (size_t)c0 * 2);
+                    const bool gate = r == pl.gate_row;            // the gate vector meets the raw token
+                    float a0, a1;
+                    a0 = bf16lo(w.x) * (gate ? xv[0] : xg[0]);       a1 = bf16hi(w.x) * (gate ? xv[1] : xg[1]);
+                    a0 = fmaf(bf16lo(w.y), gate ? xv[2] : xg[2], a0); a1 = fmaf(bf16hi(w.y), gate ? xv[3] : xg[3], a1);
+                    a0 = fmaf(bf16lo(w.z), gate ? xv[4] : xg[4], a0); a1 = fmaf(bf16hi(w.z), gate ? xv[5] : xg[5], a1);
+                    a0 = fmaf(bf16lo(w.w), gate ? xv[6] : xg[6], a0); a1 = fmaf(bf16hi(w.w), gate ? xv[7] : xg[7], a1);
+                    racc[r] = a0 + a1;
                 }
-                ++phase;
-                continue;
             }
-            const int slot = it % kD1Stages;
-            const uint32_t par = (it / kD1Stages) & 1u;
-            mbar_wait(&s.full[slot], par, &s.abort_flag);
-            if (tid == 0 && it == 0) D1_TRACE(11);
-            const int4 st = s.desc[slot];                  // kind, a, b, c (see decode_stage)
-            const unsigned char* base = s.stage[slot];
-            float dep = 0.f;
-            if (st.x == kSharedPair || st.x == kRoutedPair || st.x == kGateRow) {
-                float g, u;
-                pair_dot(base, base + (size_t)H * 2, x, lane, nchH, g, u);   // the gate row has no partner: u is unused
-                dep = g + u;
-                if (lane == 0) {
-                    if (st.x == kGateRow) *p.sgate = sigmoidf_(g);
-                    else if (st.x == kSharedPair) p.sact[st.y] = silu_mul(g, u);
-                    else p.ract[(size_t)st.y * I + st.z] = silu_mul(g, u);
-                }
-            } else if (st.x == kRouterRow) {
-                const float acc = row_dot_smem(base, xg_s, lane, nchH);
-                dep = acc;
-                if (lane == 0) {
-                    float logit = acc * rstd;
-                    if (p.router_bias) logit += p.router_bias[st.y];
-                    p.logits[st.y] = logit;
-                }
-            } else {
-                const bool routed = st.x == kRoutedDown;
-                const float* vec = routed ? ract_s + (size_t)st.y * I : sact_s;
-                const int row0 = routed ? st.z : st.y, nrows = routed ? st.w : st.z;
-                // rows_per_stage <= 8 is checked on the host
-                const float d = rows8_dot_smem(base, I * 2, nrows, vec, lane, nchI);
-                dep = d;
-                const int r = lane >> 2;
-                if ((lane & 3) == 0 && r < nrows) {
-                    if (routed) s.dpart[st.y][row0 + r] = d;
-                    else s.ysh[row0 + r] = d;
-                }
+            racc[kD1MaxRouterRows] = ss;
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+#pragma unroll
+                for (int r = 0; r <= kD1MaxRouterRows; ++r) racc[r] += __shfl_xor_sync(kFull, racc[r], o);
             }
             if (lane == 0) {
-                // the data dependence keeps the release behind the last use of the stage
-                asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&s.empty[slot])), "f"(dep) : "memory");
+#pragma unroll
+                for (int r = 0; r <= kD1MaxRouterRows; ++r) s.rpart[r][warp] = racc[r];
+                mbar_arrive(&s.rdone);
             }
-            if (tid == 0 && it == 0) D1_TRACE(12);
-            it += kD1Consumers;
+            __syncwarp();
+            if (warp == 0) {
+                // the eight K-slices meet here, in warp order
+                mbar_wait_spin(&s.rdone, 0, kWaitCycles, &s.abort_flag);
+                if (lane < pl.nrr) {
+                    float acc = 0.f, sq = 0.f;
+#pragma unroll
+                    for (int w = 0; w < kD1Consumers; ++w) { acc += s.rpart[lane][w]; sq += s.rpart[kD1MaxRouterRows][w]; }
+                    if (lane == pl.gate_row) {
+                        *p.sgate = sigmoidf_(acc);
+                    } else {
+                        const int e = blk + lane * G;
+                        float logit = acc * rsqrtf(sq / (float)H + p.eps);
+                        if (p.router_bias) logit += p.router_bias[e];
+                        // an atomic is performed at L2 at once; a plain store was seen by the pollers a microsecond later
+                        atomicExch(p.tagged + e, ((unsigned long long)s.tag << 32) | (unsigned long long)__float_as_uint(logit));
+                        p.logits[e] = logit;
+                    }
+                }
+                if (lane == 0) D1_TRACE(3);
+            }
         }
 
-        named_bar_sync(1, cthreads);
-        if (tid == 0) D1_TRACE(15);
-        if (tid < pl.nh) {
-            float acc = 0.f;
-            for (int sl = 0; sl < p.top_k; ++sl) acc = fmaf(s.wnorm[sl], s.dpart[sl][tid], acc);
-            if (p.shared_gate_up) {
-                const float sh = s.ysh[tid];
-                acc += p.shared_gate ? __ldcg(p.sgate) * sh : sh;
+        // ---- phase B: gate and up tiles against the token (column 0 of the MMA's B operand lives in lanes 0..3)
+        uint32_t bx[16][2];
+#pragma unroll
+        for (int ks = 0; ks < 16; ++ks) {
+            const unsigned char* src = xsrc + (size_t)(warp * 256 + ks * 16 + 2 * tig) * 2;
+            bx[ks][0] = gid == 0 ? d1_lds32(src) : 0u;
+            bx[ks][1] = gid == 0 ? d1_lds32(src + 16) : 0u;
+        }
+#pragma unroll 1
+        for (int n = 0; n < pl.nB; ++n) {
+            const int it = n * kD1Consumers + warp;
+            const int slot = it % kD1Stages;
+            mbar_wait(&s.full[slot], (it / kD1Stages) & 1u, &s.abort_flag);
+            if (tid == 0 && n == 0) D1_TRACE(11);
+            const uint32_t base = smem_u32(s.stage[slot]);
+            float c[4][4];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) { c[q][0] = c[q][1] = c[q][2] = c[q][3] = 0.f; }
+#pragma unroll
+            for (int sl = 0; sl < 4; ++sl) box_mma(c[sl], base + sl * 2048, &bx[sl * 4], lane);
+            const float v0 = (c[0][0] + c[1][0]) + (c[2][0] + c[3][0]);      // tile row gid     (lanes with tig == 0)
+            const float v2 = (c[0][2] + c[1][2]) + (c[2][2] + c[3][2]);      // tile row gid + 8
+            if (tig == 0) {
+                s.bpart[n][warp][gid] = v0;
+                s.bpart[n][warp][gid + 8] = v2;
             }
-            p.out[pl.h0 + tid] = acc;
-            if (p.layer_hidden && !p.resid_in) p.layer_hidden[pl.h0 + tid] = load_any(p.hidden, p.hidden_dtype, (size_t)(pl.h0 + tid)) + acc;
+            if (lane == 0) d1_release(&s.empty[slot], v0 + v2);
+        }
+        // the K-slices of every tile meet; SwiGLU; the activations are published as bf16 head + remainder
+        named_bar_sync(1, cthreads);
+        if (tid < pl.atoms * kD1Tile) {
+            const int j = tid >> 4, r = tid & 15;
+            float gsum = 0.f, usum = 0.f;
+#pragma unroll
+            for (int w = 0; w < kD1Consumers; ++w) { gsum += s.bpart[2 * j][w][r]; usum += s.bpart[2 * j + 1][w][r]; }
+            const float act = silu_mul(gsum, usum);
+            const int g = pl.atom0 + j;
+            int idx;
+            if (g < pl.shared_atoms) idx = shared_slot * I + g * kD1Tile + r;
+            else idx = (g - pl.shared_atoms) * kD1Tile + r;                   // slot * I + pair
+            const __nv_bfloat16 hi = __float2bfloat16_rn(act);
+            act_hi_g[idx] = hi;
+            act_lo_g[idx] = __float2bfloat16_rn(act - __bfloat162float(hi));
+        }
+        named_bar_sync(1, cthreads);
+        if (tid == 0) {
+            // the block's stores happen before this thread's fence (the barrier above), the fence makes them visible
+            // to whoever sees the arrival
+            D1_TRACE(5);
+            __threadfence();
+            atomicAdd(p.bar + 1, 1u);
+        }
+
+        if (pl.tile >= 0) {
+            // ---- phase C: the block's 16 output rows
+            if (tid == 0) {
+                // the counter is never reset: launch number t (== its tag, both count from 1) ends at t * G arrivals
+                spin_until(p.bar + 1, s.tag * (unsigned)G, p.wait_cycles, &s.abort_flag);
+                // every block has read the tag by now (it arrived): block 0 advances it for the next launch
+                if (blk == 0) p.bar[3] = s.tag;
+                D1_TRACE(6);
+                fence_proxy_async();
+                const uint32_t ab = (uint32_t)((p.top_k + (has_shared ? 1 : 0)) * I * 2);
+                mbar_expect_tx(&s.staged_b, 2u * ab);
+                bulk_load(s.act_hi, act_hi_g, ab, &s.staged_b);
+                bulk_load(s.act_lo, act_lo_g, ab, &s.staged_b);
+            }
+            __syncwarp();
+            // what the output rows need from global memory is fetched while the activations are on their way
+            float gate_v = 1.f, resid_v = 0.f;
+            if (tid < kD1Tile * kD1Consumers) {
+                if (has_shared && p.shared_gate) gate_v = __ldcg(p.sgate);
+                if (p.layer_hidden && !p.resid_in) resid_v = load_any(p.hidden, p.hidden_dtype, (size_t)(pl.tile * kD1Tile + (tid >> 3)));
+            }
+            mbar_wait(&s.staged_b, 0, &s.abort_flag);
+            if (tid == 0) D1_TRACE(12);
+            // one [16 x 64] down box of slot `sl` against that slot's activations (head and remainder): K-slice sums
+            auto down_box = [&](int sl, uint32_t box_addr) -> float {
+                uint32_t bh[4][2], bl[4][2];
+                const size_t off = ((size_t)sl * I + warp * 64 + 2 * tig) * 2;
+#pragma unroll
+                for (int kk = 0; kk < 4; ++kk) {
+                    bh[kk][0] = gid == 0 ? d1_lds32(s.act_hi + off + kk * 32) : 0u;
+                    bh[kk][1] = gid == 0 ? d1_lds32(s.act_hi + off + kk * 32 + 16) : 0u;
+                    bl[kk][0] = gid == 0 ? d1_lds32(s.act_lo + off + kk * 32) : 0u;
+                    bl[kk][1] = gid == 0 ? d1_lds32(s.act_lo + off + kk * 32 + 16) : 0u;
+                }
+                float ch[4] = {0.f, 0.f, 0.f, 0.f}, cl[4] = {0.f, 0.f, 0.f, 0.f};
+                box_mma(ch, box_addr, bh, lane);
+                box_mma(cl, box_addr, bl, lane);
+                const float v0 = ch[0] + cl[0], v2 = ch[2] + cl[2];
+                if (tig == 0) {
+                    s.cpart[sl][warp][gid] = v0;
+                    s.cpart[sl][warp][gid + 8] = v2;
+                }
+                return v0 + v2;
+            };
+            if (has_shared) {
+                mbar_wait(&s.sdfull, 0, &s.abort_flag);
+                down_box(shared_slot, smem_u32(s.sdown[warp]));
+            }
+#pragma unroll 1
+            for (int cst = 0; cst < pl.nC; ++cst) {
+                const int it = (pl.nB + cst) * kD1Consumers + warp;
+                const int slot = it % kD1Stages;
+                mbar_wait(&s.full[slot], (it / kD1Stages) & 1u, &s.abort_flag);
+                const uint32_t base = smem_u32(s.stage[slot]);
+                const int nu = min(4, p.top_k - cst * 4);
+                float dep = 0.f;
+#pragma unroll 4
+                for (int u = 0; u < nu; ++u) dep += down_box(cst * 4 + u, base + u * 2048);
+                if (lane == 0) d1_release(&s.empty[slot], dep);
+            }
+            named_bar_sync(1, cthreads);
+            if (tid == 0) D1_TRACE(13);
+            if (tid < kD1Tile * kD1Consumers) {
+                // thread (row, w) weights K-slice w of every slot, then the eight slices of a row meet by shuffles:
+                // a fixed order, so the result does not depend on scheduling
+                const int row = tid >> 3, w = tid & 7;
+                mbar_wait(&s.ids_ready, 0, &s.abort_flag);
+                float acc = 0.f;
+                for (int sl = 0; sl < p.top_k; ++sl) acc = fmaf(s.wnorm[sl], s.cpart[sl][w][row], acc);
+                if (has_shared) acc = fmaf(gate_v, s.cpart[shared_slot][w][row], acc);
+                acc += __shfl_xor_sync(kFull, acc, 1);
+                acc += __shfl_xor_sync(kFull, acc, 2);
+                acc += __shfl_xor_sync(kFull, acc, 4);
+                if (w == 0) {
+                    const int h = pl.tile * kD1Tile + row;
+                    p.out[h] = acc;
+                    if (p.layer_hidden && !p.resid_in) p.layer_hidden[h] = resid_v + acc;
+                }
+            }
+            if (tid == 0) D1_TRACE(15);
         }
     }
 
-    // leave: the last block to depart re-arms the barrier words for the next launch
+    // Nothing to re-arm on the way out: the arrival counter only grows (launch number x blocks) and the launch tag
+    // was advanced by block 0 once every block had read it.
     __syncthreads();
     if (tid == 0) {
         D1_TRACE(7);
-        if (p.trace) p.trace[(size_t)blk * 16 + 9] = (unsigned long long)clock64();
+        if (p.trace) p.trace[(size_t)blk * 32 + 9] = (unsigned long long)clock64();
         if (s.abort_flag && p.error_word) atomicExch(p.error_word, 2);
-        __threadfence();
-        const unsigned old = atomicAdd(p.bar + 2, 1u);
-        if (old == (unsigned)G - 1) {
-            p.bar[0] = 0u; p.bar[1] = 0u; p.bar[2] = 0u;
-            __threadfence();
-        }
     }
 }
 
+static size_t decode1_smem_bytes() { return sizeof(D1Smem) + 1024; }
+
+// one block per SM must fit (checked once per device)
+static bool decode1_resident() {
+    static int cached[64] = {0};          // 0 unknown, 1 yes, -1 no
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return false;
+    if (cached[dev] == 0) {
+        const int smem = (int)decode1_smem_bytes();
+        int n = 0;
+        bool ok = cudaFuncSetAttribute(decode1_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) == cudaSuccess &&
+                  cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, decode1_kernel, kD1Threads, smem) == cudaSuccess && n >= 1;
+        if (!ok) (void)cudaGetLastError();
+        cached[dev] = ok ? 1 : -1;
+    }
+    return cached[dev] == 1;
+}
+
 bool decode1_supported(const DecodeParams& p, int weight_dtype) {
-    if (weight_dtype != FK_BF16) return false;
-    if (p.H % 256 != 0 || p.H > 2048 || p.I % 256 != 0 || p.I > 512) return false;
-    if (p.top_k < 1 || p.E < p.top_k) return false;
+    if (weight_dtype != FK_BF16 || p.hidden_dtype != FK_BF16) return false;
+    if (p.H != kD1H || p.I != kD1I) return false;
+    if (p.top_k < 1 || p.top_k > FK_MAX_TOP_K || p.E < p.top_k || p.E > FK_MAX_EXPERTS) return false;
     const int G = sm_count();
-    if ((p.H + G - 1) / G + 1 > kD1MaxRows) return false;
+    const int tiles = kD1H / kD1Tile;
+    if (G < tiles) return false;                                              // every output tile needs a block
+    if ((p.E + G - 1) / G + (p.shared_gate ? 1 : 0) > kD1MaxRouterRows) return false;
+    const int total = (p.shared_gate_up ? kD1I / kD1Tile : 0) + p.top_k * (kD1I / kD1Tile);
+    if ((total + G - 1) / G > kD1MaxAtoms) return false;
     uintptr_t bits = reinterpret_cast<uintptr_t>(p.hidden) | reinterpret_cast<uintptr_t>(p.norm_weight) |
                      reinterpret_cast<uintptr_t>(p.router_weight) | reinterpret_cast<uintptr_t>(p.gate_up) |
                      reinterpret_cast<uintptr_t>(p.down) | reinterpret_cast<uintptr_t>(p.shared_gate_up) |
                      reinterpret_cast<uintptr_t>(p.shared_down) | reinterpret_cast<uintptr_t>(p.shared_gate) |
-                     reinterpret_cast<uintptr_t>(p.logits);
-    if (p.E % 4 != 0) return false;            // the logits travel as one bulk copy
+                     reinterpret_cast<uintptr_t>(p.act_hi) | reinterpret_cast<uintptr_t>(p.act_lo);
     bits |= reinterpret_cast<uintptr_t>(p.resid_in) | reinterpret_cast<uintptr_t>(p.update_in) | reinterpret_cast<uintptr_t>(p.resid_out);
-    return (bits & 15) == 0;
+    if (bits & 15) return false;
+    return decode1_resident();
 }
 
 int launch_decode1(const DecodeParams& p, cudaStream_t stream) {
-    const int smem = (int)(sizeof(D1Smem) + sizeof(float) * ((size_t)(FK_MAX_TOP_K + 1) * p.I + p.H) + (size_t)p.H * 10 + 128);
+    static const bool cooperative = [] { const char* e = getenv("FKMOE_D1_COOPERATIVE"); return e && e[0] == '1'; }();
+    const int smem = (int)decode1_smem_bytes();
     FK_CUDA_OK(cudaFuncSetAttribute(decode1_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem), "decode1 attr");
-    DecodeParams copy = p;
-    void* args[] = {&copy};
-    FK_CUDA_OK(cudaLaunchCooperativeKernel((const void*)decode1_kernel, dim3(sm_count()), dim3(kD1Threads), args, smem, stream),
-               "decode1 launch");
+    // [16 rows x 64 columns] boxes, 128-byte swizzle, cached per weight pointer
+    CUtensorMap gu{}, sgu{}, dn{}, sdn{};
+    const bool maps = weight_tensor_map(p.gate_up, (uint64_t)p.E * 2 * p.I, p.H, kD1Tile, &gu) &&
+                      weight_tensor_map(p.down, (uint64_t)p.E * p.H, p.I, kD1Tile, &dn) &&
+                      weight_tensor_map(p.shared_gate_up ? p.shared_gate_up : p.gate_up, 2 * (uint64_t)p.I, p.H, kD1Tile, &sgu) &&
+                      weight_tensor_map(p.shared_down ? p.shared_down : p.down, (uint64_t)p.H, p.I, kD1Tile, &sdn);
+    if (!maps) return FK_ERR_UNSUPPORTED;
+    DecodeParams q = p;
+    if (q.wait_cycles <= 0) q.wait_cycles = wait_limit_cycles();
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(sm_count());
+    cfg.blockDim = dim3(kD1Threads);
+    cfg.dynamicSmemBytes = (size_t)smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    if (cooperative) {
+        attr[0].id = cudaLaunchAttributeCooperative;
+        attr[0].val.cooperative = 1;
+        cfg.numAttrs = 1;
+    } else {
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    }
+    cfg.attrs = attr;
+    FK_CUDA_OK(cudaLaunchKernelEx(&cfg, decode1_kernel, gu, sgu, dn, sdn, q), "decode1 launch");
     note_launch();
     return FK_OK;
 }

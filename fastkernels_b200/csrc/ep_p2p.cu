@@ -75,8 +75,8 @@ __device__ __forceinline__ void ep_signal_and_wait(const EpPeers& ep, int slot0,
         // epochs only grow; the signed difference keeps the comparison right across a wrap
         while ((int)(ld_acquire_sys(flag) - epoch) < 0) {
             __nanosleep(64);
-            if (clock64() - t0 > kWaitCycles) {
-                atomicExch(reinterpret_cast<int*>(mine + 20), slot0 == 0 ? 1 : 2);
+            if (clock64() - t0 > ep.wait_cycles) {
+                atomicCAS(reinterpret_cast<int*>(mine + 20), 0, slot0 == 0 ? 1 : 2);     // the first wait that gave up is kept
                 break;
             }
         }

@@ -59,6 +59,7 @@ struct EpPeers {
     size_t partial_offset;     // EpLayout::partial
     int world, rank;           // world == 0: not expert parallel
     int tokens;                // tokens per rank
+    long long wait_cycles;     // limit of a wait on a peer's flag
 };
 
 struct EpDispatchParams {
@@ -115,7 +116,7 @@ int launch_experts_tc(const ExpertParams& p, __nv_bfloat16* xg, __nv_bfloat16* a
 // ordered weighted combine of the per-row outputs (+ shared expert, + residual)
 int launch_combine(const ExpertParams& p, cudaStream_t stream);
 
-// one token, whole layer, one cooperative launch (bf16 weights)
+// one token, whole layer, one launch (bf16 weights)
 struct DecodeParams {
     const void* hidden;
     int hidden_dtype;
@@ -134,14 +135,17 @@ struct DecodeParams {
     float* weights_mirror;
     float* out;                   // [H]
     float* layer_hidden;          // optional [H]
-    float* ract;                  // workspace [k, I]
-    float* sact;                  // workspace [I]
+    void* act_hi;                 // workspace bf16 [(k+1), I]: SwiGLU activations of the k slots and the shared expert, head
+    void* act_lo;                 // workspace bf16 [(k+1), I]: their remainders (activation = head + remainder to 2^-17)
     float* sgate;                 // workspace [1]
-    unsigned* bar;                // workspace [3]: arrive 1, arrive 2, depart (all zero between launches)
+    unsigned* bar;                // workspace [4]: unused, arrive, depart (zero between launches), launch epoch
+    unsigned long long* tagged;   // workspace [E]: (launch tag << 32 | logit bits), how the blocks exchange the logits
     int* error_word;
-    unsigned long long* trace;    // optional [blocks][8] nanosecond timestamps of the phase boundaries
+    unsigned long long* trace;    // optional [blocks][16] nanosecond timestamps of the phase boundaries
     int H, E, I, top_k;
     float eps, norm_offset;
+    long long wait_cycles;        // limit of every wait on another block (0: the library's current limit)
+
     // layer-stack mode (resid_in != null): the token is RMSNorm(resid_in + update_in) with unit gain, rounded to the
     // activation dtype of `hidden_dtype`; `hidden` is not read; resid_out receives resid_in + update_in
     const float* resid_in;        // [H] fp32 residual stream
@@ -152,6 +156,8 @@ struct DecodeParams {
 bool decode1_supported(const DecodeParams& p, int weight_dtype);
 int launch_decode1(const DecodeParams& p, cudaStream_t stream);
 int sm_count();
+// Limit, in SM clock cycles, of device-side waits on other blocks or ranks (fk_set_wait_limit_cycles; about a second by default)
+long long wait_limit_cycles();
 
 int launch_residual_norm(float* x, const float* update, void* normed, int out_dtype, int T, int H, float eps, cudaStream_t stream);
 

@@ -336,6 +336,7 @@ static int launch_experts_tc_t(const ExpertParams& p, __nv_bfloat16* xg, __nv_bf
         FK_CUDA_OK(launch_pdl(gather_rows_kernel, dim3(blocks), dim3(256), 0, stream, p, xg), "gather rows launch");
         FK_LAUNCH_OK("gather rows launch");
     }
+    stage_mark();   // end of the row gather
     TcParams tp{};
     tp.passes = p.passes; tp.meta = p.meta; tp.actb = actb; tp.y = p.y; tp.error_word = p.error_word; tp.H = p.H; tp.I = p.I;
     {

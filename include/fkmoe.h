@@ -59,8 +59,14 @@ typedef struct fk_moe_dims {
 #define FK_FLAG_FORCE_TENSOR 4u    /* use the tensor-core grouped GEMM whenever the shape allows */
 #define FK_FLAG_NO_FUSED_DECODE 8u /* T==1: run the staged kernels instead of the fused single-token kernel */
 #define FK_FLAG_REGISTER_GEMV 32u  /* grouped GEMV with direct global->register loads instead of the bulk-copy ring */
-#define FK_FLAG_TRACE 64u          /* T==1 fused kernel: write per-block phase timestamps (ns) at the start of the
-                                      workspace's y region: u64 [blocks][8]; fk_moe_trace_offset() gives the offset */
+#define FK_FLAG_TRACE 64u          /* T==1 fused kernel: write per-block phase timestamps at the start of the workspace's y
+                                      region, u64 [blocks][16] (fk_moe_trace_offset() gives the offset).  Nanoseconds of
+                                      the global timer in slots 0 entry, 1 constant copies issued, 2 token in shared
+                                      memory, 3 this block's logits published, 4 experts selected, 10 first expert
+                                      stage landed, 5 this block's activations published, 6 all blocks' published,
+                                      12 activations staged, 14 last copy issued, 13 down rows done, 15 output stored,
+                                      7 exit; 11 first stage landed; SM cycle counter in 8 (entry) and 9 (exit).
+                                      Ignored when the record (blocks * 128 bytes) does not fit the y region. */
 #define FK_FLAG_SKIP_FOREIGN 16u   /* ids outside [expert_base, expert_base+E) are skipped instead of clamped */
 #define FK_FLAG_WIDE_PASSES 128u   /* tcgen05 path: 128 tokens per pass instead of 64 (experts that see dozens of tokens) */
 
@@ -107,9 +113,23 @@ uint64_t fk_launch_count(void);
 /* Profiling aid, not a hot path: runs fk_moe_layer with CUDA events recorded on `stream`
  * between its stages, WAITS for the last one, and writes the stage durations in milliseconds
  * to stage_ms (room for 11) and their number to *stages.  Staged path: router, permute,
- * gate_up, down, combine.  No counterpart in the reference (it times with a host clock around
+ * [row gather, tensor-core path only], gate_up, down, combine; single-token kernel: one stage.  No counterpart in the reference (it times with a host clock around
  * a Python loop, e.g. bench/qwen36_real_moe_microbench.py:101-119). */
 int fk_moe_layer_timed(const fk_moe_call* call, void* stream, float* stage_ms, int* stages);
+
+/* Limit of every device-side wait on another block or another rank, in SM clock cycles (default: about one
+ * second; 0 restores the default).  A wait that runs out never traps and never spins on: the kernel raises an
+ * error word, finishes with undefined output, and the next fk_moe_status / fk_ep_status call reports it.
+ * Process-wide; applies to calls enqueued afterwards.  No counterpart in the reference, which has no
+ * device-side waits (each of its stages is a separate launch, e.g.
+ * src/fastkernels/kernels/triton/qwen36_expert.py:1249-1308). */
+int fk_set_wait_limit_cycles(long long cycles);
+
+/* Synchronises the device and reports whether a bounded device-side wait of a call that used `workspace`
+ * gave up since the last fk_moe_status on it: FK_OK, or FK_ERR_TIMEOUT with *code (may be NULL) = 1 grouped
+ * GEMV kernels, 2 single-token kernel, 3 tensor-core grouped GEMM.  The word is cleared, so the workspace
+ * can be used again.  No counterpart in the reference (see fk_set_wait_limit_cycles). */
+int fk_moe_status(void* workspace, size_t workspace_bytes, int* code);
 
 /* Byte offset inside the workspace of the FK_FLAG_TRACE record for these dims. */
 size_t fk_moe_trace_offset(const fk_moe_dims* dims);
@@ -252,8 +272,16 @@ int fk_ep_buffer_destroy(void* buffer);
  * block of experts); outputs as for fk_moe_layer.  The workspace must hold
  * fk_moe_workspace_bytes({world*tokens, hidden, experts/world, intermediate, top_k}). */
 int fk_moe_layer_ep(const fk_moe_call* c, const fk_ep_comm* comm, void* stream);
-/* Synchronises the device and returns the buffer's error word in *error (0: no wait ever gave up). */
+/* Synchronises the device and returns the buffer's error word in *error (0: no wait ever gave up; 1: the wait
+ * for the ranks' dispatched rows, 2: the wait for their partial rows; the first one that gave up is kept). */
 int fk_ep_status(const fk_ep_comm* comm, int* error);
+/* Clears an OWN exchange buffer's header (arrival epochs, tickets, error word) after a failed call, once every
+ * rank has stopped using the buffers; all ranks reset theirs before the next fk_moe_layer_ep. Synchronises. */
+int fk_ep_buffer_reset(void* buffer);
+/* fk_moe_layer_ep with CUDA events between its stages (profiling aid, waits for the call): router, dispatch +
+ * wait, permutation, [row gather, tensor-core path only], gate_up, down, combine + wait, reduce.
+ * stage_ms has room for 11 values. */
+int fk_moe_layer_ep_timed(const fk_moe_call* c, const fk_ep_comm* comm, void* stream, float* stage_ms, int* stages);
 
 #ifdef __cplusplus
 }
