@@ -9,7 +9,9 @@ intermediate 512, gated shared expert); weights ~ N(0, 0.02) bf16, hidden ~ N(0,
 logit bias ~ N(0, 0.5).  Consecutive steps use different layers' weights (a rotation of several
 resident copies, as a decoder stack does), so no step finds its weights in L2.
 
-value      tokens/s with the step's input already in HBM (CUDA events around the K steps).
+value      tokens/s with the step's input already in HBM: CUDA events around blocks of K steps, repeated until the
+           timed region is at least 0.2 s, median block.  The steps are replayed as CUDA graphs of `--layers`
+           consecutive layer calls (one per resident weight copy), the way a decoder stack issues them.
 e2e        the same through the host-buffer entry point: every step copies its hidden batch from
            pinned host memory, runs the layer and copies output, ids and weights back, then waits.
 roofline   the dominant kernel (gate_up GEMV + SwiGLU): its algorithmic bytes / its mean duration
@@ -45,7 +47,8 @@ def parse_args():
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="own", choices=["own", "reference"])
-    ap.add_argument("--batch", type=int, default=32, help="decode tokens per GPU per step")
+    ap.add_argument("--batch", type=int, default=None,
+                    help="decode tokens per GPU per step (default: 32 on one GPU, 256 per GPU expert parallel)")
     ap.add_argument("--layers", type=int, default=6, help="resident weight copies rotated between steps")
     ap.add_argument("--no-sweep", action="store_true", help="skip the per-batch sweep (1..256 tokens)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
@@ -193,14 +196,14 @@ def run_reference(args):
     from fastkernels_b200.spec import MoESpec
     from fastkernels_b200.workloads import make_hidden
     spec = MoESpec()
-    batch = args.batch
+    batch = args.batch or (32 if args.gpus == 1 else 256)
     sample = cpu_sample_tokens(batch)
     w = cpu_weights(0, 0.5)
     from oracle import moe_oracle as O
     threads = os.cpu_count() or 1
     torch.set_num_threads(threads)
-    steps = max(1, min(args.steps, 12))
-    warm = max(1, min(args.warmup, 2))
+    steps = max(1, args.steps)
+    warm = max(0, args.warmup)
     hs = [make_hidden(1000 + i, sample, spec, dtype=torch.bfloat16) for i in range(4)]
     for i in range(warm):
         O.moe_update_token_loop(hs[i % 4], *w.tuple(), top_k=8, router_bias=w.router_bias)
@@ -226,12 +229,13 @@ def run_reference(args):
 def workload_config(batch: int, gpus: int, layers: int) -> dict:
     which = "configs[1]" if batch <= 32 else "configs[2]"
     if gpus > 1:
-        which = "configs[3]-style expert parallel"
+        which = "configs[3]: expert parallel, 256 tokens per GPU" if batch == 256 else "expert parallel as configs[3], other batch"
     return {"workload": f"Qwen3.6 MoE layer decode, bf16, {batch} tokens per GPU ({which})", "hidden": 2048,
             "experts": 256, "top_k": 8, "intermediate": 512, "tokens_per_gpu": batch, "global_tokens": batch * gpus,
             "router_bias_std": 0.5, "parallelism": "single GPU" if gpus == 1 else f"ep{gpus}",
             "l2": f"weights rotate over {layers} resident layer copies per GPU; a step's weights were last touched "
-                  f"{layers} steps earlier, more than L2 apart"}
+                  f"{layers} steps earlier, more than L2 apart",
+            "replay": f"steps are replayed as CUDA graphs of {layers} consecutive layer calls (one per weight copy)"}
 
 
 # --------------------------------------------------------------------------------------------- own arm
@@ -240,22 +244,45 @@ def distinct_experts(ids) -> int:
     return int(torch.unique(ids).numel())
 
 
-def time_steps(plans, hiddens, steps: int, warmup: int):
-    """CUDA-event time of `steps` layer calls rotating over plans/hidden batches; returns ms per step."""
+MIN_TIMED_S = 0.2
+
+
+def time_steps(plans, hiddens, steps: int, warmup: int, chain=None):
+    """ms per step of `steps` layer calls rotating over the plans (= resident weight copies): CUDA events around a
+    block of exactly `steps` calls, blocks repeated until at least MIN_TIMED_S has been timed, median block.
+    Whole rotations are replayed as one CUDA graph of len(plans) calls, the remainder as single-call graphs."""
     import torch
+    from fastkernels_b200.plan import PlanChain
     n, m = len(plans), len(hiddens)
     for i, p in enumerate(plans):          # inputs are resident before the timed region starts
         p.hidden.copy_(hiddens[i % m])
-    for i in range(warmup):
-        plans[i % n].run()
+    chain = chain or PlanChain(plans)
+    full, rest = divmod(steps, n)
+    for p in plans[:rest]:
+        if p.graph is None:
+            p.capture()
+
+    def block():
+        for _ in range(full):
+            chain.replay()
+        for i in range(rest):
+            plans[i].run()
+
+    for _ in range(max(1, -(-warmup // n))):
+        chain.replay()
     torch.cuda.synchronize()
-    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    start.record()
-    for i in range(steps):
-        plans[i % n].run()
-    stop.record()
-    torch.cuda.synchronize()
-    return start.elapsed_time(stop) / steps
+    per_step, total = [], 0.0
+    while (total < MIN_TIMED_S or len(per_step) < 3) and len(per_step) < 2000:
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        start.record()
+        block()
+        stop.record()
+        torch.cuda.synchronize()
+        ms = start.elapsed_time(stop)
+        per_step.append(ms / steps)
+        total += ms * 1e-3
+    return statistics.median(per_step), len(per_step)
 
 
 def run_single(args):
@@ -273,23 +300,19 @@ def run_single(args):
     dev = torch.device("cuda", local)
     spec = MoESpec()
     peak, peak_src = measured_peak()
-    B, K, W, L = args.batch, args.steps, max(args.warmup, 3), args.layers
+    B, K, W, L = args.batch or 32, args.steps, max(args.warmup, 3), args.layers
 
     weights = [make_moe_weights(layer, spec, dtype=torch.bfloat16, device=dev, bias_std=0.5) for layer in range(L)]
     pool = 8
     hid_host = [make_hidden(1000 + i, B, spec, dtype=torch.bfloat16).pin_memory() for i in range(pool)]
     hid_dev = [h.to(dev) for h in hid_host]
 
-    def plans_for(tokens):
-        ps = [MoEDecodePlan(w, tokens, flags=args.flags) for w in weights]
-        for p in ps:
-            p.capture()
-        return ps
-
-    plans = plans_for(B)
+    plans = [MoEDecodePlan(w, B, flags=args.flags) for w in weights]
+    for p in plans:
+        p.capture()
     sampler = ClockSampler(local)
     sampler.start()
-    ms = time_steps(plans, hid_dev, K, W)
+    ms, blocks_timed = time_steps(plans, hid_dev, K, W)
     # the timed steps replay CUDA graphs, which bypass the library's launch counter: count the
     # kernels one direct call enqueues (the graph holds exactly these) and multiply by the steps
     c0 = lib.fk_launch_count()
@@ -310,7 +333,8 @@ def run_single(args):
         if i < L * pool:
             ucount.append(distinct_experts(p.topk_ids))
     stage_ms = [s / K for s in stage_sum]
-    stage_names = ["router", "permute", "gate_up", "down", "combine"][:len(stage_ms)]
+    stage_names = (["router", "permute", "gather", "gate_up", "down", "combine"] if len(stage_ms) == 6 else
+                   ["router", "permute", "gate_up", "down", "combine"][:len(stage_ms)])
     U = statistics.mean(ucount)
     layer_bytes = algorithmic_bytes(spec, B, 0) + U * spec.expert_bytes_bf16
     H, I = spec.hidden_size, spec.expert_intermediate_size
@@ -325,20 +349,24 @@ def run_single(args):
         # the step is this one kernel: its duration is the graph-replayed step (the stage events add their own gap)
         dom_kernel, dom_bytes, traffic_ratio = ("decode1_kernel (whole layer, one token, one launch)", layer_bytes,
                                                 NCU_TRAFFIC_PER_BYTE["decode1"])
+        traffic_file = "profiles/decode1_fused_b1.md"
         dom_ms = ms
     elif B <= 96:
         dom_kernel, dom_bytes, traffic_ratio = ("stream_gemv_kernel<8,true,false> (gate_up GEMV + SwiGLU, "
                                                 "TMA ring, mma.sync consumers)"), gate_up_bytes, NCU_TRAFFIC_PER_BYTE["stream_gate_up"]
+        traffic_file = "profiles/stream_gemv_b32.md"
     else:
         dom_kernel, dom_bytes, traffic_ratio = ("tc_grouped_kernel<true> (tcgen05 grouped gate_up GEMM + SwiGLU)",
                                                 gate_up_bytes, NCU_TRAFFIC_PER_BYTE["tc_gate_up"])
+        traffic_file = "profiles/tc_grouped_gemm_b256.md"
     achieved = dom_bytes / (dom_ms * 1e-3) / 1e9
     roofline = {"bound": "hbm", "kernel": dom_kernel, "achieved": achieved,
                 "peak": peak, "peak_source": peak_src, "unit": "GB/s", "frac": achieved / peak,
                 "algorithmic_bytes_per_launch": dom_bytes, "ms_per_launch": dom_ms,
                 "traffic": None if traffic_ratio is None else traffic_ratio * dom_bytes,
                 "traffic_source": None if traffic_ratio is None else
-                f"ncu dram__bytes_read.sum + dram__bytes_write.sum = {traffic_ratio:.3f} x algorithmic bytes (profiles/)",
+                f"not a live counter: algorithmic bytes x {traffic_ratio:.3f}, the DRAM read + write bytes per algorithmic "
+                f"byte of this kernel in the ncu capture summarised in {traffic_file}",
                 "stages_ms": dict(zip(stage_names, stage_ms)),
                 "layer": {"algorithmic_bytes": layer_bytes, "achieved": layer_bytes / (ms * 1e-3) / 1e9,
                           "frac": layer_bytes / (ms * 1e-3) / 1e9 / peak, "distinct_experts": U}}
@@ -367,12 +395,15 @@ def run_single(args):
     e2e = {"value": B / (max(e2e_ms, wall_ms) * 1e-3), "unit": UNIT, "ms_per_step": max(e2e_ms, wall_ms),
            "h2d_bytes_per_step": B * H * 2, "d2h_bytes_per_step": B * H * 4 + B * 8 * 12}
 
-    sweep = []
+    sweep, roofline_b1 = [], None
     if not args.no_sweep:
-        for b in (1, 4, 16, 32, 64, 128, 256):
-            ps = plans if b == B else plans_for(b)
+        import dataclasses
+        from fastkernels_b200.workloads import HOT_EXPERT_IDS
+
+        def sweep_entry(b, ws, variant):
+            ps = plans if (b == B and variant == "bias") else [MoEDecodePlan(w, b, flags=args.flags) for w in ws]
             hs = [make_hidden(2000 + i, b, spec, dtype=torch.bfloat16, device=dev) for i in range(pool)]
-            t = time_steps(ps, hs, max(20, K // 2), W)
+            t, _ = time_steps(ps, hs, max(20, K // 2), W)
             us = []
             for i in range(min(L, 2)):
                 ps[i].run(hs[i])
@@ -380,11 +411,28 @@ def run_single(args):
                 us.append(distinct_experts(ps[i].topk_ids))
             u = statistics.mean(us)
             by = algorithmic_bytes(spec, b, 0) + u * spec.expert_bytes_bf16
-            sweep.append({"batch": b, "us_per_step": t * 1e3, "tokens_per_s": b / (t * 1e-3), "distinct_experts": u,
-                          "algorithmic_bytes": by, "achieved_gbs": by / (t * 1e-3) / 1e9,
-                          "frac_of_hbm_peak": by / (t * 1e-3) / 1e9 / peak})
-            if b != B:
-                del ps
+            return {"batch": b, "routing": variant, "us_per_step": t * 1e3, "tokens_per_s": b / (t * 1e-3),
+                    "distinct_experts": u, "algorithmic_bytes": by, "achieved_gbs": by / (t * 1e-3) / 1e9,
+                    "frac_of_hbm_peak": by / (t * 1e-3) / 1e9 / peak}
+
+        for b in (1, 4, 16, 32, 64, 128, 256):
+            sweep.append(sweep_entry(b, weights, "bias"))
+        # hot-expert variant: +3.0 on eight fixed expert logits, so that about half of all routes hit them
+        hot = []
+        for w in weights:
+            bias = torch.zeros(spec.num_experts, dtype=torch.float32, device=dev)
+            bias[list(HOT_EXPERT_IDS)] += 3.0
+            hot.append(dataclasses.replace(w, router_bias=bias))
+        for b in (64, 128, 256):
+            sweep.append(sweep_entry(b, hot, "hot"))
+        one = sweep[0]
+        roofline_b1 = {"bound": "hbm", "kernel": "decode1_kernel (whole layer, one token, one launch)",
+                       "achieved": one["achieved_gbs"], "peak": peak, "peak_source": peak_src, "unit": "GB/s",
+                       "frac": one["frac_of_hbm_peak"], "algorithmic_bytes_per_launch": one["algorithmic_bytes"],
+                       "ms_per_launch": one["us_per_step"] * 1e-3,
+                       "traffic": NCU_TRAFFIC_PER_BYTE["decode1"] * one["algorithmic_bytes"],
+                       "traffic_source": "not a live counter: algorithmic bytes x the DRAM bytes per algorithmic byte of the "
+                                         "ncu capture summarised in profiles/decode1_fused_b1.md"}
 
     cpu = None
     if not args.no_cpu:
@@ -428,9 +476,9 @@ def run_single(args):
     line = {
         "metric": METRIC, "value": B / (ms * 1e-3), "unit": UNIT, "n_gpus": 1, "steps": K, "warmup": W,
         "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
-        "data": "synthetic", "config": workload_config(B, 1, L), "roofline": roofline, "cpu_baseline": cpu,
-        "e2e": e2e, "gpu_launches": int(launches), "launches_per_step": int(per_call), "clocks": clocks,
-        "sweep": sweep,
+        "data": "synthetic", "config": workload_config(B, 1, L), "roofline": roofline, "roofline_b1": roofline_b1,
+        "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": int(launches) * blocks_timed, "launches_per_step": int(per_call),
+        "timed_blocks": blocks_timed, "clocks": clocks, "sweep": sweep,
     }
     if stack is not None:
         line["stack"] = stack

@@ -352,11 +352,9 @@ static int moe_layer_impl(const fk_moe_call* c, void* stream, const LayerExtras&
         dp.out = c->out; dp.layer_hidden = c->layer_hidden;
         dp.ids_mirror = x.ids_mirror; dp.weights_mirror = x.weights_mirror;
         dp.resid_in = x.resid_in; dp.update_in = x.update_in; dp.resid_out = x.resid_out; dp.resid_eps = x.resid_eps;
-        dp.act_hi = at<__nv_bfloat16>(c->workspace, w.act);
-        dp.act_lo = at<__nv_bfloat16>(c->workspace, w.act) + (size_t)(c->dims.top_k + 1) * c->dims.intermediate;
-        dp.sgate = at<float>(c->workspace, w.shared_gate);
         dp.bar = at<unsigned>(c->workspace, w.counters);
         dp.tagged = at<unsigned long long>(c->workspace, w.tagged);
+        dp.actw = dp.tagged + FK_MAX_EXPERTS;
         dp.wait_cycles = wait_limit_cycles();
         dp.error_word = at<int>(c->workspace, w.meta) + 2;
         // the trace record is 256 bytes per block at the start of the y region: dropped when it does not fit there

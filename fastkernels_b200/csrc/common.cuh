@@ -21,7 +21,8 @@ struct Workspace {
     size_t tickets;      // u32 [kMaxTokenTiles]   router "last block" tickets (self-resetting)
     size_t counters;     // u32 [64]               misc. counters / barrier words (self-resetting)
     size_t meta;         // i32 [16]               [0]=U distinct experts hit, [1]=GEMV pass count, [2]=error word
-    size_t tagged;       // u64 [FK_MAX_EXPERTS]   single-token kernel: (launch tag << 32 | logit bits) per expert
+    size_t tagged;       // u64 [FK_MAX_EXPERTS + (FK_MAX_TOP_K + 1) * FK_MAX_INTERMEDIATE + 8]   single-token kernel:
+                         //     (launch tag << 32 | payload) words: the logits, then the SwiGLU activations, then the gate
     size_t ids32;        // i32 [R]
     size_t counts;       // i32 [E]
     size_t offsets;      // i32 [E+1]
@@ -57,7 +58,7 @@ __host__ inline Workspace workspace_layout(const fk_moe_dims& d) {
     w.tickets = take(sizeof(uint32_t) * kMaxTokenTiles);
     w.counters = take(sizeof(uint32_t) * 64);
     w.meta = take(sizeof(int32_t) * 16);
-    w.tagged = take(sizeof(uint64_t) * FK_MAX_EXPERTS);
+    w.tagged = take(sizeof(uint64_t) * (FK_MAX_EXPERTS + (FK_MAX_TOP_K + 1) * FK_MAX_INTERMEDIATE + 8));
     w.ids32 = take(sizeof(int32_t) * R);
     w.counts = take(sizeof(int32_t) * E);
     w.offsets = take(sizeof(int32_t) * (E + 1));

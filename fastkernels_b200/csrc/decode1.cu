@@ -15,8 +15,9 @@
 //   B       the selected experts' gate and up tiles stream through the 16-stage ring; the down tiles follow in
 //           the same queue as ring slots free up (their addresses depend on the ids only), so HBM stays busy
 //           across the second grid-wide dependence.
-//   sync    one counter barrier (bounded spin): every block has published its SwiGLU activations; each block
-//           stages all of them in shared memory with two bulk copies.
+//   sync    the SwiGLU activations travel like the logits: one 64-bit word each (tag << 32 | bf16 head << 16 |
+//           bf16 remainder), and every warp polls just the words of its own K-slice.  (A counter barrier cost
+//           3 us here: a fence under load, the counter's round trip, then an 18 KB copy of all activations.)
 //   C       down tiles of the block's 16 output rows, summed in slot order with the routing weights, plus the
 //           gated shared expert (and the residual).
 //
@@ -86,7 +87,6 @@ struct D1Smem {
     uint64_t rrfull;                              // the router rows have landed
     uint64_t sdfull;                              // sdown has landed
     uint64_t rdone;                               // every warp has written its router K-slice sums
-    uint64_t staged_b;                            // the activations of all blocks are in shared memory
     uint64_t ids_ready;                           // ids / wnorm written by the select warp
     float wnorm[FK_MAX_TOP_K];                    // renormalised routing weights
     int ids[FK_MAX_TOP_K];
@@ -138,11 +138,6 @@ __device__ __forceinline__ unsigned long long global_ns() {
 // words 8 and 9 hold the SM cycle counter at start and exit); the slots are listed in include/fkmoe.h
 #define D1_TRACE(slot) do { if (p.trace) p.trace[(size_t)blockIdx.x * 32 + (slot)] = global_ns(); } while (0)
 
-__device__ __forceinline__ unsigned ld_acquire_u32(const unsigned* p) {
-    unsigned v;
-    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-    return v;
-}
 __device__ __forceinline__ unsigned ld_relaxed_u32(const unsigned* p) {
     unsigned v;
     asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
@@ -152,21 +147,6 @@ __device__ __forceinline__ unsigned long long ld_relaxed_u64(const unsigned long
     unsigned long long v;
     asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
     return v;
-}
-
-// Orders this thread's earlier generic-proxy accesses (and what it has acquired from other threads) before its
-// later bulk copies, which read and write memory through the async proxy.
-__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async;" ::: "memory"); }
-
-// Bounded spin until the counter *word has reached target (a count that only grows and may wrap); false on time-out.
-__device__ __forceinline__ bool spin_until(const unsigned* word, unsigned target, long long wait_cycles, volatile int* abort_flag) {
-    if ((int)(ld_acquire_u32(word) - target) >= 0) return true;
-    const long long limit = *abort_flag ? min(wait_cycles, kWaitCyclesAfterAbort) : wait_cycles;
-    const long long t0 = clock64();
-    while ((int)(ld_acquire_u32(word) - target) < 0) {
-        if (clock64() - t0 > limit) { *abort_flag = 1; return false; }
-    }
-    return true;
 }
 
 // "The mbarriers are initialised": the producer warp arrives on named barrier 2 without waiting, every other warp
@@ -209,16 +189,20 @@ __device__ __forceinline__ void d1_release(uint64_t* bar, float dep) {
 // column 0 of B: four k-steps of ldmatrix.x4 + MMA.  bfrag[kk] holds {b0, b1} of k-step kk (zero outside lanes 0..3).
 // ldmatrix row address of a lane: matrices 0..3 = (rows 0-7, k 0-7), (rows 8-15, k 0-7), (rows 0-7, k 8-15),
 // (rows 8-15, k 8-15); the 16-byte chunk c of row r sits at chunk c ^ (r & 7).
-__device__ __forceinline__ void box_mma(float (&c)[4], uint32_t box_addr, const uint32_t (*bfrag)[2], int lane) {
+__device__ __forceinline__ void box_load(uint32_t (&a)[4][4], uint32_t box_addr, int lane) {
     const int row = (lane & 7) + ((lane >> 3) & 1) * 8;
     const uint32_t rbase = box_addr + row * 128;
     const int sel = lane >> 4, sw = row & 7;
 #pragma unroll
-    for (int kk = 0; kk < 4; ++kk) {
-        uint32_t a[4];
-        d1_ldmatrix_x4(a, rbase + (((2 * kk + sel) ^ sw) << 4));
-        d1_mma(c, a, bfrag[kk][0], bfrag[kk][1]);
-    }
+    for (int kk = 0; kk < 4; ++kk) d1_ldmatrix_x4(a[kk], rbase + (((2 * kk + sel) ^ sw) << 4));
+}
+// The shared-memory instructions are volatile asm statements and keep their program order, so the loads of a box are
+// written out before its MMAs: a load that waits for the MMA before it made every k-step cost a full load latency.
+__device__ __forceinline__ void box_mma(float (&c)[4], uint32_t box_addr, const uint32_t (*bfrag)[2], int lane) {
+    uint32_t a[4][4];
+    box_load(a, box_addr, lane);
+#pragma unroll
+    for (int kk = 0; kk < 4; ++kk) d1_mma(c, a[kk], bfrag[kk][0], bfrag[kk][1]);
 }
 
 // Select warp: wait until every expert's logit of this launch has been published, then softmax + top-k on the
@@ -246,9 +230,12 @@ __device__ __forceinline__ void poll_and_select(const DecodeParams& p, D1Smem& s
         }
         if (__all_sync(kFull, ok)) break;
         if (clock64() - t0 > p.wait_cycles) { complete = false; break; }
-        __nanosleep(64);       // 148 warps polling without a pause keep the publishing stores waiting for microseconds
+        __nanosleep(32);       // 148 warps polling without a pause keep the publishing stores waiting for microseconds
     }
     complete = __all_sync(kFull, complete);
+    // every block publishes a logit after it has read the launch tag, so all of them have read it by now: block 0
+    // advances it for the next launch
+    if (blockIdx.x == 0 && lane == 0) p.bar[3] = tag;
     if (lane == 0) D1_TRACE(18);
     if (!complete && lane == 0) s.abort_flag = 1;
     int my_i;
@@ -281,8 +268,6 @@ decode1_kernel(const __grid_constant__ CUtensorMap gu_map, const __grid_constant
     const D1Plan pl = make_plan(p, blk, G);
     const bool has_shared = p.shared_gate_up != nullptr;
     const int shared_slot = p.top_k;                       // index of the shared expert in the activation arrays
-    __nv_bfloat16* act_hi_g = reinterpret_cast<__nv_bfloat16*>(p.act_hi);
-    __nv_bfloat16* act_lo_g = reinterpret_cast<__nv_bfloat16*>(p.act_lo);
 
     if (warp == kD1Consumers) {
         // ------------------------------------------------------------------ producer warp
@@ -295,7 +280,6 @@ decode1_kernel(const __grid_constant__ CUtensorMap gu_map, const __grid_constant
             mbar_init(&s.rrfull, 1);
             mbar_init(&s.sdfull, 1);
             mbar_init(&s.rdone, kD1Consumers);
-            mbar_init(&s.staged_b, 1);
             mbar_init(&s.ids_ready, 1);
             s.abort_flag = 0;
             prefetch_tensormap(&gu_map);
@@ -419,6 +403,9 @@ decode1_kernel(const __grid_constant__ CUtensorMap gu_map, const __grid_constant
         // ------------------------------------------------------------------ consumer warps
         const int cthreads = kD1Consumers * 32;
         const int gid = lane >> 2, tig = lane & 3;
+        // the router bias of this block's rows is a constant: fetched before the token arrives
+        float bias_v = 0.f;
+        if (warp == 0 && p.router_bias && lane < pl.nrr && lane != pl.gate_row) bias_v = __ldg(p.router_bias + blk + lane * G);
         barriers_ready_wait();
         pdl_wait();
         mbar_wait_spin(&s.xready, 0, kWaitCycles, &s.abort_flag);
@@ -517,11 +504,12 @@ decode1_kernel(const __grid_constant__ CUtensorMap gu_map, const __grid_constant
 #pragma unroll
                     for (int w = 0; w < kD1Consumers; ++w) { acc += s.rpart[lane][w]; sq += s.rpart[kD1MaxRouterRows][w]; }
                     if (lane == pl.gate_row) {
-                        *p.sgate = sigmoidf_(acc);
+                        atomicExch(p.actw + (size_t)(FK_MAX_TOP_K + 1) * I,
+                                   ((unsigned long long)s.tag << 32) | (unsigned long long)__float_as_uint(sigmoidf_(acc)));
                     } else {
                         const int e = blk + lane * G;
                         float logit = acc * rsqrtf(sq / (float)H + p.eps);
-                        if (p.router_bias) logit += p.router_bias[e];
+                        if (p.router_bias) logit += bias_v;
                         // an atomic is performed at L2 at once; a plain store was seen by the pollers a microsecond later
                         atomicExch(p.tagged + e, ((unsigned long long)s.tag << 32) | (unsigned long long)__float_as_uint(logit));
                         p.logits[e] = logit;
@@ -546,21 +534,31 @@ decode1_kernel(const __grid_constant__ CUtensorMap gu_map, const __grid_constant
             mbar_wait(&s.full[slot], (it / kD1Stages) & 1u, &s.abort_flag);
             if (tid == 0 && n == 0) D1_TRACE(11);
             const uint32_t base = smem_u32(s.stage[slot]);
-            float c[4][4];
+            float c[8][4];                                 // two accumulators per box: dependent MMAs wait for each other
 #pragma unroll
-            for (int q = 0; q < 4; ++q) { c[q][0] = c[q][1] = c[q][2] = c[q][3] = 0.f; }
+            for (int q = 0; q < 8; ++q) { c[q][0] = c[q][1] = c[q][2] = c[q][3] = 0.f; }
+            {
+                uint32_t a[4][4][4];
 #pragma unroll
-            for (int sl = 0; sl < 4; ++sl) box_mma(c[sl], base + sl * 2048, &bx[sl * 4], lane);
-            const float v0 = (c[0][0] + c[1][0]) + (c[2][0] + c[3][0]);      // tile row gid     (lanes with tig == 0)
-            const float v2 = (c[0][2] + c[1][2]) + (c[2][2] + c[3][2]);      // tile row gid + 8
+                for (int sl = 0; sl < 4; ++sl) box_load(a[sl], base + sl * 2048, lane);
+#pragma unroll
+                for (int kk = 0; kk < 4; ++kk) {
+#pragma unroll
+                    for (int sl = 0; sl < 4; ++sl) d1_mma(c[2 * sl + (kk & 1)], a[sl][kk], bx[sl * 4 + kk][0], bx[sl * 4 + kk][1]);
+                }
+            }
+            const float v0 = ((c[0][0] + c[1][0]) + (c[2][0] + c[3][0])) + ((c[4][0] + c[5][0]) + (c[6][0] + c[7][0]));   // tile row gid (lanes with tig == 0)
+            const float v2 = ((c[0][2] + c[1][2]) + (c[2][2] + c[3][2])) + ((c[4][2] + c[5][2]) + (c[6][2] + c[7][2]));   // tile row gid + 8
             if (tig == 0) {
                 s.bpart[n][warp][gid] = v0;
                 s.bpart[n][warp][gid + 8] = v2;
             }
             if (lane == 0) d1_release(&s.empty[slot], v0 + v2);
         }
-        // the K-slices of every tile meet; SwiGLU; the activations are published as bf16 head + remainder
+        // the K-slices of every tile meet; SwiGLU; each activation is published as one tagged word (an atomic is
+        // performed at L2 at once and nobody waits for it)
         named_bar_sync(1, cthreads);
+        const unsigned tag = s.tag;
         if (tid < pl.atoms * kD1Tile) {
             const int j = tid >> 4, r = tid & 15;
             float gsum = 0.f, usum = 0.f;
@@ -572,66 +570,109 @@ decode1_kernel(const __grid_constant__ CUtensorMap gu_map, const __grid_constant
             if (g < pl.shared_atoms) idx = shared_slot * I + g * kD1Tile + r;
             else idx = (g - pl.shared_atoms) * kD1Tile + r;                   // slot * I + pair
             const __nv_bfloat16 hi = __float2bfloat16_rn(act);
-            act_hi_g[idx] = hi;
-            act_lo_g[idx] = __float2bfloat16_rn(act - __bfloat162float(hi));
+            const __nv_bfloat16 lo = __float2bfloat16_rn(act - __bfloat162float(hi));
+            const unsigned payload = ((unsigned)__bfloat16_as_ushort(hi) << 16) | (unsigned)__bfloat16_as_ushort(lo);
+            atomicExch(p.actw + idx, ((unsigned long long)tag << 32) | (unsigned long long)payload);
         }
-        named_bar_sync(1, cthreads);
-        if (tid == 0) {
-            // the block's stores happen before this thread's fence (the barrier above), the fence makes them visible
-            // to whoever sees the arrival
-            D1_TRACE(5);
-            __threadfence();
-            atomicAdd(p.bar + 1, 1u);
-        }
+        if (tid == 0) D1_TRACE(5);
 
         if (pl.tile >= 0) {
             // ---- phase C: the block's 16 output rows
-            if (tid == 0) {
-                // the counter is never reset: launch number t (== its tag, both count from 1) ends at t * G arrivals
-                spin_until(p.bar + 1, s.tag * (unsigned)G, p.wait_cycles, &s.abort_flag);
-                // every block has read the tag by now (it arrived): block 0 advances it for the next launch
-                if (blk == 0) p.bar[3] = s.tag;
-                D1_TRACE(6);
-                fence_proxy_async();
-                const uint32_t ab = (uint32_t)((p.top_k + (has_shared ? 1 : 0)) * I * 2);
-                mbar_expect_tx(&s.staged_b, 2u * ab);
-                bulk_load(s.act_hi, act_hi_g, ab, &s.staged_b);
-                bulk_load(s.act_lo, act_lo_g, ab, &s.staged_b);
-            }
-            __syncwarp();
             // what the output rows need from global memory is fetched while the activations are on their way
-            float gate_v = 1.f, resid_v = 0.f;
-            if (tid < kD1Tile * kD1Consumers) {
-                if (has_shared && p.shared_gate) gate_v = __ldcg(p.sgate);
-                if (p.layer_hidden && !p.resid_in) resid_v = load_any(p.hidden, p.hidden_dtype, (size_t)(pl.tile * kD1Tile + (tid >> 3)));
+            float resid_v = 0.f;
+            if (tid < kD1Tile * kD1Consumers && p.layer_hidden && !p.resid_in)
+                resid_v = load_any(p.hidden, p.hidden_dtype, (size_t)(pl.tile * kD1Tile + (tid >> 3)));
+            // This warp's K-slice of every slot's activations (64 words per slot, two per lane), polled until all
+            // carry this launch's tag; lane 0 also takes the shared-expert gate.
+            const int nslots = p.top_k + (has_shared ? 1 : 0);
+            const bool want_gate = has_shared && p.shared_gate != nullptr;
+            float gate_v = 1.f;
+            {
+                unsigned long long w[2 * (FK_MAX_TOP_K + 1)];
+                unsigned long long gw = 0ull;
+                const unsigned long long* src = p.actw + warp * 64 + lane;
+                const long long t0 = clock64();
+                for (;;) {
+#pragma unroll
+                    for (int sl = 0; sl <= FK_MAX_TOP_K; ++sl) {
+                        w[2 * sl] = sl < nslots ? ld_relaxed_u64(src + (size_t)sl * I) : 0ull;
+                        w[2 * sl + 1] = sl < nslots ? ld_relaxed_u64(src + (size_t)sl * I + 32) : 0ull;
+                    }
+                    if (want_gate && lane == 0) gw = ld_relaxed_u64(p.actw + (size_t)(FK_MAX_TOP_K + 1) * I);
+                    bool ok = !(want_gate && lane == 0) || (unsigned)(gw >> 32) == tag;
+#pragma unroll
+                    for (int sl = 0; sl <= FK_MAX_TOP_K; ++sl)
+                        ok = ok & (sl >= nslots || ((unsigned)(w[2 * sl] >> 32) == tag && (unsigned)(w[2 * sl + 1] >> 32) == tag));
+                    if (__all_sync(kFull, ok)) break;
+                    if (clock64() - t0 > (s.abort_flag ? min(p.wait_cycles, kWaitCyclesAfterAbort) : p.wait_cycles)) { s.abort_flag = 1; break; }
+                    __nanosleep(64);
+                }
+#pragma unroll
+                for (int sl = 0; sl <= FK_MAX_TOP_K; ++sl) {
+                    if (sl < nslots) {
+#pragma unroll
+                        for (int h2 = 0; h2 < 2; ++h2) {
+                            const unsigned pay = (unsigned)w[2 * sl + h2];
+                            const size_t el = (size_t)sl * I + warp * 64 + lane + 32 * h2;
+                            reinterpret_cast<unsigned short*>(s.act_hi)[el] = (unsigned short)(pay >> 16);
+                            reinterpret_cast<unsigned short*>(s.act_lo)[el] = (unsigned short)(pay & 0xffffu);
+                        }
+                    }
+                }
+                gate_v = want_gate ? __uint_as_float((unsigned)__shfl_sync(kFull, (unsigned)gw, 0)) : 1.f;
+                __syncwarp();                              // the warp reads back only its own K-slice
             }
-            mbar_wait(&s.staged_b, 0, &s.abort_flag);
             if (tid == 0) D1_TRACE(12);
-            // one [16 x 64] down box of slot `sl` against that slot's activations (head and remainder): K-slice sums
-            auto down_box = [&](int sl, uint32_t box_addr) -> float {
-                uint32_t bh[4][2], bl[4][2];
-                const size_t off = ((size_t)sl * I + warp * 64 + 2 * tig) * 2;
+            // [16 x 64] down boxes of up to two slots against those slots' activations (head and remainder): K-slice
+            // sums.  All loads of both boxes are written out first, then four independent MMA chains.
+            auto down_boxes = [&](int sl0, uint32_t addr0, int sl1, uint32_t addr1) -> float {
+                const bool two = sl1 >= 0;
+                uint32_t bh[2][4][2], bl[2][4][2], a[2][4][4];
+#pragma unroll
+                for (int b = 0; b < 2; ++b) {
+                    const size_t off = ((size_t)(b == 0 ? sl0 : (two ? sl1 : sl0)) * I + warp * 64 + 2 * tig) * 2;
+#pragma unroll
+                    for (int kk = 0; kk < 4; ++kk) {
+                        bh[b][kk][0] = gid == 0 ? d1_lds32(s.act_hi + off + kk * 32) : 0u;
+                        bh[b][kk][1] = gid == 0 ? d1_lds32(s.act_hi + off + kk * 32 + 16) : 0u;
+                        bl[b][kk][0] = gid == 0 ? d1_lds32(s.act_lo + off + kk * 32) : 0u;
+                        bl[b][kk][1] = gid == 0 ? d1_lds32(s.act_lo + off + kk * 32 + 16) : 0u;
+                    }
+                }
+                box_load(a[0], addr0, lane);
+                box_load(a[1], two ? addr1 : addr0, lane);
+                // eight independent MMAs per box (a dependent MMA waits ~100 cycles for the one before it)
+                float c[2][8][4];
+#pragma unroll
+                for (int b = 0; b < 2; ++b) {
+#pragma unroll
+                    for (int q = 0; q < 8; ++q) c[b][q][0] = c[b][q][1] = c[b][q][2] = c[b][q][3] = 0.f;
+                }
 #pragma unroll
                 for (int kk = 0; kk < 4; ++kk) {
-                    bh[kk][0] = gid == 0 ? d1_lds32(s.act_hi + off + kk * 32) : 0u;
-                    bh[kk][1] = gid == 0 ? d1_lds32(s.act_hi + off + kk * 32 + 16) : 0u;
-                    bl[kk][0] = gid == 0 ? d1_lds32(s.act_lo + off + kk * 32) : 0u;
-                    bl[kk][1] = gid == 0 ? d1_lds32(s.act_lo + off + kk * 32 + 16) : 0u;
+#pragma unroll
+                    for (int b = 0; b < 2; ++b) {
+                        d1_mma(c[b][kk], a[b][kk], bh[b][kk][0], bh[b][kk][1]);
+                        d1_mma(c[b][4 + kk], a[b][kk], bl[b][kk][0], bl[b][kk][1]);
+                    }
                 }
-                float ch[4] = {0.f, 0.f, 0.f, 0.f}, cl[4] = {0.f, 0.f, 0.f, 0.f};
-                box_mma(ch, box_addr, bh, lane);
-                box_mma(cl, box_addr, bl, lane);
-                const float v0 = ch[0] + cl[0], v2 = ch[2] + cl[2];
-                if (tig == 0) {
-                    s.cpart[sl][warp][gid] = v0;
-                    s.cpart[sl][warp][gid + 8] = v2;
+                float dep = 0.f;
+#pragma unroll
+                for (int b = 0; b < 2; ++b) {
+                    // head sums first, then the remainders: a fixed order
+                    const float v0 = ((c[b][0][0] + c[b][1][0]) + (c[b][2][0] + c[b][3][0])) + ((c[b][4][0] + c[b][5][0]) + (c[b][6][0] + c[b][7][0]));
+                    const float v2 = ((c[b][0][2] + c[b][1][2]) + (c[b][2][2] + c[b][3][2])) + ((c[b][4][2] + c[b][5][2]) + (c[b][6][2] + c[b][7][2]));
+                    const int sl = b == 0 ? sl0 : sl1;
+                    if (tig == 0 && (b == 0 || two)) {
+                        s.cpart[sl][warp][gid] = v0;
+                        s.cpart[sl][warp][gid + 8] = v2;
+                    }
+                    dep += v0 + v2;
                 }
-                return v0 + v2;
+                return dep;
             };
-            if (has_shared) {
-                mbar_wait(&s.sdfull, 0, &s.abort_flag);
-                down_box(shared_slot, smem_u32(s.sdown[warp]));
-            }
+            if (has_shared) mbar_wait(&s.sdfull, 0, &s.abort_flag);
+            bool shared_pending = has_shared;
 #pragma unroll 1
             for (int cst = 0; cst < pl.nC; ++cst) {
                 const int it = (pl.nB + cst) * kD1Consumers + warp;
@@ -640,10 +681,12 @@ decode1_kernel(const __grid_constant__ CUtensorMap gu_map, const __grid_constant
                 const uint32_t base = smem_u32(s.stage[slot]);
                 const int nu = min(4, p.top_k - cst * 4);
                 float dep = 0.f;
-#pragma unroll 4
-                for (int u = 0; u < nu; ++u) dep += down_box(cst * 4 + u, base + u * 2048);
+#pragma unroll 1
+                for (int u = 0; u < nu; u += 2)
+                    dep += down_boxes(cst * 4 + u, base + u * 2048, u + 1 < nu ? cst * 4 + u + 1 : -1, base + (u + 1) * 2048);
                 if (lane == 0) d1_release(&s.empty[slot], dep);
             }
+            if (shared_pending) down_boxes(shared_slot, smem_u32(s.sdown[warp]), -1, 0u);
             named_bar_sync(1, cthreads);
             if (tid == 0) D1_TRACE(13);
             if (tid < kD1Tile * kD1Consumers) {
@@ -653,7 +696,7 @@ decode1_kernel(const __grid_constant__ CUtensorMap gu_map, const __grid_constant
                 mbar_wait(&s.ids_ready, 0, &s.abort_flag);
                 float acc = 0.f;
                 for (int sl = 0; sl < p.top_k; ++sl) acc = fmaf(s.wnorm[sl], s.cpart[sl][w][row], acc);
-                if (has_shared) acc = fmaf(gate_v, s.cpart[shared_slot][w][row], acc);
+                if (has_shared) acc = fmaf(gate_v, s.cpart[shared_slot][w][row], acc);      // gate_v is 1 without a gate
                 acc += __shfl_xor_sync(kFull, acc, 1);
                 acc += __shfl_xor_sync(kFull, acc, 2);
                 acc += __shfl_xor_sync(kFull, acc, 4);
@@ -709,7 +752,7 @@ bool decode1_supported(const DecodeParams& p, int weight_dtype) {
                      reinterpret_cast<uintptr_t>(p.router_weight) | reinterpret_cast<uintptr_t>(p.gate_up) |
                      reinterpret_cast<uintptr_t>(p.down) | reinterpret_cast<uintptr_t>(p.shared_gate_up) |
                      reinterpret_cast<uintptr_t>(p.shared_down) | reinterpret_cast<uintptr_t>(p.shared_gate) |
-                     reinterpret_cast<uintptr_t>(p.act_hi) | reinterpret_cast<uintptr_t>(p.act_lo);
+                     reinterpret_cast<uintptr_t>(p.tagged) | reinterpret_cast<uintptr_t>(p.actw);
     bits |= reinterpret_cast<uintptr_t>(p.resid_in) | reinterpret_cast<uintptr_t>(p.update_in) | reinterpret_cast<uintptr_t>(p.resid_out);
     if (bits & 15) return false;
     return decode1_resident();

@@ -135,11 +135,10 @@ struct DecodeParams {
     float* weights_mirror;
     float* out;                   // [H]
     float* layer_hidden;          // optional [H]
-    void* act_hi;                 // workspace bf16 [(k+1), I]: SwiGLU activations of the k slots and the shared expert, head
-    void* act_lo;                 // workspace bf16 [(k+1), I]: their remainders (activation = head + remainder to 2^-17)
-    float* sgate;                 // workspace [1]
-    unsigned* bar;                // workspace [4]: unused, arrive, depart (zero between launches), launch epoch
+    unsigned* bar;                // workspace [4]: word 3 is the launch epoch (the tag of the next launch minus one)
     unsigned long long* tagged;   // workspace [E]: (launch tag << 32 | logit bits), how the blocks exchange the logits
+    unsigned long long* actw;     // workspace [(k+1)*I + 1]: (tag << 32 | bf16 head << 16 | bf16 remainder) per SwiGLU
+                                  //   activation of the k slots and the shared expert; last word: the shared gate (fp32 bits)
     int* error_word;
     unsigned long long* trace;    // optional [blocks][16] nanosecond timestamps of the phase boundaries
     int H, E, I, top_k;

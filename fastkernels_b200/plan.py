@@ -21,6 +21,39 @@ from .moe import _DTYPES, _as_weight, _ptr
 from .spec import MoEWeights
 
 
+class PlanChain:
+    """Several prepared layer calls captured back to back in ONE CUDA graph, as a decoder stack replays them.
+
+    The kernels are launched with the programmatic-dependent-launch attribute, which survives capture as a
+    programmatic edge: the next call's kernels become resident while the previous call's last blocks drain and
+    load their constant weights meanwhile; they wait for the previous call to complete before they touch
+    anything it may have written.  A replay runs every plan once, in order; each plan reads its own
+    `hidden` buffer and writes its own outputs.
+    """
+
+    def __init__(self, plans):
+        self.plans = list(plans)
+        dev = self.plans[0].device
+        s = torch.cuda.Stream(device=dev)
+        s.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(s):
+            for p in self.plans:           # warm-up outside capture (function attributes, tensor maps, lazy loading)
+                p.launch()
+        torch.cuda.current_stream().wait_stream(s)
+        torch.cuda.synchronize(dev)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            for p in self.plans:
+                p.launch()
+        self.graph = g
+
+    def __len__(self):
+        return len(self.plans)
+
+    def replay(self) -> None:
+        self.graph.replay()
+
+
 class MoEDecodePlan:
     def __init__(self, weights: MoEWeights, tokens: int, *, hidden_dtype: torch.dtype = torch.bfloat16,
                  top_k: int = 8, eps: float = 1e-6, norm_offset: float = 1.0, residual: bool = False,

@@ -60,13 +60,14 @@ typedef struct fk_moe_dims {
 #define FK_FLAG_NO_FUSED_DECODE 8u /* T==1: run the staged kernels instead of the fused single-token kernel */
 #define FK_FLAG_REGISTER_GEMV 32u  /* grouped GEMV with direct global->register loads instead of the bulk-copy ring */
 #define FK_FLAG_TRACE 64u          /* T==1 fused kernel: write per-block phase timestamps at the start of the workspace's y
-                                      region, u64 [blocks][16] (fk_moe_trace_offset() gives the offset).  Nanoseconds of
-                                      the global timer in slots 0 entry, 1 constant copies issued, 2 token in shared
-                                      memory, 3 this block's logits published, 4 experts selected, 10 first expert
-                                      stage landed, 5 this block's activations published, 6 all blocks' published,
-                                      12 activations staged, 14 last copy issued, 13 down rows done, 15 output stored,
-                                      7 exit; 11 first stage landed; SM cycle counter in 8 (entry) and 9 (exit).
-                                      Ignored when the record (blocks * 128 bytes) does not fit the y region. */
+                                      region, u64 [blocks][32] (fk_moe_trace_offset() gives the offset).  Nanoseconds of
+                                      the global timer in slots 0 entry, 1 constant copies issued, 20 the kernel before
+                                      has completed, 2 token in shared memory, 3 this block's logits published, 18 all
+                                      logits seen, 19 experts selected, 4 producer has the ids, 11 first ring stage
+                                      landed, 5 this block's activations published, 12 the activations this block needs
+                                      are in shared memory, 14 last copy issued, 13 down tiles done, 15 output stored,
+                                      7 exit (0 where a block skips the step); SM cycle counter in 8 (entry) and 9 (exit).
+                                      Ignored when the record (blocks * 256 bytes) does not fit the y region. */
 #define FK_FLAG_SKIP_FOREIGN 16u   /* ids outside [expert_base, expert_base+E) are skipped instead of clamped */
 #define FK_FLAG_WIDE_PASSES 128u   /* tcgen05 path: 128 tokens per pass instead of 64 (experts that see dozens of tokens) */
 
