@@ -53,8 +53,9 @@ def parse_args():
     ap.add_argument("--no-sweep", action="store_true", help="skip the per-batch sweep (1..256 tokens)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--flags", type=int, default=0)
-    ap.add_argument("--stack-layers", type=int, default=0,
-                    help="also time a stack of this many layers (x <- x + MoE(RMSNorm(x)), one CUDA graph) at 1 and 64 tokens")
+    ap.add_argument("--stack-layers", type=int, default=None,
+                    help="also time a stack of this many layers (x <- x + MoE(RMSNorm(x)), one CUDA graph) at 1 and 64 tokens "
+                         "(default: 40 layers when run on 8 GPUs, none otherwise; 0 turns it off)")
     ap.add_argument("--ep-eager", action="store_true", help="expert-parallel leg: no CUDA-graph capture of the layer call")
     ap.add_argument("--ep-nccl", action="store_true",
                     help="expert-parallel leg: exchange with NCCL collectives instead of the peer-memory kernels")
@@ -492,6 +493,8 @@ NCU_TRAFFIC_PER_BYTE = {"stream_gate_up": 1.011, "tc_gate_up": 1.016, "decode1":
 
 def main():
     args = parse_args()
+    if args.stack_layers is None:
+        args.stack_layers = 40 if args.gpus == 8 else 0
     if args.impl == "reference":
         run_reference(args)
         return

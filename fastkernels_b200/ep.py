@@ -103,6 +103,8 @@ def ep_moe_layer(hidden: torch.Tensor, shard: EPShard, *, top_k: int = 8, eps: f
 
     Returns `(output [T,H] f32, logits [T,E] f32, topk_ids [T,k] i64, topk_weights [T,k] f32)`;
     `output` includes the residual when `residual=True`.
+    `router_fn` / `local_experts_fn` exist for the CPU (gloo) tests of the exchange logic only, which pass the
+    oracle's compute there; nothing in the product passes them, and without CUDA tensors the call raises.
     """
     if hidden.ndim != 2:
         raise ValueError("hidden must have shape [tokens, hidden_size]")
@@ -266,15 +268,18 @@ class PeerExchange:
         _lib.check(self.lib.fk_ep_status(C.byref(self.comm), C.byref(e)), "fk_ep_status")
         return e.value
 
-    def close(self) -> None:
-        """Collective: unmaps the peers' buffers and frees the own one once every rank has unmapped it."""
+    def close(self, collective: bool = True) -> None:
+        """Unmaps the peers' buffers and frees the own one once every rank has unmapped it (a barrier on the process
+        group).  `collective=False` skips that barrier: for a shutdown after a failure, when the caller has already
+        established on the host that no rank will touch the buffers again (or that a rank is gone)."""
         if self.own is None:
             return
         torch.cuda.synchronize()
         for ptr in self._opened:
             self.lib.fk_ep_buffer_close(ptr)
         self._opened = []
-        dist.barrier(group=self.group)
+        if collective:
+            dist.barrier(group=self.group)
         self.lib.fk_ep_buffer_destroy(self.own)
         self.own = None
 
@@ -341,6 +346,15 @@ class PeerEPLayer:
     def launch(self) -> None:
         _lib.check(self.lib.fk_moe_layer_ep(C.byref(self.call), C.byref(self.exchange.comm), torch.cuda.current_stream().cuda_stream),
                    "fk_moe_layer_ep")
+
+    def timed(self) -> list[float]:
+        """One eager call with CUDA events between its stages (collective: every rank makes it); waits; stage times in
+        ms: router, dispatch + wait, permutation, [row gather], gate_up, down, combine + wait, reduce."""
+        ms = (C.c_float * 12)()
+        n = C.c_int(0)
+        _lib.check(self.lib.fk_moe_layer_ep_timed(C.byref(self.call), C.byref(self.exchange.comm),
+                                                  torch.cuda.current_stream().cuda_stream, ms, C.byref(n)), "fk_moe_layer_ep_timed")
+        return [ms[i] for i in range(n.value)]
 
     def run(self, hidden: Optional[torch.Tensor] = None):
         """Returns `(out, logits, topk_ids, topk_weights)`; `out` includes the residual when asked for at construction."""

@@ -77,6 +77,32 @@ def make_moe_weights(seed: int, spec: MoESpec, *, dtype=torch.bfloat16, device="
                       shared_gate_up, shared_down, sgate, bias if use_bias else None)
 
 
+def make_expert_subset(seed: int, spec: MoESpec, expert_ids: Sequence[int], *, dtype=torch.bfloat16, device="cpu",
+                       scale: float = 0.02) -> dict:
+    """`{expert id: (gate_up [2I,H], down [H,I])}` with exactly the values `make_moe_weights(seed, ...)` gives those
+    experts: the whole layer's sequence is drawn again (same calls, same shapes, same order) and only the asked-for
+    experts are kept.  Lets a rank that holds a shard check a few tokens against the oracle without the full layer."""
+    g = _gen(seed, device)
+    H, E, I = spec.hidden_size, spec.num_experts, spec.expert_intermediate_size
+    keep = set(int(e) for e in expert_ids)
+
+    def randn(*shape):
+        return torch.randn(*shape, generator=g, device=device, dtype=torch.float32) * scale
+
+    randn(E, H)                                                                  # router
+    torch.randn(E, generator=g, device=device, dtype=torch.float32)              # router bias
+    gate_up, down = {}, {}
+    for e in range(E):
+        w = randn(2 * I, H)
+        if e in keep:
+            gate_up[e] = w.to(dtype)
+    for e in range(E):
+        w = randn(H, I)
+        if e in keep:
+            down[e] = w.to(dtype)
+    return {e: (gate_up[e], down[e]) for e in sorted(keep)}
+
+
 def algorithmic_bytes(spec: MoESpec, tokens: int, distinct_experts: int, *, weight_bytes: int = 2,
                       hidden_bytes: int = 2, shared_gate: bool = True) -> int:
     """Bytes one layer call must move: each touched expert once, shared expert, router, gate, norm,
