@@ -38,8 +38,7 @@ def build(verbose: bool = False, force: bool = False) -> Path:
     objdir = PKG / "build"
     objdir.mkdir(exist_ok=True)
     nvcc = nvcc_path()
-    common = [nvcc, "-O3", "-std=c++17", "-lineinfo", *ARCH, "-Xcompiler", "-fPIC", "--use_fast_math=false"]
-    common = [c for c in common if c != "--use_fast_math=false"]
+    common = [nvcc, "-O3", "-std=c++17", "-lineinfo", *ARCH, "-Xcompiler", "-fPIC"]
     if verbose:
         common += ["-Xptxas", "-v"]
     procs = []

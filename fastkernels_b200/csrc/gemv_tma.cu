@@ -1,7 +1,7 @@
 // bf16 weight-streaming grouped GEMV fed by bulk (TMA) copies through shared-memory rings.
 //
-// Work unit = (pass, tile): a pass is up to 4 packed rows (tokens) of one expert (the pass list is
-// written by the permute kernel), a tile is 16 gate/up pairs (gate_up) or 64 output rows (down).
+// Work unit = (pass, tile): a pass is up to 8 packed rows (tokens) of one expert (4 with the CUDA-core consumers;
+// the pass list is written by the permute kernel), a tile is 16 gate/up pairs (gate_up) or 128 output rows (down).
 // Units are dealt round-robin to one persistent block per SM, so a hot expert spreads over many
 // blocks; its weights cross HBM once and the other passes find them in L2.
 //
@@ -461,7 +461,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) stream_gemv_kernel(const __
     if (GU) pdl_wait();       // pass list and packed order come from the permutation kernel
     // one thread fetches the pass count for the block (a load by every warp of every block queues thousands of
     // requests on one L2 line)
-    if (tid == 0) s.units = p.meta[1] * ((GU ? p.I : p.H) / TILE);
+    if (tid == 0) s.units = __ldcg(p.meta + 1) * ((GU ? p.I : p.H) / TILE);
     __syncthreads();
     if (GU) {
         pdl_trigger();        // only now: the down kernel reads the pass list without waiting (below)
@@ -482,12 +482,14 @@ __global__ void __launch_bounds__(kStreamThreads, 1) stream_gemv_kernel(const __
         {
             uint32_t it = 0;
             int unit = blockIdx.x;
-            int4 next = unit < units ? p.passes[unit / tiles] : make_int4(0, 0, 0, 0);
+            // __ldcg: in the down kernel this warp does not wait for the kernel before it (see launch_experts_stream), so
+            // the pass list must not be served from a line cached before that kernel's predecessor wrote it
+            int4 next = unit < units ? __ldcg(p.passes + unit / tiles) : make_int4(0, 0, 0, 0);
             for (; unit < units; unit += gridDim.x) {
                 const int4 pass = next;
                 const int tile = unit % tiles;
                 const int nu = unit + gridDim.x;
-                if (nu < units) next = p.passes[nu / tiles];
+                if (nu < units) next = __ldcg(p.passes + nu / tiles);
                 const __nv_bfloat16* W;
                 if (pass.x < 0) {
                     W = reinterpret_cast<const __nv_bfloat16*>(GU ? p.shared_gate_up : p.shared_down);
@@ -527,12 +529,12 @@ __global__ void __launch_bounds__(kStreamThreads, 1) stream_gemv_kernel(const __
         // ---------------------------------------------------------------- activation producer
         uint32_t ui = 0;
         int unit = blockIdx.x;
-        int4 next = unit < units ? p.passes[unit / tiles] : make_int4(0, 0, 0, 0);
+        int4 next = unit < units ? __ldcg(p.passes + unit / tiles) : make_int4(0, 0, 0, 0);
         if (!GU) pdl_wait();  // the activations are the gate_up kernel's output
         for (; unit < units; unit += gridDim.x, ++ui) {
             const int4 pass = next;
             const int nu = unit + gridDim.x;
-            if (nu < units) next = p.passes[nu / tiles];
+            if (nu < units) next = __ldcg(p.passes + nu / tiles);
             const int slot = ui % kXSlots;
             const uint32_t par = (ui / kXSlots) & 1u;
             const void* src = nullptr;
@@ -642,6 +644,12 @@ static int launch_down(const ExpertParams& p, cudaStream_t stream) {
     return launch_stream_t<KCH, false, false>(p, stream, wmap, smap);
 }
 
+// Launch order is part of the kernels' contract.  The down kernel is released by the gate_up kernel's trigger and
+// reads the pass list (and overwrites y) WITHOUT waiting for gate_up to finish; only its activation producer waits.
+// That is sound because (1) the gate_up kernel triggers only after its own griddepcontrol.wait, i.e. after the
+// permutation that wrote the pass list has completed, and (2) every kernel earlier in the chain waits before it
+// completes, so the previous call's combine (the reader of y) is done by then.  The down launch must therefore
+// directly follow a gate_up launch of this file; a kernel that triggers before it waits must not be put between.
 int launch_experts_stream(const ExpertParams& p, cudaStream_t stream) {
     if (p.T <= 0) return FK_OK;
     int st;

@@ -10,6 +10,8 @@
 // kernels this replaces are src/fastkernels/kernels/triton/qwen36_router.py:113-187.
 // Tie rule: equal probabilities go to the LOWER expert index.
 
+#include <atomic>
+
 #include "common.cuh"
 #include "kernels.cuh"
 #include "tma.cuh"
@@ -398,11 +400,17 @@ __global__ void __launch_bounds__(kRouterWarps * 32) router_fast_kernel(RouterPa
     }
 }
 
+// dynamic shared memory of router_fast_kernel<TPB, XB> at hidden size H
+static size_t router_fast_smem(int tpb, bool xb, int H) {
+    return (size_t)kRouterWarps * H * 2 + (size_t)tpb * H * (xb ? 2 : 4) + sizeof(float) * ((size_t)H + tpb + 2) + 8 * sizeof(uint64_t) + (size_t)H * 2 + 16;
+}
+constexpr size_t kMaxBlockSmem = 227 * 1024;       // opt-in limit of one block on sm_100
+
 template <int TPB, bool XB>
 static int launch_router_fast(const RouterParams& p, cudaStream_t stream) {
     const int gate = (p.shared_gate_weight && p.shared_gate_out) ? 1 : 0;
     dim3 grid((p.E + gate + kRouterWarps - 1) / kRouterWarps, (p.T + TPB - 1) / TPB);
-    const size_t smem = (size_t)kRouterWarps * p.H * 2 + (size_t)TPB * p.H * (XB ? 2 : 4) + sizeof(float) * ((size_t)p.H + TPB + 2) + 8 * sizeof(uint64_t) + (size_t)p.H * 2 + 16;
+    const size_t smem = router_fast_smem(TPB, XB, p.H);
     auto kern = router_fast_kernel<TPB, XB>;
     FK_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), "router attr");
     FK_CUDA_OK(launch_pdl(kern, grid, dim3(kRouterWarps * 32), smem, stream, p), "router launch");
@@ -663,12 +671,15 @@ int launch_router(const RouterParams& p, int weight_dtype, cudaStream_t stream) 
                     if (p.T >= 64 && p.H <= 2048 && p.H % (16 * kRmWarps) == 0 &&
                         (size_t)(kRmWarps * kRmTokens * 33) * sizeof(float) <= (size_t)33 * (p.H * 2 + 16))
                         return launch_router_mma(p, stream);
+                    // more tokens per block amortise a weight row over more tokens, as far as the block's shared memory
+                    // allows (32 tokens of 4096 columns do not fit: 16 are taken there)
                     if (p.T <= 32) return launch_router_fast<4, true>(p, stream);
                     if (p.T <= 64) return launch_router_fast<8, true>(p, stream);
-                    if (p.T <= 128) return launch_router_fast<16, true>(p, stream);
+                    if (p.T <= 128 || router_fast_smem(32, true, p.H) > kMaxBlockSmem) return launch_router_fast<16, true>(p, stream);
                     return launch_router_fast<32, true>(p, stream);
                 }
-                return p.T <= 64 ? launch_router_fast<4, false>(p, stream) : launch_router_fast<8, false>(p, stream);
+                if (p.T > 64 && router_fast_smem(8, false, p.H) <= kMaxBlockSmem) return launch_router_fast<8, false>(p, stream);
+                return launch_router_fast<4, false>(p, stream);
             }
             return (aligned && p.H % 8 == 0) ? launch_router_t<__nv_bfloat16, 8>(p, stream)
                                              : launch_router_t<__nv_bfloat16, 1>(p, stream);
@@ -695,17 +706,18 @@ static __device__ __align__(256) unsigned g_noalloc_tickets[kNoAllocTicketSlots]
 // Device address of the array for the current device.  In host code the symbol's name is only a
 // handle; the address a kernel can use has to be asked for, once per device, with that device current.
 static int noalloc_tickets(unsigned** out) {
-    static unsigned* cached[64] = {nullptr};
+    // one slot per device ordinal; host threads that make the first call on a device together all store the same value
+    static std::atomic<unsigned*> cached[64];
     int dev = 0;
     FK_CUDA_OK(cudaGetDevice(&dev), "noalloc get device");
     if (dev < 0 || dev >= 64) return FK_ERR_UNSUPPORTED;
-    if (cached[dev] == nullptr) {
-        unsigned* ptr = nullptr;
+    unsigned* ptr = cached[dev].load(std::memory_order_acquire);
+    if (ptr == nullptr) {
         FK_CUDA_OK(cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_noalloc_tickets), "noalloc symbol address");
         if (ptr == nullptr) return FK_ERR_CUDA;
-        cached[dev] = ptr;
+        cached[dev].store(ptr, std::memory_order_release);
     }
-    *out = cached[dev];
+    *out = ptr;
     return FK_OK;
 }
 

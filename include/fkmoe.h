@@ -158,7 +158,8 @@ int fk_moe_router(const fk_moe_call* call, void* stream);
  *   - at most FK_NOALLOC_MAX_TOKENS tokens per call; more is refused with FK_ERR_ARG and a message
  *     in fk_last_cuda_error();
  *   - the first call on each device looks the array's device address up (with that device current);
- *     make that first call before any stream capture begins;
+ *     make that first call before any stream capture begins; the address is kept per device ordinal
+ *     for the life of the process, so do not call this after a cudaDeviceReset of that device;
  *   - all calls on a device share the one array, cleared on `stream` at the start of every call:
  *     calls that overlap on the GPU (different streams) race on it, so keep them on one stream or
  *     otherwise ordered. */

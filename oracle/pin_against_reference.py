@@ -44,6 +44,9 @@ CASES = {
                  torch.float32, 13, 0.0),
     "real16_bf16": (MoESpec(hidden_size=2048, num_experts=16, num_routed_experts=8, expert_intermediate_size=512), 4,
                     torch.bfloat16, 14, 0.0),
+    # the full layer shape (H 2048, E 256, I 512, top-8); outputs come from qwen36_real_moe_update itself
+    "real_full_fp32_1tok": (MoESpec(), 1, torch.float32, 31, 0.0),       # benchmark configuration 1: fp32, one token
+    "real_full_bf16_4tok": (MoESpec(), 4, torch.bfloat16, 32, 0.0),
 }
 ROUTER_CASES = {
     # full-shape router (E=256, H=2048), several tokens

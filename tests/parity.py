@@ -38,6 +38,21 @@ def check_output(out, ref, weight_dtype, *, strict=True):
     return ma, rl
 
 
+def check_output_where_ids_agree(out, ids, ref_ids, ref_out, weight_dtype, *, what=""):
+    """Outputs are compared token by token on every token whose ids equal the oracle's.  A token whose cut is a
+    near-tie may route differently (fp32 sums in another order) and is left out, but never silently: at most one
+    token in 64 (and at least one allowed) may be left out, and the count is printed."""
+    ids_c = ids.cpu()
+    same = (ids_c == ref_ids).all(dim=-1)
+    excluded = int((~same).sum())
+    allowed = max(1, ids_c.shape[0] // 64)
+    assert excluded <= allowed, f"{what}: {excluded} of {ids_c.shape[0]} tokens route differently from the oracle (allowed {allowed})"
+    assert int(same.sum()) > 0, f"{what}: no token left to compare"
+    if excluded:
+        print(f"{what}: {excluded} near-tie token(s) left out of the output comparison")
+    return check_output(out.float().cpu()[same], ref_out[same], weight_dtype)
+
+
 def oracle_layer(hidden, w, top_k, **kw):
     cpu = [None if t is None else t.detach().cpu() for t in w.tuple()]
     bias = None if w.router_bias is None else w.router_bias.cpu()

@@ -33,7 +33,7 @@ from fastkernels_b200.kernels.triton import (
 from fastkernels_b200.moe import expert_permutation
 from fastkernels_b200.spec import MoESpec, MoEWeights
 from fastkernels_b200.workloads import HOT_EXPERT_IDS, make_hidden, make_moe_weights
-from tests.parity import check_output, check_routing, oracle_layer
+from tests.parity import check_output, check_output_where_ids_agree, check_routing, oracle_layer
 from tests.tolerances import default_tolerance
 
 pytestmark = pytest.mark.gpu
@@ -176,6 +176,42 @@ def test_router_odd_shapes_and_many_experts():
         assert torch.equal(ids.cpu(), own_ids)
 
 
+@pytest.mark.parametrize("tokens", [1, 130, 300])
+def test_router_widest_hidden_size(tokens):
+    """H = 4096, the limit the header advertises: the bf16 fast path must pick a block size that fits its shared
+    memory (32 tokens of 4096 columns do not)."""
+    H, E = 4096, 256
+    hidden = _randn(tokens, H, dtype=torch.bfloat16, seed=20)
+    norm_w = _randn(H, dtype=torch.bfloat16, seed=21, scale=0.1)
+    router_w = _randn(E, H, dtype=torch.bfloat16, seed=22, scale=0.02)
+    logits, ids, weights = triton_qwen36_batched_moe_router_decode(hidden, norm_w, router_w, top_k=8)
+    rl, rid, rw = O.router(hidden.cpu(), norm_w.cpu(), router_w.cpu(), top_k=8)
+    torch.testing.assert_close(logits.cpu(), rl, atol=1e-4, rtol=1e-4)
+    own_ids, own_w = O.route_from_logits(logits.cpu(), 8)
+    assert torch.equal(ids.cpu(), own_ids)
+    torch.testing.assert_close(weights.cpu(), own_w, atol=1e-6, rtol=1e-5)
+
+
+def test_alternating_routings_on_one_workspace_never_see_a_stale_pass_list(real_bf16_biased):
+    """Two batches with different routing alternate on one prepared call (one workspace, programmatic dependent
+    launch on): the down kernel reads the pass list without waiting for the gate_up kernel, so a stale list or a
+    y buffer overwritten too early would show up as a difference from the first results."""
+    from fastkernels_b200.plan import MoEDecodePlan
+    w = real_bf16_biased
+    for tokens in (8, 32):
+        plan = MoEDecodePlan(w, tokens)
+        xs = [make_hidden(600 + i, tokens, REAL, dtype=torch.bfloat16, device="cuda") for i in range(2)]
+        want = []
+        for x in xs:
+            out, _, ids, _ = plan.run(x)
+            want.append((out.clone(), ids.clone()))
+        assert not torch.equal(want[0][1], want[1][1])
+        plan.capture()
+        for rep in range(40):
+            out, _, ids, _ = plan.run(xs[rep % 2])
+            assert torch.equal(ids, want[rep % 2][1]) and torch.equal(out, want[rep % 2][0]), f"{tokens} tokens, repetition {rep}"
+
+
 # ---------------------------------------------------------------- experts with fixed routing
 def _fixed_routing(tokens):
     ids = torch.tensor([[(i + t) % 256 for i in FIXED_IDS] for t in range(tokens)], dtype=torch.int64)
@@ -260,8 +296,7 @@ def test_full_layer_bf16_real_shape(real_bf16_biased, tokens):
     out, logits, ids, weights = triton_qwen36_batched_moe_decode(hidden, *w.tuple(), top_k=8, router_bias=w.router_bias)
     ref = oracle_layer(hidden, w, 8)
     check_routing(logits, ids, weights, ref, torch.bfloat16)
-    if torch.equal(ids.cpu(), ref.topk_ids):
-        check_output(out, ref.output, torch.bfloat16)
+    check_output_where_ids_agree(out, ids, ref.topk_ids, ref.output, torch.bfloat16, what=f"layer, {tokens} tokens")
     hist = triton_expert_histogram(ids, 256)
     assert torch.equal(hist.cpu(), O.expert_histogram(ids.cpu(), 256))
     # bitwise run-to-run determinism
@@ -344,8 +379,8 @@ def test_tensor_core_grouped_gemm_matches_gemv_path_and_oracle(real_bf16_biased,
     check_output(tc[0], gemv[0].cpu(), torch.bfloat16)
     sample = torch.arange(0, tokens, max(1, tokens // 6))
     ref = oracle_layer(hidden[sample.cuda()], w, 8)
-    if torch.equal(tc[2].cpu()[sample], ref.topk_ids):
-        check_output(tc[0][sample.cuda()], ref.output, torch.bfloat16)
+    check_output_where_ids_agree(tc[0][sample.cuda()], tc[2][sample.cuda()], ref.topk_ids, ref.output, torch.bfloat16,
+                                 what=f"tensor-core path, {tokens} tokens")
 
 
 def test_tensor_core_path_hot_experts_and_fp32_hidden():
@@ -358,8 +393,8 @@ def test_tensor_core_path_hot_experts_and_fp32_hidden():
     sample = torch.arange(0, 192, 24)
     ref = oracle_layer(hidden[sample.cuda()], w, 8)
     assert torch.equal(ids.cpu()[sample][ref.margin > 2e-6], ref.topk_ids[ref.margin > 2e-6])
-    if torch.equal(ids.cpu()[sample], ref.topk_ids):
-        check_output(out[sample.cuda()], ref.output, torch.bfloat16)
+    check_output_where_ids_agree(out[sample.cuda()], ids[sample.cuda()], ref.topk_ids, ref.output, torch.bfloat16,
+                                 what="hot experts, fp32 hidden")
 
 
 def test_full_layer_fp32_hidden_with_bf16_weights(real_bf16):
@@ -392,9 +427,13 @@ def test_full_layer_matches_reference_golden(name):
     np.testing.assert_allclose(logits.cpu().numpy(), gold["logits"], atol=1e-4, rtol=1e-4)
     clear = torch.from_numpy(gold["margin"]) > 2e-6
     assert torch.equal(ids.cpu()[clear], torch.from_numpy(gold["topk_ids"])[clear])
-    if bool(clear.all()):
-        assert torch.equal(triton_expert_histogram(ids, spec.num_experts).cpu(), torch.from_numpy(gold["histogram"]))
-        check_output(out, torch.from_numpy(gold["output"]), dtype)
+    gold_ids = torch.from_numpy(gold["topk_ids"])
+    hist = triton_expert_histogram(ids, spec.num_experts).cpu()
+    assert torch.equal(hist, O.expert_histogram(ids.cpu(), spec.num_experts))
+    agree = (ids.cpu() == gold_ids).all(dim=-1)
+    assert int((~agree).sum()) <= max(1, tokens // 64)
+    assert bool(agree.all()) is False or torch.equal(hist, torch.from_numpy(gold["histogram"]))
+    check_output_where_ids_agree(out, ids, gold_ids, torch.from_numpy(gold["output"]), dtype, what=f"golden {name}")
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
@@ -481,8 +520,29 @@ def test_full_size_batches_properties(tokens, hot):
     ref = oracle_layer(hidden[sample.cuda()], w, 8)
     clear = ref.margin > 2e-6
     assert torch.equal(ids.cpu()[sample][clear], ref.topk_ids[clear])
-    if bool(clear.all()):
-        check_output(out[sample.cuda()], ref.output, torch.bfloat16)
+    check_output_where_ids_agree(out[sample.cuda()], ids[sample.cuda()], ref.topk_ids, ref.output, torch.bfloat16,
+                                 what=f"{tokens} tokens, hot={hot}")
+
+
+@pytest.mark.parametrize("hot", [False, True])
+def test_full_256_token_batch_every_token_against_the_token_loop_oracle(hot):
+    """The largest single-GPU batch, all 256 tokens (not a sample), against the oracle with the reference's own loop
+    structure (token by token, route by route)."""
+    w = make_moe_weights(3, REAL, dtype=torch.bfloat16, device="cuda", bias_std=0.0 if hot else 0.5,
+                         hot_experts=HOT_EXPERT_IDS if hot else None)
+    tokens = 256
+    hidden = make_hidden(900 + int(hot), tokens, REAL, dtype=torch.bfloat16, device="cuda")
+    out, logits, ids, weights = triton_qwen36_batched_moe_decode(hidden, *w.tuple(), router_bias=w.router_bias)
+    wc = w.to("cpu")
+    ref_out = O.moe_update_token_loop(hidden.cpu(), *wc.tuple(), top_k=8, router_bias=wc.router_bias)
+    ref_logits, ref_ids, ref_w = O.router(hidden.cpu(), wc.norm_weight, wc.router_weight, top_k=8, router_bias=wc.router_bias)
+    torch.testing.assert_close(logits.cpu(), ref_logits, atol=1e-4, rtol=1e-4)
+    own_ids, _ = O.route_from_logits(logits.cpu(), 8)
+    assert torch.equal(ids.cpu(), own_ids)
+    assert torch.equal(triton_expert_histogram(ids, 256).cpu(), O.expert_histogram(ids.cpu(), 256))
+    if hot:
+        assert int(triton_expert_histogram(ids, 256).cpu()[list(HOT_EXPERT_IDS)].sum()) > tokens * 8 // 4
+    check_output_where_ids_agree(out, ids, ref_ids, ref_out, torch.bfloat16, what=f"256 tokens, hot={hot}")
 
 
 # ---------------------------------------------------------------- layer stack
@@ -564,8 +624,9 @@ def test_single_token_fused_kernel_first_run_on_fresh_weights():
         assert torch.equal(outs[0][0], outs[2][0]) and torch.equal(outs[1][0], outs[2][0]), f"weights {rep}"
         assert torch.equal(outs[0][1], outs[2][1])
         ref = oracle_layer(x, w, 8)
-        if bool((ref.margin > 2e-6).all()):
-            assert torch.equal(outs[0][1].cpu(), ref.topk_ids)
+        assert float(ref.margin.min()) > 2e-6, "pick another seed: this token's cut is a near-tie"
+        assert torch.equal(outs[0][1].cpu(), ref.topk_ids)
+        check_output(outs[0][0], ref.output, torch.bfloat16)
         del plan, w
 
 
@@ -652,8 +713,8 @@ def test_peer_memory_layer_with_one_rank_equals_the_plain_layer(real_bf16_biased
         ref = oracle_layer(hidden[sample.cuda()], w32, 8)
         clear = ref.margin > 2e-6
         assert torch.equal(ids.cpu()[sample][clear], ref.topk_ids[clear])
-        if bool(clear.all()):
-            check_output(out[sample.cuda()], ref.output, torch.bfloat16)
+        check_output_where_ids_agree(out[sample.cuda()], ids[sample.cuda()], ref.topk_ids, ref.output, torch.bfloat16,
+                                     what="32 experts, 600 tokens")
         assert exchange.error() == 0
         exchange.close()
     finally:
