@@ -249,6 +249,110 @@ def pack_qwen36_moe_weights_from_state_dict(tensors: Mapping[str, Any], layer_id
     return PackedMoELayer(weights, keys, (lo, hi))
 
 
+class LazySafetensors(Mapping):
+    """Name -> tensor view of a safetensors checkpoint (one file, or a directory of shards with or without an
+    index), fetched tensor by tensor.  Only the shards that hold a requested name are opened, and a tensor is
+    read when it is asked for (the files are memory-mapped), so packing one layer, or one rank's block of
+    experts, never loads the rest of the checkpoint."""
+
+    def __init__(self, path):
+        try:
+            from safetensors import safe_open
+        except ImportError as exc:  # pragma: no cover - optional dependency
+            raise RuntimeError("safetensors is required to load Qwen3.6 MoE weights") from exc
+        import json
+        from pathlib import Path
+        self._open = safe_open
+        self._handles = {}
+        source = Path(path)
+        self._where = {}
+        if source.is_dir():
+            index_files = sorted(source.glob("*.safetensors.index.json"))
+            if index_files:
+                with index_files[0].open("r", encoding="utf-8") as handle:
+                    index = json.load(handle)
+                weight_map = index.get("weight_map", {})
+                if not isinstance(weight_map, dict):
+                    raise ValueError(f"{index_files[0]} does not contain a valid weight_map")
+                self._where = {key: source / str(name) for key, name in weight_map.items()}
+                self.indexed = True
+                return
+            files = sorted(source.glob("*.safetensors"))
+        else:
+            files = [source] if source.exists() else []
+        if not files:
+            raise FileNotFoundError(f"no safetensors files found at {source}")
+        self.indexed = False
+        for f in files:
+            for key in self._handle(f).keys():
+                self._where[key] = f
+
+    def _handle(self, file):
+        h = self._handles.get(file)
+        if h is None:
+            if not file.exists():
+                raise FileNotFoundError(f"{file} is named by the safetensors index but does not exist")
+            h = self._open(str(file), framework="pt", device="cpu")
+            self._handles[file] = h
+        return h
+
+    def __getitem__(self, key):
+        return self._handle(self._where[key]).get_tensor(key)
+
+    def __contains__(self, key):
+        return key in self._where
+
+    def __iter__(self):
+        return iter(self._where)
+
+    def __len__(self):
+        return len(self._where)
+
+    def files_for(self, keys) -> list:
+        return sorted({self._where[k] for k in keys})
+
+
+def _flatten_keys(keys: MoEWeightKeys) -> list:
+    out = []
+    for item in (keys.norm_weight, keys.router_weight, keys.expert_gate_up_weight, keys.expert_down_weight,
+                 keys.shared_gate_up_weight, keys.shared_down_weight, keys.shared_expert_gate_weight):
+        stack = [item]
+        while stack:
+            cur = stack.pop()
+            if cur is None:
+                continue
+            if isinstance(cur, str):
+                out.append(cur)
+            else:
+                stack.extend(cur)
+    return out
+
+
+def load_qwen36_moe_weights_from_safetensors(path, layer_idx: int, *, spec: Optional[MoESpec] = None,
+                                             layer_prefixes: Sequence[str] = DEFAULT_LAYER_PREFIXES,
+                                             device: Optional[Union[str, torch.device]] = None,
+                                             dtype: Optional[torch.dtype] = None,
+                                             expert_range: Optional[tuple] = None) -> PackedMoELayer:
+    """Load and pack one MoE layer from a safetensors file or directory (reference:
+    src/fastkernels/models/qwen36_weights.py:656-716, same lookup order: an index file's weight map if the directory
+    has one, else every `*.safetensors` file in it; same errors: `ValueError` for an index without a weight map,
+    `KeyError` when the index lacks a resolved name, `FileNotFoundError` when nothing is there).
+
+    Where the reference reads every shard that holds one of the layer's tensors completely into host memory and then
+    packs, this goes through `LazySafetensors`: tensors are fetched one at a time from memory-mapped shards and
+    converted to `dtype` on `device` as they are packed, and with `expert_range` a rank touches only its own
+    experts' tensors."""
+    spec = spec or qwen36_35b_a3b_spec()
+    view = LazySafetensors(path)
+    if view.indexed:
+        keys = resolve_qwen36_moe_weight_keys(view, layer_idx, spec=spec, layer_prefixes=layer_prefixes)
+        missing = sorted(k for k in set(_flatten_keys(keys)) if k not in view)
+        if missing:
+            raise KeyError(f"safetensors index is missing resolved keys: {missing[:8]}")
+    return pack_qwen36_moe_weights_from_state_dict(view, layer_idx, spec=spec, layer_prefixes=layer_prefixes, device=device,
+                                                   dtype=dtype, expert_range=expert_range)
+
+
 def state_dict_from_moe_weights(w: MoEWeights, layer_idx: int, *, prefix: str = "model.language_model.layers",
                                 grouped: bool = True) -> dict:
     """The inverse, for tests and synthetic checkpoints: a checkpoint-style mapping (grouped tensors as in the

@@ -113,6 +113,31 @@ def pin_weight_packer(reference_path: str) -> None:
             assert (a is None) == (b is None) and (a is None or torch.equal(a, b)), (name, field)
         print(f"pinned: weight packer [{name}] keys and tensors equal the reference packer's")
 
+    # the safetensors loader on a two-shard checkpoint with an index (the reference's own loader test layout,
+    # tests/test_qwen36_spec.py:544-606) and on the same directory without the index
+    import json
+    import tempfile
+    from safetensors.torch import save_file
+    from fastkernels_b200.weights import load_qwen36_moe_weights_from_safetensors
+    ckpt = variants["split"]
+    names = sorted(ckpt)
+    with tempfile.TemporaryDirectory() as tmp:
+        halves = {"model-00001-of-00002.safetensors": names[: len(names) // 2], "model-00002-of-00002.safetensors": names[len(names) // 2:]}
+        for fname, ks in halves.items():
+            save_file({k: ckpt[k].contiguous() for k in ks}, os.path.join(tmp, fname))
+        index = os.path.join(tmp, "model.safetensors.index.json")
+        with open(index, "w", encoding="utf-8") as f:
+            json.dump({"metadata": {}, "weight_map": {k: fname for fname, ks in halves.items() for k in ks}}, f)
+        for how in ("with index", "without index"):
+            if how == "without index":
+                os.remove(index)
+            ref = rw.load_qwen36_moe_weights_from_safetensors(tmp, 3, spec=rspec)
+            ours = load_qwen36_moe_weights_from_safetensors(tmp, 3, spec=spec).weights
+            for field in fields:
+                a, b = getattr(ref, field), getattr(ours, field)
+                assert (a is None) == (b is None) and (a is None or torch.equal(a, b)), (how, field)
+            print(f"pinned: safetensors loader [{how}] tensors equal the reference loader's")
+
 
 def main() -> None:
     ap = argparse.ArgumentParser()

@@ -142,3 +142,70 @@ def test_errors():
         pack_qwen36_moe_weights_from_state_dict(split_checkpoint(), 7, spec=SPEC)
     with pytest.raises(ValueError, match="expert_range"):
         pack_qwen36_moe_weights_from_state_dict(split_checkpoint(), 0, spec=SPEC, expert_range=(3, 9))
+
+
+def _two_shard_checkpoint(tmp_path, spec, layer=0):
+    """The fake checkpoint of the reference's loader test (tests/test_qwen36_spec.py:544-606): norm and router in
+    the first shard, split per-expert and shared-expert projections in the second, an index that maps the names."""
+    import json
+    safetensors = pytest.importorskip("safetensors.torch")
+    H, E, I = spec.hidden_size, spec.num_experts, spec.expert_intermediate_size
+    shard_a = {f"model.layers.{layer}.post_attention_layernorm.weight": torch.arange(H, dtype=torch.float32),
+               f"model.layers.{layer}.mlp.gate.weight": torch.arange(E * H, dtype=torch.float32).reshape(E, H)}
+    shard_b = {f"model.layers.{layer}.mlp.shared_expert.gate_proj.weight": torch.full((I, H), 3.0),
+               f"model.layers.{layer}.mlp.shared_expert.up_proj.weight": torch.full((I, H), 4.0),
+               f"model.layers.{layer}.mlp.shared_expert.down_proj.weight": torch.full((H, I), 5.0)}
+    for e in range(E):
+        shard_b[f"model.layers.{layer}.mlp.experts.{e}.gate_proj.weight"] = torch.full((I, H), float(e + 1))
+        shard_b[f"model.layers.{layer}.mlp.experts.{e}.up_proj.weight"] = torch.full((I, H), float(e + 11))
+        shard_b[f"model.layers.{layer}.mlp.experts.{e}.down_proj.weight"] = torch.full((H, I), float(e + 21))
+    safetensors.save_file(shard_a, str(tmp_path / "model-00001-of-00002.safetensors"))
+    safetensors.save_file(shard_b, str(tmp_path / "model-00002-of-00002.safetensors"))
+    weight_map = {key: "model-00001-of-00002.safetensors" for key in shard_a}
+    weight_map.update({key: "model-00002-of-00002.safetensors" for key in shard_b})
+    (tmp_path / "model.safetensors.index.json").write_text(json.dumps({"metadata": {}, "weight_map": weight_map}), encoding="utf-8")
+    return shard_a, shard_b
+
+
+def test_loader_uses_the_safetensors_index(tmp_path):
+    from fastkernels_b200.weights import load_qwen36_moe_weights_from_safetensors
+    spec = synthetic_qwen36_spec()
+    H, E, I = spec.hidden_size, spec.num_experts, spec.expert_intermediate_size
+    shard_a, shard_b = _two_shard_checkpoint(tmp_path, spec)
+    packed = load_qwen36_moe_weights_from_safetensors(tmp_path, 0, spec=spec).weights
+    assert packed.expert_gate_up_weight.shape == (E, 2 * I, H)
+    torch.testing.assert_close(packed.expert_gate_up_weight[1, :I], shard_b["model.layers.0.mlp.experts.1.gate_proj.weight"])
+    torch.testing.assert_close(packed.expert_gate_up_weight[1, I:], shard_b["model.layers.0.mlp.experts.1.up_proj.weight"])
+    torch.testing.assert_close(packed.shared_gate_up_weight[I:], shard_b["model.layers.0.mlp.shared_expert.up_proj.weight"])
+    torch.testing.assert_close(packed.expert_down_weight[2], shard_b["model.layers.0.mlp.experts.2.down_proj.weight"])
+    torch.testing.assert_close(packed.router_weight, shard_a["model.layers.0.mlp.gate.weight"])
+    assert packed.shared_expert_gate_weight is None
+    # a rank's shard and a compute dtype, without touching the other experts
+    part = load_qwen36_moe_weights_from_safetensors(tmp_path, 0, spec=spec, expert_range=(1, 3), dtype=torch.bfloat16)
+    assert part.expert_range == (1, 3) and part.weights.expert_down_weight.shape == (2, H, I)
+    assert part.weights.expert_down_weight.dtype == torch.bfloat16
+    torch.testing.assert_close(part.weights.expert_down_weight[0].float(), torch.full((H, I), 22.0))
+
+
+def test_loader_without_an_index_and_its_errors(tmp_path):
+    import json
+    from fastkernels_b200.weights import load_qwen36_moe_weights_from_safetensors
+    spec = synthetic_qwen36_spec()
+    with pytest.raises(FileNotFoundError):
+        load_qwen36_moe_weights_from_safetensors(tmp_path, 0, spec=spec)
+    _two_shard_checkpoint(tmp_path, spec)
+    index = tmp_path / "model.safetensors.index.json"
+    kept = json.loads(index.read_text())
+    # every *.safetensors file of the directory when there is no index
+    index.unlink()
+    packed = load_qwen36_moe_weights_from_safetensors(tmp_path, 0, spec=spec).weights
+    assert packed.expert_down_weight.shape[0] == spec.num_experts
+    # an index whose weight map is not a mapping
+    index.write_text(json.dumps({"weight_map": []}), encoding="utf-8")
+    with pytest.raises(ValueError, match="weight_map"):
+        load_qwen36_moe_weights_from_safetensors(tmp_path, 0, spec=spec)
+    # an index that lacks a tensor of the layer
+    del kept["weight_map"]["model.layers.0.mlp.experts.3.down_proj.weight"]
+    index.write_text(json.dumps(kept), encoding="utf-8")
+    with pytest.raises(KeyError):
+        load_qwen36_moe_weights_from_safetensors(tmp_path, 0, spec=spec)
