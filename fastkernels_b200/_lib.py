@@ -18,7 +18,6 @@ FLAG_FORCE_GEMV = 2
 FLAG_FORCE_TENSOR = 4
 FLAG_NO_FUSED_DECODE = 8
 FLAG_SKIP_FOREIGN = 16
-FLAG_REGISTER_GEMV = 32
 FLAG_TRACE = 64
 FLAG_WIDE_PASSES = 128
 
@@ -62,6 +61,7 @@ SIGNATURES = {
     "fk_last_cuda_error": (C.c_char_p, []),
     "fk_launch_count": (C.c_uint64, []),
     "fk_moe_layer_timed": (C.c_int, [C.POINTER(Call), C.c_void_p, C.POINTER(C.c_float), C.POINTER(C.c_int)]),
+    "fk_moe_experts_timed": (C.c_int, [C.POINTER(Call), C.c_void_p, C.POINTER(C.c_float), C.POINTER(C.c_int)]),
     "fk_moe_trace_offset": (C.c_size_t, [C.POINTER(Dims)]),
     "fk_moe_workspace_bytes": (C.c_size_t, [C.POINTER(Dims)]),
     "fk_moe_workspace_init": (C.c_int, [C.c_void_p, C.c_size_t, C.c_void_p]),

@@ -91,15 +91,16 @@ static int run_experts(const fk_moe_call* c, const Workspace& w, const long long
     // consumers (bf16 models, 8-token passes) up to 96 tokens per call, with the CUDA-core consumers below 64.
     // Above that the tcgen05 grouped GEMM (64-token passes) takes over.
     const bool generic = (c->flags & FK_FLAG_FORCE_GENERIC) != 0;
-    const bool stream_ok = !generic && !(c->flags & FK_FLAG_REGISTER_GEMV) && stream_path_supported(ep, c->weight_dtype);
+    const bool stream_ok = !generic && stream_path_supported(ep, c->weight_dtype);
     const int stream_rows = stream_ok ? stream_pass_rows(ep) : 4;
     const int stream_max_tokens = stream_rows == 8 ? 96 : 63;
-    const bool want_tc = !generic && !(c->flags & (FK_FLAG_FORCE_GEMV | FK_FLAG_REGISTER_GEMV)) &&
+    const bool want_tc = !generic && !(c->flags & FK_FLAG_FORCE_GEMV) &&
                          ((c->flags & FK_FLAG_FORCE_TENSOR) || d.tokens > stream_max_tokens || !stream_ok);
     const bool use_tc = want_tc && (d.tokens >= 64 || (c->flags & FK_FLAG_FORCE_TENSOR)) && tc_path_supported(ep, c->weight_dtype);
     const bool use_stream = !use_tc && stream_ok;
-    // 128-token passes are an option (FK_FLAG_WIDE_PASSES), not a default: at 64 tokens per expert (8 ranks x 256
-    // tokens) they halve the passes but leave room for 4 ring stages instead of 7, and measured slower (153 vs 144 us)
+    // Measured for one rank of 8 x 256 tokens: gate_up 57 us with 64-token passes, 75 us with 128-token passes and two
+    // weight tiles per unit (fewer bytes cross the SM boundary, but four ring stages instead of seven and one round of
+    // large units).  So the wide form stays an option, not a default.
     (void)avg_rows_per_expert;
     const int tc_rows = (c->flags & FK_FLAG_WIDE_PASSES) ? 128 : 64;
     pp.pass_rows = use_tc ? tc_rows : (use_stream ? stream_rows : 4);
@@ -121,8 +122,6 @@ static int run_experts(const fk_moe_call* c, const Workspace& w, const long long
         st = launch_experts_tc(ep, at<__nv_bfloat16>(ws, w.xg), at<__nv_bfloat16>(ws, w.actb), tc_rows, stream);
     else if (use_stream)
         st = launch_experts_stream(ep, stream);
-    else if (!generic && sh_n == d.tokens && gemv_path_supported(ep, c->weight_dtype))
-        st = launch_experts_gemv(ep, stream);
     else
         st = launch_experts_generic(ep, c->weight_dtype, stream);
     if (st != FK_OK) return st;
@@ -194,6 +193,10 @@ uint64_t fk_launch_count(void) { return __atomic_load_n(&g_launches, __ATOMIC_RE
 
 int fk_moe_layer_timed(const fk_moe_call* c, void* stream, float* stage_ms, int* stages) {
     return run_timed(stream, stage_ms, stages, [&] { return fk_moe_layer(c, stream); });
+}
+
+int fk_moe_experts_timed(const fk_moe_call* c, void* stream, float* stage_ms, int* stages) {
+    return run_timed(stream, stage_ms, stages, [&] { stage_mark(); return fk_moe_experts(c, stream); });
 }
 
 int fk_moe_layer_ep_timed(const fk_moe_call* c, const fk_ep_comm* comm, void* stream, float* stage_ms, int* stages) {
@@ -341,7 +344,7 @@ static int moe_layer_impl(const fk_moe_call* c, void* stream, const LayerExtras&
     rp.T = c->dims.tokens; rp.H = c->dims.hidden; rp.E = c->dims.experts; rp.top_k = c->dims.top_k;
     rp.eps = c->eps; rp.norm_offset = c->norm_offset;
     stage_mark();   // start
-    if (c->dims.tokens == 1 && !(c->flags & (FK_FLAG_NO_FUSED_DECODE | FK_FLAG_FORCE_GENERIC | FK_FLAG_REGISTER_GEMV))) {
+    if (c->dims.tokens == 1 && !(c->flags & (FK_FLAG_NO_FUSED_DECODE | FK_FLAG_FORCE_GENERIC))) {
         DecodeParams dp{};
         dp.hidden = c->hidden; dp.hidden_dtype = c->hidden_dtype;
         dp.norm_weight = c->norm_weight; dp.router_weight = c->router_weight; dp.router_bias = c->router_bias;

@@ -29,7 +29,6 @@ struct Workspace {
     size_t touched;      // i32 [E+1]   ascending list of experts with count>0
     size_t order;        // i32 [R]     packed row -> route (token*k+slot)
     size_t inv;          // i32 [R]     route -> packed row
-    size_t tiles;        // i32 [4*maxTiles]  tensor-core tile table (expert, row0, rows, pad)
     size_t passes;       // int4 [R+T+1]  GEMV pass list: (expert or -1 for shared, first packed row, rows<=4, first token)
     size_t shared_gate;  // f32 [T]
     size_t act;          // f32 [(R+T), I]  SwiGLU activations per packed row (+ shared rows)
@@ -65,7 +64,6 @@ __host__ inline Workspace workspace_layout(const fk_moe_dims& d) {
     w.touched = take(sizeof(int32_t) * (E + 1));
     w.order = take(sizeof(int32_t) * R);
     w.inv = take(sizeof(int32_t) * R);
-    w.tiles = take(sizeof(int32_t) * 4 * (rpad / 16 + 1));
     w.passes = take(sizeof(int32_t) * 4 * (R + T + 1));
     w.shared_gate = take(sizeof(float) * T);
     w.act = take(sizeof(float) * rows * I);

@@ -103,10 +103,7 @@ struct ExpertParams {
 int launch_combine_ep(const ExpertParams& p, cudaStream_t stream);
 // shape-agnostic kernels (any dtype, any H/I)
 int launch_experts_generic(const ExpertParams& p, int weight_dtype, cudaStream_t stream);
-// bf16 weight-streaming grouped GEMV (H,I in {256,512,1024,2048})
-bool gemv_path_supported(const ExpertParams& p, int weight_dtype);
-int launch_experts_gemv(const ExpertParams& p, cudaStream_t stream);
-// bf16 grouped GEMV fed by bulk copies through a shared-memory ring (same shapes as the GEMV path)
+// bf16 grouped GEMV fed by bulk copies through a shared-memory ring (H, I in {256, 512, 1024, 2048})
 bool stream_path_supported(const ExpertParams& p, int weight_dtype);
 int launch_experts_stream(const ExpertParams& p, cudaStream_t stream);
 int stream_pass_rows(const ExpertParams& p);    // 8 when both streaming kernels run their tensor-core consumers, else 4

@@ -33,9 +33,14 @@ namespace fk {
 constexpr int kTcStagesMax = 8;
 constexpr int kTcThreads = 192;
 constexpr int kTcTileBytes = 128 * 64 * 2;          // one 128-row x 64-column bf16 operand tile
-__host__ __device__ constexpr int tc_stages(bool gu, int nmax) { return nmax == 64 ? (gu ? 7 : 8) : (gu ? 4 : 6); }
+// MT = weight tiles per unit (they share the unit's activation tile: with 2, the activations of a pass cross the SM
+// boundary half as often).  Ring depth: what fits beside the barriers and the up-value buffer.
+__host__ __device__ constexpr int tc_stages(bool gu, int nmax, int mt) {
+    return mt == 2 ? 4 : (nmax == 64 ? (gu ? 7 : 8) : (gu ? 5 : 6));
+}
 __host__ __device__ constexpr int tc_b_bytes(int nmax) { return nmax * 64 * 2; }
-__host__ __device__ constexpr int tc_ustride(int nmax) { return nmax + 1; }   // row stride (floats) of the up-value buffer
+constexpr int kTcUStride = 17;                      // row stride (floats) of the up-value exchange buffer (16 columns at a time)
+constexpr int kTcUBytes = 2 * 64 * kTcUStride * (int)sizeof(float);
 
 struct TcBarriers {
     uint64_t full[kTcStagesMax];
@@ -56,23 +61,24 @@ struct TcParams {
     int H, I;
 };
 
-template <bool GU, int NMAX>
+template <bool GU, int NMAX, int MT>
 __global__ void __launch_bounds__(kTcThreads, 1)
 tc_grouped_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ CUtensorMap smap,
                   const __grid_constant__ CUtensorMap amap, TcParams p) {
     extern __shared__ unsigned char smem_dyn[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~uintptr_t(1023));
     constexpr int kTcBBytes = tc_b_bytes(NMAX);
-    constexpr int kTcUStride = tc_ustride(NMAX);
-    constexpr int kTcTmemCols = 2 * NMAX;                 // two accumulator buffers
-    constexpr int kStageBytes = kTcTileBytes + kTcBBytes;
-    constexpr int kNumStages = tc_stages(GU, NMAX);
+    constexpr int kTcTmemCols = 2 * MT * NMAX;            // two accumulator buffers of MT tiles
+    static_assert(kTcTmemCols <= 512 && (kTcTmemCols & (kTcTmemCols - 1)) == 0, "tensor memory holds 512 columns");
+    constexpr int kABytes = MT * kTcTileBytes;
+    constexpr int kStageBytes = kABytes + kTcBBytes;
+    constexpr int kNumStages = tc_stages(GU, NMAX, MT);
     TcBarriers& bar = *reinterpret_cast<TcBarriers*>(smem + kNumStages * kStageBytes);
     float* ubuf = reinterpret_cast<float*>(smem + kNumStages * kStageBytes + 1024);   // GU: [2][64][kTcUStride]
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int K = GU ? p.H : p.I;
     const int chunks = K / 64;
-    const int tiles = GU ? p.I / 64 : p.H / 128;
+    const int tiles = (GU ? p.I / 64 : p.H / 128) / MT;     // units per pass
     const int rows_per_expert = GU ? 2 * p.I : p.H;
     if (tid == 0) {
         for (int i = 0; i < kNumStages; ++i) { mbar_init(&bar.full[i], 1); mbar_init(&bar.empty[i], 1); }
@@ -105,22 +111,29 @@ tc_grouped_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constan
                 const int mt = unit % tiles;
                 const int npad = (pass.z + 15) & ~15;
                 const CUtensorMap* wm = pass.x < 0 ? &smap : &wmap;
-                const int wrow = (pass.x < 0 ? 0 : pass.x * rows_per_expert) + mt * (GU ? 64 : 128);
+                const int wrow = (pass.x < 0 ? 0 : pass.x * rows_per_expert) + mt * MT * (GU ? 64 : 128);
                 for (int c = 0; c < chunks; ++c, ++it) {
                     const int stage = it % kNumStages;
                     const uint32_t par = (it / kNumStages) & 1u;
                     mbar_wait(&bar.empty[stage], par ^ 1u, &bar.abort_flag);
                     unsigned char* st = smem + stage * kStageBytes;
-                    mbar_expect_tx(&bar.full[stage], kTcTileBytes + npad * 128);
-                    if (GU) {
-                        tma_load_2d(st, wm, c * 64, wrow, &bar.full[stage]);                            // 64 gate rows
-                        tma_load_2d(st + kTcTileBytes / 2, wm, c * 64, wrow + p.I, &bar.full[stage]);   // 64 up rows
-                    } else {
-                        tma_load_2d(st, wm, c * 64, wrow, &bar.full[stage]);
+                    // activations: whole 64-row boxes (rows past the pass belong to the next expert or are zero-filled
+                    // past the end; the epilogue ignores them).  Boxes of 16 rows cost one TMA instruction per 2 KB.
+                    const int nb64 = (npad + 63) / 64;
+                    mbar_expect_tx(&bar.full[stage], kABytes + nb64 * 64 * 128);
+#pragma unroll
+                    for (int t = 0; t < MT; ++t) {
+                        unsigned char* at = st + t * kTcTileBytes;
+                        if (GU) {
+                            tma_load_2d(at, wm, c * 64, wrow + t * 64, &bar.full[stage]);                            // 64 gate rows
+                            tma_load_2d(at + kTcTileBytes / 2, wm, c * 64, wrow + t * 64 + p.I, &bar.full[stage]);   // 64 up rows
+                        } else {
+                            tma_load_2d(at, wm, c * 64, wrow + t * 128, &bar.full[stage]);
+                        }
                     }
-                    unsigned char* bt = st + kTcTileBytes;
-                    for (int j = 0; j < npad / 16; ++j)
-                        tma_load_2d(bt + j * 16 * 128, &amap, c * 64, pass.y + j * 16, &bar.full[stage]);
+                    unsigned char* bt = st + kABytes;
+                    for (int j = 0; j < nb64; ++j)
+                        tma_load_2d(bt + j * 64 * 128, &amap, c * 64, pass.y + j * 64, &bar.full[stage]);
                 }
             }
         }
@@ -135,18 +148,20 @@ tc_grouped_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constan
                 const uint32_t acc = ui & 1u;
                 mbar_wait(&bar.tempty[acc], ((ui >> 1) & 1u) ^ 1u, &bar.abort_flag);
                 tc_fence_after_sync();
-                const uint32_t d0 = tmem_base + acc * (uint32_t)NMAX;
+                const uint32_t d0 = tmem_base + acc * (uint32_t)(MT * NMAX);
                 for (int c = 0; c < chunks; ++c, ++it) {
                     const int stage = it % kNumStages;
                     const uint32_t par = (it / kNumStages) & 1u;
                     mbar_wait(&bar.full[stage], par, &bar.abort_flag);
                     tc_fence_after_sync();
                     const unsigned char* st = smem + stage * kStageBytes;
-                    const unsigned char* bt = st + kTcTileBytes;
+                    const unsigned char* bt = st + kABytes;
 #pragma unroll
                     for (int kk = 0; kk < 4; ++kk) {
                         const uint32_t accum = (c > 0 || kk > 0) ? 1u : 0u;
-                        umma_bf16(d0, umma_smem_desc(st + kk * 32), umma_smem_desc(bt + kk * 32), idesc, accum);
+#pragma unroll
+                        for (int t = 0; t < MT; ++t)
+                            umma_bf16(d0 + t * NMAX, umma_smem_desc(st + t * kTcTileBytes + kk * 32), umma_smem_desc(bt + kk * 32), idesc, accum);
                     }
                     umma_commit(&bar.empty[stage]);      // the stage is free once these MMAs have read it
                 }
@@ -157,7 +172,7 @@ tc_grouped_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constan
         // ------------------------------------------------------------------ epilogue warps
         const int q = warp & 3;                          // TMEM lane quarter this warp may read
         const int r = q * 32 + lane;                     // row of the 128-row tile
-        uint32_t ui = 0;
+        uint32_t ui = 0, uc = 0;                         // units done; 16-column chunks handed over (selects the buffer)
         for (int unit = blockIdx.x; unit < units; unit += gridDim.x, ++ui) {
             const int4 pass = p.passes[unit / tiles];
             const int mt = unit % tiles;
@@ -165,41 +180,43 @@ tc_grouped_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constan
             const uint32_t acc = ui & 1u;
             mbar_wait(&bar.tfull[acc], (ui >> 1) & 1u, &bar.abort_flag);
             tc_fence_after_sync();
-            const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + acc * (uint32_t)NMAX;
-            if (GU) {
-                // lanes 64..127 hold the up rows: hand them to the warps that hold the gate rows of the same pairs
-                float* ub = ubuf + (size_t)acc * 64 * kTcUStride;
-                if (q >= 2) {
-                    for (int c16 = 0; c16 < npad / 16; ++c16) {
-                        float u[16];
-                        tmem_ld16(taddr + c16 * 16, u);
+            const uint32_t taddr0 = tmem_base + ((uint32_t)(q * 32) << 16) + acc * (uint32_t)(MT * NMAX);
+#pragma unroll 1
+            for (int t = 0; t < MT; ++t) {
+                const uint32_t taddr = taddr0 + t * NMAX;
+                const int tile = mt * MT + t;
+                if (GU) {
+                    // lanes 64..127 hold the up rows: they reach the warps that hold the gate rows of the same pairs through
+                    // shared memory, 16 columns at a time in two alternating buffers (one barrier per 16 columns)
+                    for (int c16 = 0; c16 < npad / 16; ++c16, ++uc) {
+                        float* ub = ubuf + (size_t)(uc & 1u) * 64 * kTcUStride;
+                        float v[16];
+                        tmem_ld16(taddr + c16 * 16, v);
+                        if (q >= 2) {
 #pragma unroll
-                        for (int t = 0; t < 16; ++t) ub[(size_t)(r - 64) * kTcUStride + c16 * 16 + t] = u[t];
+                            for (int j = 0; j < 16; ++j) ub[(size_t)(r - 64) * kTcUStride + j] = v[j];
+                        }
+                        named_bar_sync(2, 128);
+                        if (q < 2) {
+#pragma unroll
+                            for (int j = 0; j < 16; ++j) {
+                                const int tok = c16 * 16 + j;
+                                if (tok < n) {
+                                    const float u = ub[(size_t)r * kTcUStride + j];
+                                    p.actb[(size_t)(pass.y + tok) * p.I + tile * 64 + r] = __float2bfloat16_rn(silu_mul(v[j], u));
+                                }
+                            }
+                        }
                     }
-                }
-                named_bar_sync(2, 128);
-                if (q < 2) {
+                } else {
                     for (int c16 = 0; c16 < npad / 16; ++c16) {
                         float g[16];
                         tmem_ld16(taddr + c16 * 16, g);
 #pragma unroll
-                        for (int t = 0; t < 16; ++t) {
-                            const int tok = c16 * 16 + t;
-                            if (tok < n) {
-                                const float u = ub[(size_t)r * kTcUStride + tok];
-                                p.actb[(size_t)(pass.y + tok) * p.I + mt * 64 + r] = __float2bfloat16_rn(silu_mul(g[t], u));
-                            }
+                        for (int j = 0; j < 16; ++j) {
+                            const int tok = c16 * 16 + j;
+                            if (tok < n) p.y[(size_t)(pass.y + tok) * p.H + tile * 128 + r] = g[j];
                         }
-                    }
-                }
-            } else {
-                for (int c16 = 0; c16 < npad / 16; ++c16) {
-                    float g[16];
-                    tmem_ld16(taddr + c16 * 16, g);
-#pragma unroll
-                    for (int t = 0; t < 16; ++t) {
-                        const int tok = c16 * 16 + t;
-                        if (tok < n) p.y[(size_t)(pass.y + tok) * p.H + mt * 128 + r] = g[t];
                     }
                 }
             }
@@ -313,7 +330,7 @@ bool tc_path_supported(const ExpertParams& p, int weight_dtype) {
 }
 
 // gather -> gate_up GEMM (+SwiGLU) -> down GEMM; the pass list in p.passes must hold passes of <= NMAX rows
-template <int NMAX>
+template <int NMAX, int MT>
 static int launch_experts_tc_t(const ExpertParams& p, __nv_bfloat16* xg, __nv_bfloat16* actb, cudaStream_t stream) {
     if (p.T <= 0) return FK_OK;
     const uint64_t rows = (uint64_t)p.routes + (p.shared_gate_up ? p.shared_n : 0);
@@ -323,10 +340,10 @@ static int launch_experts_tc_t(const ExpertParams& p, __nv_bfloat16* xg, __nv_bf
     const uint64_t e_rows = p.gate_up ? (uint64_t)p.E : 0;
     bool ok = weight_tensor_map(dummy_gu, p.gate_up ? e_rows * 2 * p.I : 2 * p.I, p.H, 64, &w_gu) &&
               weight_tensor_map(p.shared_gate_up ? p.shared_gate_up : dummy_gu, 2 * (uint64_t)p.I, p.H, 64, &s_gu) &&
-              weight_tensor_map(xg, rows, p.H, 16, &a_x) &&
+              weight_tensor_map(xg, rows, p.H, 64, &a_x) &&
               weight_tensor_map(dummy_dn, p.down ? e_rows * p.H : p.H, p.I, 128, &w_dn) &&
               weight_tensor_map(p.shared_down ? p.shared_down : dummy_dn, (uint64_t)p.H, p.I, 128, &s_dn) &&
-              weight_tensor_map(actb, rows, p.I, 16, &a_act);
+              weight_tensor_map(actb, rows, p.I, 64, &a_act);
     if (!ok) return FK_ERR_UNSUPPORTED;
 
     {
@@ -340,16 +357,16 @@ static int launch_experts_tc_t(const ExpertParams& p, __nv_bfloat16* xg, __nv_bf
     TcParams tp{};
     tp.passes = p.passes; tp.meta = p.meta; tp.actb = actb; tp.y = p.y; tp.error_word = p.error_word; tp.H = p.H; tp.I = p.I;
     {
-        auto kern = tc_grouped_kernel<true, NMAX>;
-        const int smem = tc_stages(true, NMAX) * (kTcTileBytes + tc_b_bytes(NMAX)) + 1024 + 2 * 64 * tc_ustride(NMAX) * (int)sizeof(float) + 1024;
+        auto kern = tc_grouped_kernel<true, NMAX, MT>;
+        const int smem = tc_stages(true, NMAX, MT) * (MT * kTcTileBytes + tc_b_bytes(NMAX)) + 1024 + kTcUBytes + 1024;
         FK_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem), "tc gate_up attr");
         FK_CUDA_OK(launch_pdl(kern, dim3(sm_count()), dim3(kTcThreads), (size_t)smem, stream, w_gu, s_gu, a_x, tp), "tc gate_up launch");
         FK_LAUNCH_OK("tc gate_up launch");
     }
     stage_mark();   // end of gate_up
     {
-        auto kern = tc_grouped_kernel<false, NMAX>;
-        const int smem = tc_stages(false, NMAX) * (kTcTileBytes + tc_b_bytes(NMAX)) + 1024 + 1024;
+        auto kern = tc_grouped_kernel<false, NMAX, MT>;
+        const int smem = tc_stages(false, NMAX, MT) * (MT * kTcTileBytes + tc_b_bytes(NMAX)) + 1024 + 1024;
         FK_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem), "tc down attr");
         FK_CUDA_OK(launch_pdl(kern, dim3(sm_count()), dim3(kTcThreads), (size_t)smem, stream, w_dn, s_dn, a_act, tp), "tc down launch");
         FK_LAUNCH_OK("tc down launch");
@@ -358,8 +375,13 @@ static int launch_experts_tc_t(const ExpertParams& p, __nv_bfloat16* xg, __nv_bf
     return FK_OK;
 }
 
+// pass_rows 64: one weight tile per unit (experts that see a few tokens: the kernel is a weight stream);
+// pass_rows 128: 128-token passes and two weight tiles per unit (experts that see dozens of tokens: what crosses the
+// SM boundary per expert drops from two passes x (weights + 8 x activations) to weights + 4 x activations).
 int launch_experts_tc(const ExpertParams& p, __nv_bfloat16* xg, __nv_bfloat16* actb, int pass_rows, cudaStream_t stream) {
-    return pass_rows > 64 ? launch_experts_tc_t<128>(p, xg, actb, stream) : launch_experts_tc_t<64>(p, xg, actb, stream);
+    const bool pairs_ok = (p.I / 64) % 2 == 0 && (p.H / 128) % 2 == 0;
+    if (pass_rows > 64) return pairs_ok ? launch_experts_tc_t<128, 2>(p, xg, actb, stream) : launch_experts_tc_t<128, 1>(p, xg, actb, stream);
+    return launch_experts_tc_t<64, 1>(p, xg, actb, stream);
 }
 
 }  // namespace fk

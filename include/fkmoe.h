@@ -58,7 +58,6 @@ typedef struct fk_moe_dims {
 #define FK_FLAG_FORCE_GEMV 2u      /* never use the tensor-core grouped GEMM */
 #define FK_FLAG_FORCE_TENSOR 4u    /* use the tensor-core grouped GEMM whenever the shape allows */
 #define FK_FLAG_NO_FUSED_DECODE 8u /* T==1: run the staged kernels instead of the fused single-token kernel */
-#define FK_FLAG_REGISTER_GEMV 32u  /* grouped GEMV with direct global->register loads instead of the bulk-copy ring */
 #define FK_FLAG_TRACE 64u          /* T==1 fused kernel: write per-block phase timestamps at the start of the workspace's y
                                       region, u64 [blocks][32] (fk_moe_trace_offset() gives the offset).  Nanoseconds of
                                       the global timer in slots 0 entry, 1 constant copies issued, 20 the kernel before
@@ -69,7 +68,7 @@ typedef struct fk_moe_dims {
                                       7 exit (0 where a block skips the step); SM cycle counter in 8 (entry) and 9 (exit).
                                       Ignored when the record (blocks * 256 bytes) does not fit the y region. */
 #define FK_FLAG_SKIP_FOREIGN 16u   /* ids outside [expert_base, expert_base+E) are skipped instead of clamped */
-#define FK_FLAG_WIDE_PASSES 128u   /* tcgen05 path: 128 tokens per pass instead of 64 (experts that see dozens of tokens) */
+#define FK_FLAG_WIDE_PASSES 128u   /* tcgen05 path: 128 tokens per pass and two weight tiles per unit instead of 64 and one */
 
 typedef struct fk_moe_call {
     fk_moe_dims dims;
@@ -117,6 +116,8 @@ uint64_t fk_launch_count(void);
  * [row gather, tensor-core path only], gate_up, down, combine; single-token kernel: one stage.  No counterpart in the reference (it times with a host clock around
  * a Python loop, e.g. bench/qwen36_real_moe_microbench.py:101-119). */
 int fk_moe_layer_timed(const fk_moe_call* call, void* stream, float* stage_ms, int* stages);
+/* The same for fk_moe_experts: permute (with the shared-gate kernel, if any), [row gather], gate_up, down, combine. */
+int fk_moe_experts_timed(const fk_moe_call* call, void* stream, float* stage_ms, int* stages);
 
 /* Limit of every device-side wait on another block or another rank, in SM clock cycles (default: about one
  * second; 0 restores the default).  A wait that runs out never traps and never spins on: the kernel raises an

@@ -77,7 +77,8 @@ def test_expert_histogram_bit_exact(idtype):
     assert torch.equal(cand.cpu(), O.expert_histogram(ids, 256))
 
 
-@pytest.mark.parametrize("tokens,experts", [(1, 256), (7, 5), (64, 256), (256, 256), (2048, 32), (300, 1024)])
+@pytest.mark.parametrize("tokens,experts", [(1, 256), (7, 5), (64, 256), (256, 256), (2048, 32), (300, 1024), (511, 256), (513, 64),
+                                            (2048, 256), (5000, 1024)])
 def test_expert_permutation_bit_exact(tokens, experts):
     g = torch.Generator().manual_seed(tokens)
     ids = torch.randint(0, experts, (tokens, 8), generator=g)
@@ -318,7 +319,7 @@ def test_full_layer_single_token_api(real_bf16):
     check_output(out_u, oracle_layer(hidden.unsqueeze(0), w_u, 8).output[0], torch.bfloat16)
 
 
-@pytest.mark.parametrize("flags", [_lib.FLAG_FORCE_GENERIC, _lib.FLAG_REGISTER_GEMV])
+@pytest.mark.parametrize("flags", [_lib.FLAG_FORCE_GENERIC, _lib.FLAG_FORCE_GEMV | _lib.FLAG_NO_FUSED_DECODE])
 def test_full_layer_generic_kernels_agree(real_bf16, flags):
     w = real_bf16
     hidden = make_hidden(9, 3, REAL, dtype=torch.bfloat16, device="cuda")
