@@ -22,9 +22,12 @@
 //           gated shared expert (and the residual).
 //
 // Consumers.  Warp w owns columns [256 w, 256 w + 256) of the hidden dimension (phase B) and [64 w, 64 w + 64) of
-// the intermediate dimension (phase C).  A stage is one [16 rows x 256 columns] weight tile (four 128-byte-swizzled
-// TMA boxes), read with ldmatrix and multiplied on the tensor cores (mma.sync m16n8k16, bf16 in, fp32 accumulate):
-// the sixteen weight rows are the M rows, the token is column 0 of N.  Seven of the eight N columns are wasted, and
+// the intermediate dimension (phase C).  A stage is 8 KB of weights in 128-byte-swizzled TMA boxes of 16 rows x 64
+// columns: in phase B 16 gate rows and their 16 up rows over 128 columns (two copies through a 3-D view of the
+// gate_up tensor, each bringing a gate box and its up box: copies of 2 KB streamed at 5.5 TB/s in a stand-alone
+// probe, copies of 4 KB at 6.1), in phase C the down tiles of four slots.  Boxes are read with ldmatrix and
+// multiplied on the tensor cores (mma.sync m16n8k16, bf16 in, fp32 accumulate): the sixteen weight rows are the
+// M rows, the token is column 0 of N.  Seven of the eight N columns are wasted, and
 // it is still five times fewer instructions than unpacking bf16 pairs and issuing one FMA per weight, which is what
 // bounded this kernel before (each warp issued ~4300 instructions at ~6 stall cycles each).  Products of bf16
 // values are exact in fp32, so the sums differ from a CUDA-core dot product only in their order.  The fp32 SwiGLU
@@ -91,6 +94,7 @@ struct D1Smem {
     float wnorm[FK_MAX_TOP_K];                    // renormalised routing weights
     int ids[FK_MAX_TOP_K];
     unsigned tag;                                 // this launch's tag for the published logits
+    int nids;                                     // ids[0 .. nids) are valid (grows while the select warp runs its rounds)
     int abort_flag;
 };
 
@@ -240,7 +244,15 @@ __device__ __forceinline__ void poll_and_select(const DecodeParams& p, D1Smem& s
     if (!complete && lane == 0) s.abort_flag = 1;
     int my_i;
     float my_w;
-    topk_warp_regs<EPL>(v, p.E, p.top_k, lane, my_i, my_w);
+    // every winner is handed to the producer warp as soon as its round is over: the blocks whose gate_up tiles belong
+    // to the first slots start their copies a microsecond before the last round and the weights are done
+    topk_warp_regs<EPL>(v, p.E, p.top_k, lane, my_i, my_w, [&](int r, int expert) {
+        if (lane == 0) {
+            s.ids[r] = expert;
+            __threadfence_block();
+            *reinterpret_cast<volatile int*>(&s.nids) = r + 1;
+        }
+    });
     if (lane < p.top_k) {
         s.ids[lane] = my_i;
         s.wnorm[lane] = my_w;
@@ -282,6 +294,7 @@ decode1_kernel(const __grid_constant__ CUtensorMap gu_map, const __grid_constant
             mbar_init(&s.rdone, kD1Consumers);
             mbar_init(&s.ids_ready, 1);
             s.abort_flag = 0;
+            s.nids = 0;
             prefetch_tensormap(&gu_map);
             prefetch_tensormap(&dn_map);
         }
@@ -310,7 +323,7 @@ decode1_kernel(const __grid_constant__ CUtensorMap gu_map, const __grid_constant
         // are issued as ring slots free up.
         const int nstatic = 2 * max(0, min(pl.atoms, pl.shared_atoms - pl.atom0)) * kD1Consumers;   // stages of shared atoms
         const int total = (pl.nB + pl.nC) * kD1Consumers;
-        bool token_issued = false, have_ids = false;
+        bool token_issued = false;
 #pragma unroll 1
         for (int base = 0; base < total || !token_issued; base += kD1Stages) {
 #pragma unroll 1
@@ -341,19 +354,6 @@ decode1_kernel(const __grid_constant__ CUtensorMap gu_map, const __grid_constant
                         }
                         __syncwarp();
                     }
-                    if (!have_ids && base + kD1Stages > nstatic && base < total) {
-                        have_ids = true;
-                        if (lane == 0) {
-                            // a short pause between polls: this warp shares its scheduler with the warp that publishes the logits
-                            const long long t0 = clock64();
-                            while (!mbar_try_wait(&s.ids_ready, 0)) {
-                                __nanosleep(32);
-                                if (clock64() - t0 > kWaitCycles) { s.abort_flag = 1; break; }
-                            }
-                            D1_TRACE(4);
-                        }
-                        __syncwarp();
-                    }
                 }
                 if (lane < kD1Stages && it < total && ((it < nstatic) == (half == 0))) {
                     const int n = it >> 3, w = it & 7;            // stage n of warp w
@@ -361,23 +361,40 @@ decode1_kernel(const __grid_constant__ CUtensorMap gu_map, const __grid_constant
                     const uint32_t par = (it / kD1Stages) & 1u;
                     mbar_wait(&s.empty[slot], par ^ 1u, &s.abort_flag);      // passes at once on a slot's first lap
                     unsigned char* dst = s.stage[slot];
+                    // the ids this stage's addresses depend on: one slot for a gate_up stage, all of them for a down stage
+                    int need = 0;
+                    if (n >= pl.nB) need = p.top_k;
+                    else if (pl.atom0 + (n >> 1) >= pl.shared_atoms) need = (pl.atom0 + (n >> 1) - pl.shared_atoms) / (I / kD1Tile) + 1;
+                    if (need > 0 && *reinterpret_cast<volatile int*>(&s.nids) < need) {
+                        // a short pause between polls: this warp shares its scheduler with warps that have work
+                        const long long t0 = clock64();
+                        while (*reinterpret_cast<volatile int*>(&s.nids) < need) {
+                            __nanosleep(20);
+                            if (clock64() - t0 > kWaitCycles) { s.abort_flag = 1; break; }
+                        }
+                    }
+                    __threadfence_block();                        // ids[] is read after the count that covers it
+                    if (it == nstatic) D1_TRACE(4);
                     if (n < pl.nB) {
-                        // gate (even n) or up (odd n) tile of atom n / 2, columns [256 w, 256 w + 256)
+                        // half n & 1 of atom n / 2: columns [256 w + 128 (n & 1), + 128) of the 16 gate rows and of
+                        // their up rows, as two copies of [2 halves x 16 rows x 64 columns] (4 KB each)
                         const int g = pl.atom0 + (n >> 1);
                         const CUtensorMap* map;
-                        int y;
+                        int y, z;
                         if (g < pl.shared_atoms) {
                             map = &sgu_map;
                             y = g * kD1Tile;
+                            z = 0;
                         } else {
                             const int q = g - pl.shared_atoms;
                             map = &gu_map;
-                            y = s.ids[q / (I / kD1Tile)] * 2 * I + (q % (I / kD1Tile)) * kD1Tile;
+                            y = (q % (I / kD1Tile)) * kD1Tile;
+                            z = 2 * s.ids[q / (I / kD1Tile)];
                         }
-                        if (n & 1) y += I;
                         mbar_expect_tx(&s.full[slot], kD1StageBytes);
 #pragma unroll
-                        for (int sl = 0; sl < 4; ++sl) tma_load_2d(dst + sl * 2048, map, w * 256 + sl * 64, y, &s.full[slot]);
+                        for (int op = 0; op < 2; ++op)
+                            tma_load_3d(dst + op * 4096, map, w * 256 + (n & 1) * 128 + op * 64, y, z, &s.full[slot]);
                     } else {
                         // down tiles of four slots, columns [64 w, 64 w + 64) of the block's 16 output rows
                         const int c = n - pl.nB;
@@ -528,32 +545,43 @@ decode1_kernel(const __grid_constant__ CUtensorMap gu_map, const __grid_constant
             bx[ks][1] = gid == 0 ? d1_lds32(src + 16) : 0u;
         }
 #pragma unroll 1
-        for (int n = 0; n < pl.nB; ++n) {
-            const int it = n * kD1Consumers + warp;
-            const int slot = it % kD1Stages;
-            mbar_wait(&s.full[slot], (it / kD1Stages) & 1u, &s.abort_flag);
-            if (tid == 0 && n == 0) D1_TRACE(11);
-            const uint32_t base = smem_u32(s.stage[slot]);
-            float c[8][4];                                 // two accumulators per box: dependent MMAs wait for each other
+        for (int j = 0; j < pl.atoms; ++j) {
+            // a stage holds four boxes: gate and up rows over columns [0, 64) of the stage, then over [64, 128)
+            float g0 = 0.f, g2 = 0.f, u0 = 0.f, u2 = 0.f;       // tile rows gid and gid + 8 (lanes with tig == 0)
 #pragma unroll
-            for (int q = 0; q < 8; ++q) { c[q][0] = c[q][1] = c[q][2] = c[q][3] = 0.f; }
-            {
-                uint32_t a[4][4][4];
+            for (int h = 0; h < 2; ++h) {
+                const int it = (2 * j + h) * kD1Consumers + warp;
+                const int slot = it % kD1Stages;
+                mbar_wait(&s.full[slot], (it / kD1Stages) & 1u, &s.abort_flag);
+                if (tid == 0 && j == 0 && h == 0) D1_TRACE(11);
+                const uint32_t base = smem_u32(s.stage[slot]);
+                float c[8][4];                             // gate: c[0..3], up: c[4..7]; two per box: dependent MMAs wait for each other
 #pragma unroll
-                for (int sl = 0; sl < 4; ++sl) box_load(a[sl], base + sl * 2048, lane);
+                for (int q = 0; q < 8; ++q) { c[q][0] = c[q][1] = c[q][2] = c[q][3] = 0.f; }
+                {
+                    uint32_t a[4][4][4];
 #pragma unroll
-                for (int kk = 0; kk < 4; ++kk) {
+                    for (int sl = 0; sl < 4; ++sl) box_load(a[sl], base + sl * 2048, lane);
 #pragma unroll
-                    for (int sl = 0; sl < 4; ++sl) d1_mma(c[2 * sl + (kk & 1)], a[sl][kk], bx[sl * 4 + kk][0], bx[sl * 4 + kk][1]);
+                    for (int kk = 0; kk < 4; ++kk) {
+#pragma unroll
+                        for (int sl = 0; sl < 4; ++sl) {
+                            const int ks = h * 8 + (sl >> 1) * 4 + kk;          // k-step within the warp's 256 columns
+                            d1_mma(c[(sl & 1) * 4 + (sl >> 1) * 2 + (kk & 1)], a[sl][kk], bx[ks][0], bx[ks][1]);
+                        }
+                    }
                 }
+                const float gs0 = (c[0][0] + c[1][0]) + (c[2][0] + c[3][0]), gs2 = (c[0][2] + c[1][2]) + (c[2][2] + c[3][2]);
+                const float us0 = (c[4][0] + c[5][0]) + (c[6][0] + c[7][0]), us2 = (c[4][2] + c[5][2]) + (c[6][2] + c[7][2]);
+                g0 += gs0; g2 += gs2; u0 += us0; u2 += us2;
+                if (lane == 0) d1_release(&s.empty[slot], (gs0 + gs2) + (us0 + us2));
             }
-            const float v0 = ((c[0][0] + c[1][0]) + (c[2][0] + c[3][0])) + ((c[4][0] + c[5][0]) + (c[6][0] + c[7][0]));   // tile row gid (lanes with tig == 0)
-            const float v2 = ((c[0][2] + c[1][2]) + (c[2][2] + c[3][2])) + ((c[4][2] + c[5][2]) + (c[6][2] + c[7][2]));   // tile row gid + 8
             if (tig == 0) {
-                s.bpart[n][warp][gid] = v0;
-                s.bpart[n][warp][gid + 8] = v2;
+                s.bpart[2 * j][warp][gid] = g0;
+                s.bpart[2 * j][warp][gid + 8] = g2;
+                s.bpart[2 * j + 1][warp][gid] = u0;
+                s.bpart[2 * j + 1][warp][gid + 8] = u2;
             }
-            if (lane == 0) d1_release(&s.empty[slot], v0 + v2);
         }
         // the K-slices of every tile meet; SwiGLU; each activation is published as one tagged word (an atomic is
         // performed at L2 at once and nobody waits for it)
@@ -762,11 +790,11 @@ int launch_decode1(const DecodeParams& p, cudaStream_t stream) {
     static const bool cooperative = [] { const char* e = getenv("FKMOE_D1_COOPERATIVE"); return e && e[0] == '1'; }();
     const int smem = (int)decode1_smem_bytes();
     FK_CUDA_OK(cudaFuncSetAttribute(decode1_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem), "decode1 attr");
-    // [16 rows x 64 columns] boxes, 128-byte swizzle, cached per weight pointer
+    // gate_up: [2 halves x 16 rows x 64 columns] boxes; down: [16 rows x 64 columns] boxes; 128-byte swizzle, cached per weight pointer
     CUtensorMap gu{}, sgu{}, dn{}, sdn{};
-    const bool maps = weight_tensor_map(p.gate_up, (uint64_t)p.E * 2 * p.I, p.H, kD1Tile, &gu) &&
+    const bool maps = gate_up_pair_map(p.gate_up, (uint64_t)p.E, p.I, p.H, kD1Tile, &gu) &&
                       weight_tensor_map(p.down, (uint64_t)p.E * p.H, p.I, kD1Tile, &dn) &&
-                      weight_tensor_map(p.shared_gate_up ? p.shared_gate_up : p.gate_up, 2 * (uint64_t)p.I, p.H, kD1Tile, &sgu) &&
+                      gate_up_pair_map(p.shared_gate_up ? p.shared_gate_up : p.gate_up, 1, p.I, p.H, kD1Tile, &sgu) &&
                       weight_tensor_map(p.shared_down ? p.shared_down : p.down, (uint64_t)p.H, p.I, kD1Tile, &sdn);
     if (!maps) return FK_ERR_UNSUPPORTED;
     DecodeParams q = p;

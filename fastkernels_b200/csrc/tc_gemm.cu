@@ -319,6 +319,33 @@ bool weight_tensor_map(const void* base, uint64_t rows, uint64_t cols, uint32_t 
     return true;
 }
 
+// 3-D view of a bf16 gate_up tensor [experts][2][half_rows][cols] (gate rows, then up rows, per expert):
+// coordinates (column, row within the half, 2 * expert + half); box = [2 halves][box_rows][64 columns], 128-byte
+// swizzle.  One copy brings box_rows gate rows together with their up rows: half as many copies for the same bytes.
+bool gate_up_pair_map(const void* base, uint64_t experts, uint64_t half_rows, uint64_t cols, uint32_t box_rows, CUtensorMap* out) {
+    static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
+    static std::mutex mu;
+    MapKey key{base, experts * half_rows, cols, box_rows | (uint32_t)(half_rows << 8)};
+    std::lock_guard<std::mutex> lock(mu);
+    auto it = cache.find(key);
+    if (it != cache.end()) { *out = it->second; return true; }
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return false;
+    cuuint64_t dims[3] = {cols, half_rows, 2 * experts};
+    cuuint64_t strides[2] = {cols * 2, half_rows * cols * 2};
+    cuuint32_t box[3] = {64, box_rows, 2};
+    cuuint32_t elem[3] = {1, 1, 1};
+    CUtensorMap m;
+    CUresult r = fn(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, elem,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return false;
+    if (cache.size() > 4096) cache.clear();
+    cache.emplace(key, m);
+    *out = m;
+    return true;
+}
+
 bool tc_path_supported(const ExpertParams& p, int weight_dtype) {
     if (weight_dtype != FK_BF16) return false;
     if (p.H % 128 != 0 || p.I % 64 != 0 || p.H < 128 || p.I < 64) return false;

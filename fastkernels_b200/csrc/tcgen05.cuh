@@ -19,6 +19,12 @@ __device__ __forceinline__ void tma_load_2d(void* dst_smem, const CUtensorMap* m
         ::"r"(smem_u32(dst_smem)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(x), "r"(y)
         : "memory");
 }
+__device__ __forceinline__ void tma_load_3d(void* dst_smem, const CUtensorMap* map, int x, int y, int z, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+        ::"r"(smem_u32(dst_smem)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z)
+        : "memory");
+}
 __device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* map) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
 }
@@ -85,5 +91,6 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, float (&v)[16]) {
 // Cached tensor map of a row-major bf16 matrix [rows, cols] with boxes of [box_rows, 64 columns] and
 // 128-byte swizzle (tc_gemm.cu).  False when the driver's encoder is not available.
 bool weight_tensor_map(const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows, CUtensorMap* out);
+bool gate_up_pair_map(const void* base, uint64_t experts, uint64_t half_rows, uint64_t cols, uint32_t box_rows, CUtensorMap* out);
 
 }  // namespace fk

@@ -10,8 +10,14 @@ namespace fk {
 // After the call lane r < top_k holds the r-th winner in (my_i, my_w); my_w is renormalised over the winners.
 // Reference: probs = softmax(logits); top-k of probs; weights = selected / sum(selected) (qwen36_real.py:335-337).
 // Every router kernel of the library selects through this one function, so they agree bit for bit on equal logits.
-template <int EPL>
-__device__ __forceinline__ void topk_warp_regs(float (&v)[EPL], int E, int top_k, int lane, int& my_i, float& my_w) {
+struct TopkNoHook {
+    __device__ __forceinline__ void operator()(int, int) const {}
+};
+// on_round(r, expert) is called by every lane as soon as the r-th winner is known (a caller that can start work
+// per winner does not have to wait for the last round and the weights).
+template <int EPL, typename Hook = TopkNoHook>
+__device__ __forceinline__ void topk_warp_regs(float (&v)[EPL], int E, int top_k, int lane, int& my_i, float& my_w,
+                                               Hook on_round = Hook()) {
     // Selection works on the logits: softmax is monotonic, so the k largest probabilities are the k largest logits,
     // and the renormalised weight of a winner, p_i / sum of the winners' p_j, is exp(l_i - m) / sum of the winners'
     // exp(l_j - m): the normaliser of the full softmax cancels, and only k exponentials are needed instead of E.
@@ -40,6 +46,7 @@ __device__ __forceinline__ void topk_warp_regs(float (&v)[EPL], int E, int top_k
 #pragma unroll
         for (int j = 0; j < EPL; ++j) key[j] = ((unsigned)(j * 32 + lane) == bi) ? 0u : key[j];
         if (lane == r) { my_k = mk; my_i = (int)bi; }
+        on_round(r, (int)bi);
     }
     // lanes 0..k-1 hold the winners in descending order: lane 0 has the maximum
     const unsigned ku = (my_k & 0x80000000u) ? (my_k & 0x7fffffffu) : ~my_k;
