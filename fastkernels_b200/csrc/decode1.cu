@@ -69,6 +69,7 @@ constexpr int kD1Tile = 16;                      // MMA M: gate (or up) rows per
 constexpr int kD1MaxRouterRows = 4;              // router rows of a block, the shared-expert gate vector included
 constexpr int kD1MaxAtoms = 4;                   // gate_up atoms (16 gate/up pairs of one expert) per block
 constexpr int kD1ActElems = (FK_MAX_TOP_K + 1) * kD1I;
+constexpr int kD1IdValid = 1 << 30;              // flag bit of D1Smem::ids
 
 struct D1Smem {
     unsigned char stage[kD1Stages][kD1StageBytes];                // 1 KB aligned: the swizzle is a function of the address
@@ -92,16 +93,15 @@ struct D1Smem {
     uint64_t rdone;                               // every warp has written its router K-slice sums
     uint64_t ids_ready;                           // ids / wnorm written by the select warp
     float wnorm[FK_MAX_TOP_K];                    // renormalised routing weights
-    int ids[FK_MAX_TOP_K];
+    int ids[FK_MAX_TOP_K];                        // expert | kD1IdValid, written round by round while the select warp runs
     unsigned tag;                                 // this launch's tag for the published logits
-    int nids;                                     // ids[0 .. nids) are valid (grows while the select warp runs its rounds)
     int abort_flag;
 };
 
 // Static split of the work among the G blocks.
 //   router   block b takes rows b, b + G, ...; the last block also takes the shared-expert gate vector.
-//   gate_up  "atoms" of 16 gate/up pairs of one expert: first the shared expert's (I/16), then slot by slot the
-//            routed experts' (top_k * I/16), dealt evenly.  (The blocks meet between gate_up and down, so each of
+//   gate_up  "atoms" of 16 gate/up pairs of one expert: first the shared expert's (I/16), then the routed experts'
+//            (top_k * I/16, in the order of d1_routed_atom), dealt evenly.  (The blocks meet between gate_up and down, so each of
 //            the two phases has to be balanced by itself: giving the blocks without an output tile more atoms
 //            made everybody wait for them.)
 //   down     block b < H/16 owns output rows [16 b, 16 b + 16); the other blocks leave after gate_up.
@@ -132,6 +132,11 @@ __device__ __forceinline__ D1Plan make_plan(const DecodeParams& p, int b, int G)
     pl.nC = pl.tile >= 0 ? (p.top_k + 3) / 4 : 0;
     return pl;
 }
+
+// The q-th routed gate_up atom in dealing order -> its position slot * (I / 16) + pair16.  The winners arrive slot by
+// slot while the select warp runs its rounds, so consecutive atoms alternate between the first and the last slots:
+// every block then holds one atom it can start early, and all blocks finish the phase together.
+__device__ __forceinline__ int d1_routed_atom(int q, int nq) { return (q & 1) ? nq - 1 - (q >> 1) : (q >> 1); }
 
 __device__ __forceinline__ unsigned long long global_ns() {
     unsigned long long t;
@@ -209,6 +214,12 @@ __device__ __forceinline__ void box_mma(float (&c)[4], uint32_t box_addr, const 
     for (int kk = 0; kk < 4; ++kk) d1_mma(c, a[kk], bfrag[kk][0], bfrag[kk][1]);
 }
 
+// The expert of routing slot `sl` (the select warp publishes expert | kD1IdValid round by round; the rounds run while
+// the first slots' copies are already on their way).  0 if it never came: the launch then reports a time-out.
+__device__ __forceinline__ int d1_id(D1Smem& s, int sl) {
+    return *reinterpret_cast<volatile int*>(&s.ids[sl]) & (kD1IdValid - 1);
+}
+
 // Select warp: wait until every expert's logit of this launch has been published, then softmax + top-k on the
 // values the lanes already hold (lane L owns experts j*32 + L).  Writes ids / renormalised weights to shared memory
 // (and to the outputs from block 0).
@@ -247,14 +258,9 @@ __device__ __forceinline__ void poll_and_select(const DecodeParams& p, D1Smem& s
     // every winner is handed to the producer warp as soon as its round is over: the blocks whose gate_up tiles belong
     // to the first slots start their copies a microsecond before the last round and the weights are done
     topk_warp_regs<EPL>(v, p.E, p.top_k, lane, my_i, my_w, [&](int r, int expert) {
-        if (lane == 0) {
-            s.ids[r] = expert;
-            __threadfence_block();
-            *reinterpret_cast<volatile int*>(&s.nids) = r + 1;
-        }
+        if (lane == 0) *reinterpret_cast<volatile int*>(&s.ids[r]) = expert | kD1IdValid;     // id and "valid" in one word: no fence
     });
     if (lane < p.top_k) {
-        s.ids[lane] = my_i;
         s.wnorm[lane] = my_w;
         if (write_global) {
             p.topk_ids[lane] = my_i;
@@ -287,6 +293,7 @@ decode1_kernel(const __grid_constant__ CUtensorMap gu_map, const __grid_constant
             mbar_init(&s.full[lane], 1);
             mbar_init(&s.empty[lane], 1);
         }
+        if (lane < FK_MAX_TOP_K) s.ids[lane] = 0;
         if (lane == 0) {
             mbar_init(&s.xready, 2);              // the copies' transaction count + the tag
             mbar_init(&s.rrfull, 1);
@@ -294,7 +301,6 @@ decode1_kernel(const __grid_constant__ CUtensorMap gu_map, const __grid_constant
             mbar_init(&s.rdone, kD1Consumers);
             mbar_init(&s.ids_ready, 1);
             s.abort_flag = 0;
-            s.nids = 0;
             prefetch_tensormap(&gu_map);
             prefetch_tensormap(&dn_map);
         }
@@ -355,56 +361,64 @@ decode1_kernel(const __grid_constant__ CUtensorMap gu_map, const __grid_constant
                         __syncwarp();
                     }
                 }
-                if (lane < kD1Stages && it < total && ((it < nstatic) == (half == 0))) {
-                    const int n = it >> 3, w = it & 7;            // stage n of warp w
-                    const int slot = it % kD1Stages;
-                    const uint32_t par = (it / kD1Stages) & 1u;
-                    mbar_wait(&s.empty[slot], par ^ 1u, &s.abort_flag);      // passes at once on a slot's first lap
-                    unsigned char* dst = s.stage[slot];
-                    // the ids this stage's addresses depend on: one slot for a gate_up stage, all of them for a down stage
-                    int need = 0;
-                    if (n >= pl.nB) need = p.top_k;
-                    else if (pl.atom0 + (n >> 1) >= pl.shared_atoms) need = (pl.atom0 + (n >> 1) - pl.shared_atoms) / (I / kD1Tile) + 1;
-                    if (need > 0 && *reinterpret_cast<volatile int*>(&s.nids) < need) {
-                        // a short pause between polls: this warp shares its scheduler with warps that have work
-                        const long long t0 = clock64();
-                        while (*reinterpret_cast<volatile int*>(&s.nids) < need) {
-                            __nanosleep(20);
-                            if (clock64() - t0 > kWaitCycles) { s.abort_flag = 1; break; }
-                        }
-                    }
-                    __threadfence_block();                        // ids[] is read after the count that covers it
-                    if (it == nstatic) D1_TRACE(4);
-                    if (n < pl.nB) {
-                        // half n & 1 of atom n / 2: columns [256 w + 128 (n & 1), + 128) of the 16 gate rows and of
-                        // their up rows, as two copies of [2 halves x 16 rows x 64 columns] (4 KB each)
-                        const int g = pl.atom0 + (n >> 1);
-                        const CUtensorMap* map;
-                        int y, z;
-                        if (g < pl.shared_atoms) {
-                            map = &sgu_map;
-                            y = g * kD1Tile;
-                            z = 0;
-                        } else {
-                            const int q = g - pl.shared_atoms;
-                            map = &gu_map;
-                            y = (q % (I / kD1Tile)) * kD1Tile;
-                            z = 2 * s.ids[q / (I / kD1Tile)];
-                        }
-                        mbar_expect_tx(&s.full[slot], kD1StageBytes);
-#pragma unroll
-                        for (int op = 0; op < 2; ++op)
-                            tma_load_3d(dst + op * 4096, map, w * 256 + (n & 1) * 128 + op * 64, y, z, &s.full[slot]);
-                    } else {
-                        // down tiles of four slots, columns [64 w, 64 w + 64) of the block's 16 output rows
-                        const int c = n - pl.nB;
-                        const int nu = min(4, p.top_k - c * 4);
-                        mbar_expect_tx(&s.full[slot], (uint32_t)nu * 2048u);
-                        for (int u = 0; u < nu; ++u)
-                            tma_load_2d(dst + u * 2048, &dn_map, w * 64, s.ids[c * 4 + u] * H + pl.tile * kD1Tile, &s.full[slot]);
+                // Every lane polls its own slot and issues the moment the slot is free and the ids its addresses need
+                // are known: at the turn from gate_up to down the copies of a freed slot must not wait for the
+                // slowest slot of the lap (nor for a sleeping poll loop: that cost a microsecond there).
+                bool pending = lane < kD1Stages && it < total && ((it < nstatic) == (half == 0));
+                const int n = it >> 3, w = it & 7;                // stage n of warp w
+                const int slot = it % kD1Stages;
+                const uint32_t par = (it / kD1Stages) & 1u;
+                int q = -1, id_last = -1;                         // routed atom; the last routing slot whose id is needed
+                if (pending) {
+                    if (n >= pl.nB) {
+                        id_last = min((n - pl.nB) * 4 + 4, p.top_k) - 1;
+                    } else if (pl.atom0 + (n >> 1) >= pl.shared_atoms) {
+                        q = d1_routed_atom(pl.atom0 + (n >> 1) - pl.shared_atoms, p.top_k * (I / kD1Tile));
+                        id_last = q / (I / kD1Tile);
                     }
                 }
-                __syncwarp();
+                const long long t0 = clock64();
+                while (__any_sync(kFull, pending)) {
+                    bool go = false;
+                    if (pending) {
+                        go = mbar_try_wait(&s.empty[slot], par ^ 1u);          // passes at once on a slot's first lap
+                        if (go && id_last >= 0) go = (*reinterpret_cast<volatile int*>(&s.ids[id_last]) & kD1IdValid) != 0;
+                        if (!go && clock64() - t0 > kWaitCycles) { s.abort_flag = 1; go = true; }
+                    }
+                    if (go) {
+                        pending = false;
+                        unsigned char* dst = s.stage[slot];
+                        if (n < pl.nB) {
+                            // half n & 1 of atom n / 2: columns [256 w + 128 (n & 1), + 128) of the 16 gate rows and
+                            // of their up rows, as two copies of [2 halves x 16 rows x 64 columns] (4 KB each)
+                            const CUtensorMap* map;
+                            int y, z;
+                            if (q < 0) {
+                                map = &sgu_map;
+                                y = (pl.atom0 + (n >> 1)) * kD1Tile;
+                                z = 0;
+                            } else {
+                                map = &gu_map;
+                                y = (q % (I / kD1Tile)) * kD1Tile;
+                                z = 2 * d1_id(s, id_last);
+                            }
+                            mbar_expect_tx(&s.full[slot], kD1StageBytes);
+#pragma unroll
+                            for (int op = 0; op < 2; ++op)
+                                tma_load_3d(dst + op * 4096, map, w * 256 + (n & 1) * 128 + op * 64, y, z, &s.full[slot]);
+                        } else {
+                            // down tiles of four slots, columns [64 w, 64 w + 64) of the block's 16 output rows
+                            const int c = n - pl.nB;
+                            const int nu = min(4, p.top_k - c * 4);
+                            mbar_expect_tx(&s.full[slot], (uint32_t)nu * 2048u);
+                            for (int u = 0; u < nu; ++u)
+                                tma_load_2d(dst + u * 2048, &dn_map, w * 64, d1_id(s, c * 4 + u) * H + pl.tile * kD1Tile, &s.full[slot]);
+                        }
+                        if (it == nstatic) D1_TRACE(4);
+                    } else if (pending) {
+                        __nanosleep(20);          // this warp shares its scheduler with warps that have work
+                    }
+                }
             }
         }
         if (lane == 0) D1_TRACE(14);
@@ -596,7 +610,7 @@ decode1_kernel(const __grid_constant__ CUtensorMap gu_map, const __grid_constant
             const int g = pl.atom0 + j;
             int idx;
             if (g < pl.shared_atoms) idx = shared_slot * I + g * kD1Tile + r;
-            else idx = (g - pl.shared_atoms) * kD1Tile + r;                   // slot * I + pair
+            else idx = d1_routed_atom(g - pl.shared_atoms, p.top_k * (I / kD1Tile)) * kD1Tile + r;     // slot * I + pair
             const __nv_bfloat16 hi = __float2bfloat16_rn(act);
             const __nv_bfloat16 lo = __float2bfloat16_rn(act - __bfloat162float(hi));
             const unsigned payload = ((unsigned)__bfloat16_as_ushort(hi) << 16) | (unsigned)__bfloat16_as_ushort(lo);
