@@ -348,9 +348,13 @@ def run_single(args):
     # traffic grows in proportion to the experts touched.
     if len(stage_ms) == 1:
         # the step is this one kernel: its duration is the graph-replayed step (the stage events add their own gap)
-        dom_kernel, dom_bytes, traffic_ratio = ("decode1_kernel (whole layer, one token, one launch)", layer_bytes,
-                                                NCU_TRAFFIC_PER_BYTE["decode1"])
-        traffic_file = "profiles/decode1_fused_b1.md"
+        if B == 1:
+            dom_kernel, traffic_ratio, traffic_file = ("decode1_kernel (whole layer, one token, one launch)",
+                                                       NCU_TRAFFIC_PER_BYTE["decode1"], "profiles/decode1_fused_b1.md")
+        else:
+            dom_kernel, traffic_ratio, traffic_file = ("decode_few_kernel (whole layer, two to four tokens, one launch)",
+                                                       NCU_TRAFFIC_PER_BYTE.get("decode_few"), "profiles/decode_few_b4.md")
+        dom_bytes = layer_bytes
         dom_ms = ms
     elif B <= 96:
         dom_kernel, dom_bytes, traffic_ratio = ("stream_gemv_kernel<8,true,false> (gate_up GEMV + SwiGLU, "
@@ -488,7 +492,7 @@ def run_single(args):
 
 # DRAM bytes (read + write) per algorithmic byte of the dominant kernel, from the ncu captures summarised in
 # profiles/stream_gemv_b32.md, profiles/tc_grouped_gemm_b256.md and profiles/decode1_fused_b1.md.
-NCU_TRAFFIC_PER_BYTE = {"stream_gate_up": 1.011, "tc_gate_up": 1.016, "decode1": 1.007}
+NCU_TRAFFIC_PER_BYTE = {"stream_gate_up": 1.010, "tc_gate_up": 1.015, "decode1": 1.006}      # profiles/*.md; none yet for decode_few
 
 
 def main():

@@ -344,7 +344,8 @@ static int moe_layer_impl(const fk_moe_call* c, void* stream, const LayerExtras&
     rp.T = c->dims.tokens; rp.H = c->dims.hidden; rp.E = c->dims.experts; rp.top_k = c->dims.top_k;
     rp.eps = c->eps; rp.norm_offset = c->norm_offset;
     stage_mark();   // start
-    if (c->dims.tokens == 1 && !(c->flags & (FK_FLAG_NO_FUSED_DECODE | FK_FLAG_FORCE_GENERIC))) {
+    if (c->dims.tokens <= 4 && !(c->flags & (FK_FLAG_NO_FUSED_DECODE | FK_FLAG_FORCE_GENERIC)) &&
+        (c->dims.tokens == 1 || x.resid_in == nullptr)) {
         DecodeParams dp{};
         dp.hidden = c->hidden; dp.hidden_dtype = c->hidden_dtype;
         dp.norm_weight = c->norm_weight; dp.router_weight = c->router_weight; dp.router_bias = c->router_bias;
@@ -364,9 +365,15 @@ static int moe_layer_impl(const fk_moe_call* c, void* stream, const LayerExtras&
         const bool trace_fits = (size_t)sm_count() * 256 <= w.xg - w.y;
         dp.trace = ((c->flags & FK_FLAG_TRACE) && trace_fits) ? at<unsigned long long>(c->workspace, w.y) : nullptr;
         dp.H = c->dims.hidden; dp.E = c->dims.experts; dp.I = c->dims.intermediate; dp.top_k = c->dims.top_k;
+        dp.T = c->dims.tokens;
         dp.eps = c->eps; dp.norm_offset = c->norm_offset;
-        if (decode1_supported(dp, c->weight_dtype)) {
+        if (dp.T == 1 && decode1_supported(dp, c->weight_dtype)) {
             st = launch_decode1(dp, s);
+            stage_mark();   // end of the fused kernel
+            return st;
+        }
+        if (dp.T > 1 && decode_few_supported(dp, c->weight_dtype)) {
+            st = launch_decode_few(dp, s);
             stage_mark();   // end of the fused kernel
             return st;
         }

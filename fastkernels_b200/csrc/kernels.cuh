@@ -139,6 +139,7 @@ struct DecodeParams {
     int* error_word;
     unsigned long long* trace;    // optional [blocks][16] nanosecond timestamps of the phase boundaries
     int H, E, I, top_k;
+    int T;                        // tokens: 1 for the single-token kernel, 2..4 for decode_few (all arrays then have T rows)
     float eps, norm_offset;
     long long wait_cycles;        // limit of every wait on another block (0: the library's current limit)
 
@@ -151,6 +152,9 @@ struct DecodeParams {
 };
 bool decode1_supported(const DecodeParams& p, int weight_dtype);
 int launch_decode1(const DecodeParams& p, cudaStream_t stream);
+// the same layer call for two to four tokens in one launch (decode_few.cu)
+bool decode_few_supported(const DecodeParams& p, int weight_dtype);
+int launch_decode_few(const DecodeParams& p, cudaStream_t stream);
 int sm_count();
 // Limit, in SM clock cycles, of device-side waits on other blocks or ranks (fk_set_wait_limit_cycles; about a second by default)
 long long wait_limit_cycles();

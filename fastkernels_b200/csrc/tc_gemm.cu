@@ -346,6 +346,33 @@ bool gate_up_pair_map(const void* base, uint64_t experts, uint64_t half_rows, ui
     return true;
 }
 
+// 3-D view of a row-major bf16 matrix [rows][cols] as (64 columns, column group, row): box = [box_rows][2 groups][64
+// columns], 128-byte swizzle.  One copy brings box_rows x 128 columns; in shared memory row r holds its two 128-byte
+// groups one after the other (line 2 r + g), and the swizzle goes by that line number.
+bool column_pair_map(const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows, CUtensorMap* out) {
+    static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
+    static std::mutex mu;
+    MapKey key{base, rows, cols, box_rows};
+    std::lock_guard<std::mutex> lock(mu);
+    auto it = cache.find(key);
+    if (it != cache.end()) { *out = it->second; return true; }
+    EncodeTiledFn fn = encode_fn();
+    if (!fn || cols % 128 != 0) return false;
+    cuuint64_t dims[3] = {64, cols / 64, rows};
+    cuuint64_t strides[2] = {128, cols * 2};
+    cuuint32_t box[3] = {64, 2, box_rows};
+    cuuint32_t elem[3] = {1, 1, 1};
+    CUtensorMap m;
+    CUresult r = fn(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, elem,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return false;
+    if (cache.size() > 4096) cache.clear();
+    cache.emplace(key, m);
+    *out = m;
+    return true;
+}
+
 bool tc_path_supported(const ExpertParams& p, int weight_dtype) {
     if (weight_dtype != FK_BF16) return false;
     if (p.H % 128 != 0 || p.I % 64 != 0 || p.H < 128 || p.I < 64) return false;

@@ -91,6 +91,7 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, float (&v)[16]) {
 // Cached tensor map of a row-major bf16 matrix [rows, cols] with boxes of [box_rows, 64 columns] and
 // 128-byte swizzle (tc_gemm.cu).  False when the driver's encoder is not available.
 bool weight_tensor_map(const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows, CUtensorMap* out);
+bool column_pair_map(const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows, CUtensorMap* out);
 bool gate_up_pair_map(const void* base, uint64_t experts, uint64_t half_rows, uint64_t cols, uint32_t box_rows, CUtensorMap* out);
 
 }  // namespace fk

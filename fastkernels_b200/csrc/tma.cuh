@@ -38,6 +38,19 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
+// Non-blocking form: try_wait may suspend the thread for a hardware-chosen time when the phase is not complete,
+// which a warp whose lanes watch different barriers pays on every poll; test_wait only looks.
+__device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
 
 // Returns false on time-out (and raises *abort_flag, a shared-memory word of the block).
 // Waiting threads back off with nanosleep: a tight poll of a shared-memory barrier by whole warps

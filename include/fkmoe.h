@@ -57,8 +57,8 @@ typedef struct fk_moe_dims {
 #define FK_FLAG_FORCE_GENERIC 1u   /* use the shape-agnostic kernels even where a fast path exists */
 #define FK_FLAG_FORCE_GEMV 2u      /* never use the tensor-core grouped GEMM */
 #define FK_FLAG_FORCE_TENSOR 4u    /* use the tensor-core grouped GEMM whenever the shape allows */
-#define FK_FLAG_NO_FUSED_DECODE 8u /* T==1: run the staged kernels instead of the fused single-token kernel */
-#define FK_FLAG_TRACE 64u          /* T==1 fused kernel: write per-block phase timestamps at the start of the workspace's y
+#define FK_FLAG_NO_FUSED_DECODE 8u /* T<=4: run the staged kernels instead of the single-launch kernels (one token; two to four) */
+#define FK_FLAG_TRACE 64u          /* T<=4 single-launch kernels: write per-block phase timestamps at the start of the workspace's y
                                       region, u64 [blocks][32] (fk_moe_trace_offset() gives the offset).  Nanoseconds of
                                       the global timer in slots 0 entry, 1 constant copies issued, 20 the kernel before
                                       has completed, 2 token in shared memory, 3 this block's logits published, 18 all
@@ -66,6 +66,8 @@ typedef struct fk_moe_dims {
                                       landed, 5 this block's activations published, 12 the activations this block needs
                                       are in shared memory, 14 last copy issued, 13 down tiles done, 15 output stored,
                                       7 exit (0 where a block skips the step); SM cycle counter in 8 (entry) and 9 (exit).
+                                      Two to four tokens: 19 is "distinct experts listed", and there are 25 every block has
+                                      published, 26 / 27 first down stage landed / done; no 1, 8, 9.
                                       Ignored when the record (blocks * 256 bytes) does not fit the y region. */
 #define FK_FLAG_SKIP_FOREIGN 16u   /* ids outside [expert_base, expert_base+E) are skipped instead of clamped */
 #define FK_FLAG_WIDE_PASSES 128u   /* tcgen05 path: 128 tokens per pass and two weight tiles per unit instead of 64 and one */

@@ -25,11 +25,13 @@ def _status(lib, ws):
     return st, code.value
 
 
-def test_single_token_kernel_wait_runs_out_and_is_reported():
+@pytest.mark.parametrize("tokens", [1, 4])
+def test_single_launch_kernels_wait_runs_out_and_is_reported(tokens):
+    """tokens = 1: the single-token kernel; tokens = 4: the kernel for two to four tokens."""
     lib = _lib.load()
     w = make_moe_weights(41, REAL, dtype=torch.bfloat16, device="cuda", bias_std=0.5)
-    x = make_hidden(41, 1, REAL, dtype=torch.bfloat16, device="cuda")
-    plan = MoEDecodePlan(w, 1)
+    x = make_hidden(41, tokens, REAL, dtype=torch.bfloat16, device="cuda")
+    plan = MoEDecodePlan(w, tokens)
     good = [t.clone() for t in plan.run(x)]
     torch.cuda.synchronize()
     assert _status(lib, plan.workspace) == (FK_OK, 0)
@@ -38,7 +40,7 @@ def test_single_token_kernel_wait_runs_out_and_is_reported():
         plan.run(x)                                              # returns by itself; the output is undefined
         torch.cuda.synchronize()
         st, code = _status(lib, plan.workspace)
-        assert st == FK_ERR_TIMEOUT and code == 2                # 2: the single-token kernel
+        assert st == FK_ERR_TIMEOUT and code == 2                # 2: a single-launch decode kernel
         assert _status(lib, plan.workspace) == (FK_OK, 0)        # reading the status clears it
     finally:
         assert lib.fk_set_wait_limit_cycles(0) == FK_OK          # back to the default (about a second)

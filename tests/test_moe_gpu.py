@@ -323,7 +323,7 @@ def test_full_layer_single_token_api(real_bf16):
 def test_full_layer_generic_kernels_agree(real_bf16, flags):
     w = real_bf16
     hidden = make_hidden(9, 3, REAL, dtype=torch.bfloat16, device="cuda")
-    fast, _, ids_f, _ = triton_qwen36_batched_moe_decode(hidden, *w.tuple())
+    fast, _, ids_f, _ = triton_qwen36_batched_moe_decode(hidden, *w.tuple(), flags=_lib.FLAG_NO_FUSED_DECODE)
     slow, _, ids_s, _ = triton_qwen36_batched_moe_decode(hidden, *w.tuple(), flags=flags)
     assert torch.equal(ids_f, ids_s)
     torch.testing.assert_close(fast, slow, atol=2e-5, rtol=1e-4)
@@ -350,6 +350,81 @@ def test_single_token_fused_kernel_matches_staged_path_and_oracle(real_bf16_bias
         check_output(fused[1], ref.output, torch.bfloat16)
         again = triton_qwen36_batched_moe_layer_decode(hidden, *args, router_bias=rb)
         assert torch.equal(again[1], fused[1])                        # bitwise repeatable
+
+
+@pytest.mark.parametrize("tokens", [2, 3, 4])
+@pytest.mark.parametrize("gated,bias", [(True, True), (False, False)])
+def test_few_token_fused_kernel_matches_staged_path_and_oracle(real_bf16_biased, tokens, gated, bias):
+    """Two to four tokens take one launch (decode_few.cu): routing bit-exact against the staged kernels, the update
+    within the bf16-activation tolerance of both the staged path and the oracle, bitwise repeatable."""
+    w = real_bf16_biased
+    args = list(w.tuple())
+    if not gated:
+        args[6] = None
+    rb = w.router_bias if bias else None
+    for seed in range(3):
+        hidden = make_hidden(700 + 10 * tokens + seed, tokens, REAL, dtype=torch.bfloat16, device="cuda")
+        fused = triton_qwen36_batched_moe_layer_decode(hidden, *args, router_bias=rb)
+        staged = triton_qwen36_batched_moe_layer_decode(hidden, *args, router_bias=rb, flags=_lib.FLAG_NO_FUSED_DECODE)
+        assert torch.equal(fused[3], staged[3])                       # ids
+        torch.testing.assert_close(fused[2], staged[2], atol=1e-5, rtol=1e-5)   # logits
+        torch.testing.assert_close(fused[4], staged[4], atol=1e-6, rtol=1e-5)   # weights
+        assert O.max_abs(fused[1].cpu(), staged[1].cpu()) <= 2e-2 and O.rel_l2(fused[1].cpu(), staged[1].cpu()) <= 5e-3
+        torch.testing.assert_close(fused[0], hidden.float() + fused[1], atol=0, rtol=0)
+        ref = oracle_layer(hidden, MoEWeights(*args, rb), 8)
+        check_routing(fused[2], fused[3], fused[4], ref, torch.bfloat16)
+        check_output_where_ids_agree(fused[1], fused[3], ref.topk_ids, ref.output, torch.bfloat16, what=f"few-token kernel, {tokens} tokens")
+        again = triton_qwen36_batched_moe_layer_decode(hidden, *args, router_bias=rb)
+        assert torch.equal(again[1], fused[1]) and torch.equal(again[3], fused[3])      # bitwise repeatable
+
+
+def test_few_token_fused_kernel_tokens_sharing_experts():
+    """Experts chosen by several tokens are streamed once and multiplied for all of them: identical tokens share all
+    eight experts, hot experts are shared by most tokens, and a token's result must not depend on its neighbours."""
+    w = make_moe_weights(55, REAL, dtype=torch.bfloat16, device="cuda", bias_std=0.5, hot_experts=HOT_EXPERT_IDS)
+    x = make_hidden(56, 4, REAL, dtype=torch.bfloat16, device="cuda")
+    same = x[:1].repeat(4, 1).contiguous()
+    out, _, ids, _ = triton_qwen36_batched_moe_decode(same, *w.tuple(), router_bias=w.router_bias)
+    assert all(torch.equal(ids[0], ids[t]) for t in range(1, 4))
+    assert all(torch.equal(out[0], out[t]) for t in range(1, 4)), "identical tokens must give identical rows"
+    out, logits, ids, weights = triton_qwen36_batched_moe_decode(x, *w.tuple(), router_bias=w.router_bias)
+    assert len(set(ids.flatten().tolist())) < 32, "the case needs experts shared between tokens"
+    ref = oracle_layer(x, w, 8)
+    check_routing(logits, ids, weights, ref, torch.bfloat16)
+    check_output_where_ids_agree(out, ids, ref.topk_ids, ref.output, torch.bfloat16, what="few-token kernel, shared experts")
+    # a token's row does not depend on which tokens travel with it
+    pair, _, ids2, _ = triton_qwen36_batched_moe_decode(x[1:3].contiguous(), *w.tuple(), router_bias=w.router_bias)
+    assert torch.equal(ids2, ids[1:3])
+    assert O.max_abs(pair.cpu(), out[1:3].cpu()) <= 1e-4
+
+
+def test_few_token_fused_kernel_sees_fresh_data_every_call(real_bf16_biased):
+    """Alternating two batches on one workspace: a stale logit or activation word of the previous call (same address,
+    older tag) would show up as a mismatch."""
+    from fastkernels_b200.plan import MoEDecodePlan
+    w = real_bf16_biased
+    plan = MoEDecodePlan(w, 4)
+    xa = make_hidden(911, 4, REAL, dtype=torch.bfloat16, device="cuda")
+    xb = (xa.flip(0) * -1.3).to(torch.bfloat16)
+    refs = []
+    for x in (xa, xb):
+        out, logits, ids, weights = plan.run(x)
+        torch.cuda.synchronize()
+        refs.append((out.clone(), ids.clone()))
+    assert not torch.equal(refs[0][1], refs[1][1])
+    for i in range(300):
+        out, _, ids, _ = plan.run(xa if i % 2 == 0 else xb)
+        if i % 20 >= 18:
+            torch.cuda.synchronize()
+            assert torch.equal(out, refs[i % 2][0]) and torch.equal(ids, refs[i % 2][1]), f"call {i}"
+    # and interleaved with the single-token kernel on the same weights (the two share nothing but the GPU)
+    one = MoEDecodePlan(w, 1)
+    o1 = one.run(xa[:1].contiguous())[0].clone()
+    for i in range(20):
+        plan.run(xb)
+        o = one.run(xa[:1].contiguous())[0]
+    torch.cuda.synchronize()
+    assert torch.equal(o, o1)
 
 
 def test_single_token_fused_kernel_fp32_hidden_and_many_calls(real_bf16):
