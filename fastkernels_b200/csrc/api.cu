@@ -366,6 +366,8 @@ static int moe_layer_impl(const fk_moe_call* c, void* stream, const LayerExtras&
         dp.trace = ((c->flags & FK_FLAG_TRACE) && trace_fits) ? at<unsigned long long>(c->workspace, w.y) : nullptr;
         dp.H = c->dims.hidden; dp.E = c->dims.experts; dp.I = c->dims.intermediate; dp.top_k = c->dims.top_k;
         dp.T = c->dims.tokens;
+        // the few-token kernel's activation rows: in the y region (unused on this path), behind the trace record
+        dp.act_rows = (w.xg - w.y >= (size_t)65536 + 36 * 1024 * 2) ? at<uint32_t>(c->workspace, w.y) + 16384 : nullptr;
         dp.eps = c->eps; dp.norm_offset = c->norm_offset;
         if (dp.T == 1 && decode1_supported(dp, c->weight_dtype)) {
             st = launch_decode1(dp, s);

@@ -13,7 +13,10 @@
 //     blocks, and one [16 x 512] down tile to every block that owns 16 output rows;
 //   * activations travel as plain bf16 (what the grouped-GEMM path of larger batches does too) and are fetched with
 //     bulk copies once a counter says that every block has published; the down products are weighted and summed
-//     per token in registers, expert by expert in list order, so the result does not depend on scheduling.
+//     per token in registers, expert by expert in list order, so the result does not depend on scheduling;
+//   * the experts are worked off in two halves with a counter each, so that the exchange of the first half's
+//     activations runs under the second half's gate_up stream and the exchange of the second half's under the
+//     first half's down tiles: neither exchange (a fence, a count, a 16 KB copy: 3 us) shows in the run time.
 //
 // The staged path (router, permutation, gate_up, down, combine: five launches) needs 49 us for four tokens, of which
 // the 171 MB of weights account for 26 us at the copy bandwidth; the rest is the latency of five dependent launches.
@@ -40,7 +43,7 @@ static_assert(kFH == kFConsumers * 256 && kFI == kFConsumers * 64, "one K-slice 
 constexpr int kFThreads = (kFConsumers + 1 + kFMaxT) * 32;   // consumers + producer warp + one select warp per token
 constexpr int kFTile = 16;                       // MMA M: gate (or up) rows per stage, output rows per block
 constexpr int kFMaxRouterRows = 4;               // router rows of a block, the shared-expert gate vector included
-constexpr int kFMaxAtoms = 8;                    // gate_up atoms per block (the shared expert's one included)
+constexpr int kFMaxAtoms = 6;                    // gate_up atoms per block and half (the shared expert's one included)
 constexpr int kFUnits = kFMaxT * FK_MAX_TOP_K;   // (token, routing slot) pairs = the most distinct experts
 constexpr int kFActRows = kFUnits + kFMaxT;      // activation rows of I values: (token, slot), then the shared expert per token
 constexpr int kFAtomsPerExpert = kFI / kFTile;   // 32
@@ -57,7 +60,7 @@ struct FSmem {
         } in;                                                     // read until the tokens sit in registers (start of gate_up)
         unsigned char act[kFActRows * kFI * 2];                   // bf16 activations of all rows (written in the down phase)
     } u;
-    float bpart[2 * kFMaxAtoms][kFConsumers][kFTile][kFMaxT];     // gate_up: K-slice sums per atom half (gate, up), row, token
+    float bpart[2 * kFMaxAtoms][kFConsumers][kFTile][kFMaxT];     // gate_up: K-slice sums per atom (gate, up), row, token; reused by the second half
     float cpart[2][kFConsumers][kFTile][kFMaxT];                  // down: K-slice sums, [0] routed (weighted), [1] shared expert
     float rpart[kFMaxRouterRows + 1][kFMaxT][kFConsumers];        // router rows: K-slice sums; last row: sum of squares
     uint64_t full[kFStages];
@@ -68,14 +71,17 @@ struct FSmem {
     uint64_t rdone;                               // every warp has written its router K-slice sums
     uint64_t sel_done;                            // every select warp has written its token's ids and weights
     uint64_t plan_ready;                          // the distinct-expert list is complete
-    uint64_t actfull;                             // all activation rows have landed in shared memory
+    uint64_t actfull[2];                          // the activation rows of a half have landed in shared memory
+    uint64_t pubbar[2];                           // the consumers have stored this block's activations of a half
     float wnorm[kFMaxT][FK_MAX_TOP_K];            // renormalised routing weights
     int ids[kFMaxT][FK_MAX_TOP_K];
     int uexp[kFUnits];                            // distinct experts in order of first appearance in (token, slot) order
     float uw[kFUnits][kFMaxT];                    // routing weight token t gives distinct expert u (0: not chosen)
-    int urow[kFUnits][kFMaxT];                    // activation row t * top_k + slot of that choice, or -1
+    int urow[kFUnits][kFMaxT];                    // activation row of that choice (rows are numbered expert by expert in list
+                                                  // order, so a half's rows are contiguous), or -1
     float gate[kFMaxT];                           // sigmoid gate of the shared expert per token
     int U;                                        // number of distinct experts
+    int rows0, rows;                              // activation rows of the first half, of both
     unsigned tag;                                 // this launch's tag for the exchanged words
     unsigned done_target;                         // value of the "activations published" counter once every block has added to it
     int abort_flag;
@@ -97,14 +103,34 @@ __device__ __forceinline__ FPlan few_static_plan(const DecodeParams& p, int b, i
     pl.tile = b < kFH / kFTile ? b : -1;
     return pl;
 }
-// Routed gate_up atoms [first, first + count) of block b out of U * 32.  The blocks that hold a shared-expert atom
-// come last in the dealing order, so the remainder goes to the others first.
-__device__ __forceinline__ void few_routed_atoms(int U, int b, int G, bool has_shared, int& first, int& count) {
-    const int total = U * kFAtomsPerExpert;
-    const int rb = has_shared ? (b + G - kFAtomsPerExpert) % G : b;
+// The distinct experts are worked off in two halves (the first one a multiple of four experts), each with its own
+// "published" counter: while the second half's gate_up streams, the first half's activations are already exchanged,
+// and while the second half's are exchanged, the first half's down tiles are multiplied.  Within a half the 32 atoms
+// per expert are dealt evenly over all blocks; the remainders of the two halves go to different blocks, and the
+// blocks that hold a shared-expert atom come last.
+struct FDyn {
+    int U, U0;              // distinct experts; those of the first half
+    int first0, cnt0;       // this block's atoms of the first half: [first0, first0 + cnt0) out of U0 * 32
+    int first1, cnt1;       // ... of the second half, out of (U - U0) * 32, counted from atom U0 * 32
+};
+__device__ __forceinline__ void few_deal(int total, int b, int G, int rot, int& first, int& count) {
+    const int rb = (b + G - rot % G) % G;
     const int q = total / G, r = total - q * G;
     first = rb * q + min(rb, r);
     count = q + (rb < r ? 1 : 0);
+}
+__device__ __forceinline__ FDyn few_dynamic_plan(int U, int b, int G, bool has_shared) {
+    FDyn d;
+    d.U = min(max(U, 0), kFUnits);
+    d.U0 = min(d.U, 4 * ((d.U + 7) / 8));
+    const int rot0 = has_shared ? kFAtomsPerExpert : 0;
+    few_deal(d.U0 * kFAtomsPerExpert, b, G, rot0, d.first0, d.cnt0);
+    few_deal((d.U - d.U0) * kFAtomsPerExpert, b, G, rot0 + (d.U0 * kFAtomsPerExpert) % G, d.first1, d.cnt1);
+    return d;
+}
+// global atom (expert * 32 + atom within the expert) of the block's k-th routed atom
+__device__ __forceinline__ int few_atom(const FDyn& d, int k) {
+    return k < d.cnt0 ? d.first0 + k : d.U0 * kFAtomsPerExpert + d.first1 + (k - d.cnt0);
 }
 
 #define FEW_TRACE(slot) do { if (p.trace) p.trace[(size_t)blockIdx.x * 32 + (slot)] = global_ns(); } while (0)
@@ -176,11 +202,24 @@ __device__ __forceinline__ void few_build_plan(const DecodeParams& p, FSmem& s, 
     const int u_of_leader = __popc(leaders & ((1u << lane) - 1u));
     const int u = __shfl_sync(kFull, u_of_leader, __ffs(same) - 1);   // the list position of this lane's expert
     if (leader) s.uexp[u] = id;
+    // activation rows, expert by expert in list order, tokens ascending within an expert
+    const int members = __popc(same);
+    int base = leader ? members : 0;                                  // exclusive prefix sum over the leaders, in lane order
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+        const int v = __shfl_up_sync(kFull, base, off);
+        if (lane >= off) base += v;
+    }
+    base -= leader ? members : 0;
+    const int row = __shfl_sync(kFull, base, __ffs(same) - 1) + __popc(same & ((1u << lane) - 1u));
     if (valid) {
         s.uw[u][t] = s.wnorm[t][sl];                                  // a token chooses an expert at most once
-        s.urow[u][t] = t * p.top_k + sl;
+        s.urow[u][t] = row;
     }
-    if (lane == 0) s.U = __popc(leaders);
+    const int U = __popc(leaders);
+    const int U0 = min(U, 4 * ((U + 7) / 8));
+    const unsigned in_first = __ballot_sync(kFull, valid && u < U0);
+    if (lane == 0) { s.U = U; s.rows0 = __popc(in_first); s.rows = n; }
     __syncwarp();
 }
 
@@ -213,7 +252,10 @@ decode_few_kernel(const __grid_constant__ CUtensorMap gu_map, const __grid_const
             mbar_init(&s.rdone, kFConsumers);
             mbar_init(&s.sel_done, (uint32_t)T);
             mbar_init(&s.plan_ready, 1);
-            mbar_init(&s.actfull, 1);
+            mbar_init(&s.actfull[0], 1);
+            mbar_init(&s.actfull[1], 1);
+            mbar_init(&s.pubbar[0], 1);
+            mbar_init(&s.pubbar[1], 1);
             s.abort_flag = 0;
             prefetch_tensormap(&gu_map);
             prefetch_tensormap(&dn_map);
@@ -240,7 +282,8 @@ decode_few_kernel(const __grid_constant__ CUtensorMap gu_map, const __grid_const
         // gate_up stages (two per atom: the shared expert's atom, if the block has one, is known from the start), then
         // the down stages (four distinct experts each) of a block that owns output rows.
         const int nstatic = pl.shared_atom >= 0 ? 2 * kFConsumers : 0;
-        int total = nstatic, nB = nstatic / kFConsumers, first = 0, natoms_r = 0, U = 0;
+        int total = nstatic, nB = nstatic / kFConsumers;
+        FDyn dyn{};
         bool token_issued = false, planned = false;
 #pragma unroll 1
         for (int base = 0; base < total || !planned; base += kFStages) {
@@ -258,8 +301,9 @@ decode_few_kernel(const __grid_constant__ CUtensorMap gu_map, const __grid_const
                                 bulk_load(s.u.in.xraw[t], reinterpret_cast<const unsigned char*>(p.hidden) + (size_t)t * H * 2, (uint32_t)H * 2u, &s.xready);
                             bulk_load(s.u.in.nw, p.norm_weight, (uint32_t)H * 2u, &s.xready);
                             s.tag = ld_relaxed_u32(p.bar + 3) + 1u;
-                            // word 1 counts the finished launches of this kernel on this workspace, word 0 the blocks
-                            // that have published their activations (it is never reset: G more per launch)
+                            // word 1 counts the finished launches of this kernel on this workspace, words 0 and 2 the
+                            // blocks that have published the activations of the first / second half of the experts
+                            // (never reset: G more per launch)
                             s.done_target = (ld_relaxed_u32(p.bar + 1) + 1u) * (unsigned)G;
                             mbar_arrive(&s.xready);
                         }
@@ -276,10 +320,9 @@ decode_few_kernel(const __grid_constant__ CUtensorMap gu_map, const __grid_const
                             FEW_TRACE(4);
                         }
                         __syncwarp();
-                        U = min(max(*reinterpret_cast<volatile int*>(&s.U), 0), kFUnits);
-                        few_routed_atoms(U, blk, G, has_shared, first, natoms_r);
-                        nB = nstatic / kFConsumers + 2 * natoms_r;
-                        const int nC = pl.tile >= 0 ? (U + 3) / 4 : 0;
+                        dyn = few_dynamic_plan(*reinterpret_cast<volatile int*>(&s.U), blk, G, has_shared);
+                        nB = nstatic / kFConsumers + 2 * (dyn.cnt0 + dyn.cnt1);
+                        const int nC = pl.tile >= 0 ? (dyn.U + 3) / 4 : 0;
                         total = (nB + nC) * kFConsumers;
                     }
                 }
@@ -307,7 +350,7 @@ decode_few_kernel(const __grid_constant__ CUtensorMap gu_map, const __grid_const
                                 y = pl.shared_atom * kFTile;
                                 z = 0;
                             } else {
-                                const int a = first + ((n - nstatic / kFConsumers) >> 1);
+                                const int a = few_atom(dyn, (n - nstatic / kFConsumers) >> 1);
                                 map = &gu_map;
                                 y = (a % kFAtomsPerExpert) * kFTile;
                                 z = 2 * s.uexp[a / kFAtomsPerExpert];
@@ -322,7 +365,7 @@ decode_few_kernel(const __grid_constant__ CUtensorMap gu_map, const __grid_const
                             // output rows: one copy of 4 KB per expert.  (Copies of 2 KB, four per stage, kept this
                             // warp busier issuing than the memory system delivering.)
                             const int c = n - nB;
-                            const int nu = min(2, max(0, U - c * 4 - 2 * (w >> 2)));
+                            const int nu = min(2, max(0, dyn.U - c * 4 - 2 * (w >> 2)));
                             mbar_expect_tx(&s.full[slot], (uint32_t)nu * 4096u);       // nothing to fetch: the arrival alone completes the phase
                             for (int q = 0; q < nu; ++q)
                                 tma_load_3d(dst + q * 4096, &dn_map, 0, 2 * (w & 3), s.uexp[c * 4 + 2 * (w >> 2) + q] * H + pl.tile * kFTile, &s.full[slot]);
@@ -347,6 +390,45 @@ decode_few_kernel(const __grid_constant__ CUtensorMap gu_map, const __grid_const
                 mbar_wait_spin(&s.sel_done, 0, kWaitCycles, &s.abort_flag);
                 few_build_plan(p, s, lane);
                 if (lane == 0) { mbar_arrive(&s.plan_ready); FEW_TRACE(19); }
+                // afterwards this warp counts the block's two publications (see `publish` below)
+                if (lane == 0) {
+#pragma unroll 1
+                    for (int which = 0; which < 2; ++which) {
+                        mbar_wait(&s.pubbar[which], 0, &s.abort_flag);
+                        __threadfence();
+                        atomicAdd(p.bar + (which ? 2 : 0), 1u);
+                    }
+                }
+            }
+            if (t == 1 && pl.tile >= 0) {
+                // This warp has nothing else to do: it fetches the activation rows for the block's down phase.  Per
+                // half of the experts: watch the counter of the blocks that have published (one thread per block),
+                // then one bulk copy of the half's rows (the shared expert's rows travel with the first half) into the
+                // space the tokens and router rows no longer need.  (Tagged words, as for the logits, were tried
+                // first: 1024 warps polling 9 MB of them took 7 us per round.)
+                mbar_wait(&s.plan_ready, 0, &s.abort_flag);
+                if (lane == 0) {
+                    const unsigned char* src = reinterpret_cast<const unsigned char*>(p.act_rows);
+                    const int rows0 = min(max(s.rows0, 0), kFUnits), rows = min(max(s.rows, rows0), kFUnits);
+                    const long long t0 = clock64();
+#pragma unroll 1
+                    for (int half = 0; half < 2; ++half) {
+                        const unsigned target = s.done_target;
+                        const unsigned* counter = p.bar + (half ? 2 : 0);
+                        while ((int)(ld_acquire_u32(counter) - target) < 0) {
+                            if (clock64() - t0 > (s.abort_flag ? min(p.wait_cycles, kWaitCyclesAfterAbort) : p.wait_cycles)) { s.abort_flag = 1; break; }
+                            __nanosleep(100);
+                        }
+                        FEW_TRACE(half ? 25 : 22);
+                        asm volatile("fence.proxy.async;" ::: "memory");       // the copies read what other blocks' threads stored
+                        const int r0 = half ? rows0 : 0, r1 = half ? rows : rows0;
+                        const uint32_t routed_bytes = (uint32_t)(r1 - r0) * I * 2u;
+                        const uint32_t shared_bytes = (half == 0 && has_shared) ? (uint32_t)T * I * 2u : 0u;
+                        mbar_expect_tx(&s.actfull[half], routed_bytes + shared_bytes);      // no bytes: the arrival completes the phase
+                        if (routed_bytes) bulk_load(s.u.act + (size_t)r0 * I * 2, src + (size_t)r0 * I * 2, routed_bytes, &s.actfull[half]);
+                        if (shared_bytes) bulk_load(s.u.act + (size_t)kFUnits * I * 2, src + (size_t)kFUnits * I * 2, shared_bytes, &s.actfull[half]);
+                    }
+                }
             }
         }
     } else {
@@ -443,19 +525,62 @@ decode_few_kernel(const __grid_constant__ CUtensorMap gu_map, const __grid_const
             bx[ks][0] = gid < T ? d1_lds32(src) : 0u;
             bx[ks][1] = gid < T ? d1_lds32(src + 16) : 0u;
         }
-        int natoms = pl.shared_atom >= 0 ? 1 : 0;      // grows once the distinct experts are known
-        bool planned = false;
+        const int sh = pl.shared_atom >= 0 ? 1 : 0;
+        const unsigned tag = s.tag;
+        FDyn dyn{};                                    // known once the distinct experts are listed
+        // The K-slice sums of the block's atoms [j0, j1) meet (they sit in bpart from index 0 on); SwiGLU; the activations
+        // go to global memory as plain bf16 pairs; then "this block has published half `which`": a thread of another
+        // warp, which has met this block's threads at a barrier, fences (the block's stores are visible before the
+        // count) and adds one.  Work item = (atom, pair of rows, token).
+        auto publish = [&](int j0, int j1, int which) {
+            named_bar_sync(1, cthreads);
+            const int items = (j1 - j0) * (kFTile / 2) * T;
+            for (int item = tid; item < items; item += cthreads) {
+                const int t = item % T, rp = (item / T) % (kFTile / 2), jb = item / (T * (kFTile / 2)), j = j0 + jb;
+                int row, atom_in_expert;
+                if (j < sh) {
+                    row = kFUnits + t;
+                    atom_in_expert = pl.shared_atom;
+                } else {
+                    const int a = few_atom(dyn, j - sh);
+                    row = s.urow[a / kFAtomsPerExpert][t];
+                    atom_in_expert = a % kFAtomsPerExpert;
+                }
+                if (row < 0) continue;                                // this token did not choose the expert
+                float acts[2];
+#pragma unroll
+                for (int k2 = 0; k2 < 2; ++k2) {
+                    const int r = 2 * rp + k2;
+                    float gsum = 0.f, usum = 0.f;
+#pragma unroll
+                    for (int w = 0; w < kFConsumers; ++w) { gsum += s.bpart[2 * jb][w][r][t]; usum += s.bpart[2 * jb + 1][w][r][t]; }
+                    acts[k2] = silu_mul(gsum, usum);
+                }
+                p.act_rows[(size_t)row * kFWordsPerRow + atom_in_expert * (kFTile / 2) + rp] =
+                    (unsigned)__bfloat16_as_ushort(__float2bfloat16_rn(acts[0])) |
+                    ((unsigned)__bfloat16_as_ushort(__float2bfloat16_rn(acts[1])) << 16);
+            }
+            named_bar_sync(1, cthreads);
+            // the fence takes a microsecond or two under load: it is left to a warp that has nothing else to do
+            if (tid == 0) { mbar_arrive(&s.pubbar[which]); FEW_TRACE(which ? 5 : 21); }
+        };
+        int n_first = sh, natoms = sh;                 // atoms of the first half (the shared expert's included), of both halves
+        bool planned = false, published0 = false;
 #pragma unroll 1
         for (int j = 0; ; ++j) {
-            if (j >= natoms) {
-                if (planned) break;
+            if (j >= natoms && !planned) {
                 planned = true;
                 mbar_wait(&s.plan_ready, 0, &s.abort_flag);
-                int first, count;
-                few_routed_atoms(min(max(s.U, 0), kFUnits), blk, G, has_shared, first, count);
-                natoms += count;
-                if (j >= natoms) break;
+                dyn = few_dynamic_plan(s.U, blk, G, has_shared);
+                n_first = sh + dyn.cnt0;
+                natoms = n_first + dyn.cnt1;
             }
+            if (planned && !published0 && j == n_first) {
+                published0 = true;
+                publish(0, n_first, 0);
+            }
+            if (j >= natoms) break;
+            const int jb = j < n_first ? j : j - n_first;      // the second half reuses the K-slice sum buffers
             // a stage holds four boxes: gate and up rows over columns [0, 64) of the stage, then over [64, 128)
             float gs[4] = {0.f, 0.f, 0.f, 0.f}, us[4] = {0.f, 0.f, 0.f, 0.f};   // rows gid, gid + 8 x tokens 2 tig, 2 tig + 1
 #pragma unroll
@@ -492,102 +617,38 @@ decode_few_kernel(const __grid_constant__ CUtensorMap gu_map, const __grid_const
                 if (lane == 0) d1_release(&s.empty[slot], dep);
             }
             if (tig < 2) {
-                *reinterpret_cast<float2*>(&s.bpart[2 * j][warp][gid][2 * tig]) = make_float2(gs[0], gs[1]);
-                *reinterpret_cast<float2*>(&s.bpart[2 * j][warp][gid + 8][2 * tig]) = make_float2(gs[2], gs[3]);
-                *reinterpret_cast<float2*>(&s.bpart[2 * j + 1][warp][gid][2 * tig]) = make_float2(us[0], us[1]);
-                *reinterpret_cast<float2*>(&s.bpart[2 * j + 1][warp][gid + 8][2 * tig]) = make_float2(us[2], us[3]);
+                *reinterpret_cast<float2*>(&s.bpart[2 * jb][warp][gid][2 * tig]) = make_float2(gs[0], gs[1]);
+                *reinterpret_cast<float2*>(&s.bpart[2 * jb][warp][gid + 8][2 * tig]) = make_float2(gs[2], gs[3]);
+                *reinterpret_cast<float2*>(&s.bpart[2 * jb + 1][warp][gid][2 * tig]) = make_float2(us[0], us[1]);
+                *reinterpret_cast<float2*>(&s.bpart[2 * jb + 1][warp][gid + 8][2 * tig]) = make_float2(us[2], us[3]);
             }
         }
-        // The K-slices of every tile meet; SwiGLU; the activations go to global memory as plain bf16 pairs.  Work item =
-        // (atom, pair of rows, token).  The blocks that own output rows fetch all activation rows with bulk copies once
-        // every block has published, which a counter tells them: a thread that has met its block at a barrier
-        // fences (making the block's stores visible before the count) and adds one.  (Tagged words, as for the
-        // logits, were tried first: 1024 warps polling 9 MB of them took 7 us per round.)
-        named_bar_sync(1, cthreads);
-        const unsigned tag = s.tag;
-        {
-            int first, count;
-            few_routed_atoms(min(max(s.U, 0), kFUnits), blk, G, has_shared, first, count);
-            const int sh = pl.shared_atom >= 0 ? 1 : 0;
-            const int items = natoms * (kFTile / 2) * T;
-            uint32_t* const actb = reinterpret_cast<uint32_t*>(p.actw);       // [rows][I / 2] pairs of bf16
-            for (int item = tid; item < items; item += cthreads) {
-                const int t = item % T, rp = (item / T) % (kFTile / 2), j = item / (T * (kFTile / 2));
-                int row, atom_in_expert;
-                if (j < sh) {
-                    row = kFUnits + t;
-                    atom_in_expert = pl.shared_atom;
-                } else {
-                    const int a = first + (j - sh);
-                    row = s.urow[a / kFAtomsPerExpert][t];
-                    atom_in_expert = a % kFAtomsPerExpert;
-                }
-                if (row < 0) continue;                                // this token did not choose the expert
-                float acts[2];
-#pragma unroll
-                for (int k2 = 0; k2 < 2; ++k2) {
-                    const int r = 2 * rp + k2;
-                    float gsum = 0.f, usum = 0.f;
-#pragma unroll
-                    for (int w = 0; w < kFConsumers; ++w) { gsum += s.bpart[2 * j][w][r][t]; usum += s.bpart[2 * j + 1][w][r][t]; }
-                    acts[k2] = silu_mul(gsum, usum);
-                }
-                actb[(size_t)row * kFWordsPerRow + atom_in_expert * (kFTile / 2) + rp] =
-                    (unsigned)__bfloat16_as_ushort(__float2bfloat16_rn(acts[0])) |
-                    ((unsigned)__bfloat16_as_ushort(__float2bfloat16_rn(acts[1])) << 16);
-            }
-        }
-        named_bar_sync(1, cthreads);
-        if (tid == 0) {
-            __threadfence();
-            atomicAdd(p.bar, 1u);
-            FEW_TRACE(5);
-        }
+        publish(n_first, natoms, 1);
 
         if (pl.tile >= 0) {
             // ---- down: the block's 16 output rows for every token
-            const int U = min(max(s.U, 0), kFUnits);
+            const int U = dyn.U;
             float resid_v = 0.f;
             if (tid < kFTile * T && p.layer_hidden)
                 resid_v = load_any(p.hidden, p.hidden_dtype, (size_t)(tid / kFTile) * H + pl.tile * kFTile + (tid % kFTile));
             const bool want_gate = has_shared && p.shared_gate != nullptr;
-            {
-                const long long t0 = clock64();
-                if (tid == 0) {
-                    // one poller per block; then the rows come as two bulk copies (the (token, slot) rows, the shared
-                    // expert's rows) into the space the tokens and router rows no longer need.  (One copy per row into
-                    // rows padded against bank conflicts took twice as long, and the fragment loads are not what bounds
-                    // the phase.)
-                    const unsigned target = s.done_target;
-                    while ((int)(ld_acquire_u32(p.bar) - target) < 0) {
+            if (warp == 0 && lane < T) {
+                float gv = 1.f;
+                if (want_gate) {
+                    unsigned long long gw2 = 0ull;
+                    const long long t0 = clock64();
+                    for (;;) {
+                        gw2 = ld_relaxed_u64(gatew + lane);
+                        if ((unsigned)(gw2 >> 32) == tag) break;
                         if (clock64() - t0 > (s.abort_flag ? min(p.wait_cycles, kWaitCyclesAfterAbort) : p.wait_cycles)) { s.abort_flag = 1; break; }
-                        __nanosleep(100);
+                        __nanosleep(64);
                     }
-                    FEW_TRACE(25);
-                    asm volatile("fence.proxy.async;" ::: "memory");       // the copies read what other blocks' threads stored
-                    const uint32_t routed_bytes = (uint32_t)(T * p.top_k) * I * 2u, shared_bytes = has_shared ? (uint32_t)T * I * 2u : 0u;
-                    mbar_expect_tx(&s.actfull, routed_bytes + shared_bytes);
-                    const unsigned char* src = reinterpret_cast<const unsigned char*>(p.actw);
-                    bulk_load(s.u.act, src, routed_bytes, &s.actfull);
-                    if (shared_bytes) bulk_load(s.u.act + (size_t)kFUnits * I * 2, src + (size_t)kFUnits * I * 2, shared_bytes, &s.actfull);
+                    gv = __uint_as_float((unsigned)gw2);
                 }
-                if (warp == 0 && lane < T) {
-                    float gv = 1.f;
-                    if (want_gate) {
-                        unsigned long long gw2 = 0ull;
-                        for (;;) {
-                            gw2 = ld_relaxed_u64(gatew + lane);
-                            if ((unsigned)(gw2 >> 32) == tag) break;
-                            if (clock64() - t0 > (s.abort_flag ? min(p.wait_cycles, kWaitCyclesAfterAbort) : p.wait_cycles)) { s.abort_flag = 1; break; }
-                            __nanosleep(64);
-                        }
-                        gv = __uint_as_float((unsigned)gw2);
-                    }
-                    s.gate[lane] = gv;
-                }
-                __syncwarp();
-                mbar_wait(&s.actfull, 0, &s.abort_flag);
+                s.gate[lane] = gv;
             }
+            __syncwarp();
+            mbar_wait(&s.actfull[0], 0, &s.abort_flag);       // the first half's rows (fetched by a select warp)
             if (tid == 0) FEW_TRACE(12);
             // B fragments of activation row `row` (or zeros when negative) of this lane's token: k-steps from column col0 on
             auto act_frag = [&](int row, int col0, auto& b) {
@@ -600,12 +661,12 @@ decode_few_kernel(const __grid_constant__ CUtensorMap gu_map, const __grid_const
             };
             float acc[4] = {0.f, 0.f, 0.f, 0.f};          // rows gid, gid + 8 x tokens 2 tig, 2 tig + 1, routing weights applied
             const int nC = (U + 3) / 4;
-            int natoms_r, first_r;
-            few_routed_atoms(U, blk, G, has_shared, first_r, natoms_r);
-            const int nB = (pl.shared_atom >= 0 ? 2 : 0) + 2 * natoms_r;
+            const int nB = 2 * natoms;
+            const int first_of_second_half = dyn.U0 < U ? dyn.U0 / 4 : nC;        // U0 is a multiple of four when U0 < U
             const int hf = warp >> 2, qd = warp & 3;      // which two experts of a group, which quarter of the columns
 #pragma unroll 1
             for (int cst = 0; cst < nC; ++cst) {
+                if (cst == first_of_second_half) mbar_wait(&s.actfull[1], 0, &s.abort_flag);
                 const int it = (nB + cst) * kFConsumers + warp;
                 const int slot = it % kFStages;
                 mbar_wait(&s.full[slot], (it / kFStages) & 1u, &s.abort_flag);
@@ -742,7 +803,8 @@ bool decode_few_supported(const DecodeParams& p, int weight_dtype) {
     if (G < kFH / kFTile) return false;                                        // every output tile needs a block
     if ((p.E + G - 1) / G + (p.shared_gate ? 1 : 0) > kFMaxRouterRows) return false;
     if (((p.E + G - 1) / G + (p.shared_gate ? 1 : 0)) * p.T > 32) return false;      // one lane per (row, token)
-    if ((p.T * p.top_k * kFAtomsPerExpert + G - 1) / G + 1 > kFMaxAtoms) return false;
+    if ((kFUnits / 2 * kFAtomsPerExpert + G - 1) / G + 1 > kFMaxAtoms) return false;       // atoms of a block per half
+    if (p.act_rows == nullptr || (reinterpret_cast<uintptr_t>(p.act_rows) & 15)) return false;
     uintptr_t bits = reinterpret_cast<uintptr_t>(p.hidden) | reinterpret_cast<uintptr_t>(p.norm_weight) |
                      reinterpret_cast<uintptr_t>(p.router_weight) | reinterpret_cast<uintptr_t>(p.gate_up) |
                      reinterpret_cast<uintptr_t>(p.down) | reinterpret_cast<uintptr_t>(p.shared_gate_up) |

@@ -136,6 +136,7 @@ struct DecodeParams {
     unsigned long long* tagged;   // workspace [E]: (launch tag << 32 | logit bits), how the blocks exchange the logits
     unsigned long long* actw;     // workspace [(k+1)*I + 1]: (tag << 32 | bf16 head << 16 | bf16 remainder) per SwiGLU
                                   //   activation of the k slots and the shared expert; last word: the shared gate (fp32 bits)
+    uint32_t* act_rows;           // decode_few: workspace [36][I / 2] pairs of bf16, the activations of its (expert, token) rows
     int* error_word;
     unsigned long long* trace;    // optional [blocks][16] nanosecond timestamps of the phase boundaries
     int H, E, I, top_k;

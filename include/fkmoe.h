@@ -66,8 +66,9 @@ typedef struct fk_moe_dims {
                                       landed, 5 this block's activations published, 12 the activations this block needs
                                       are in shared memory, 14 last copy issued, 13 down tiles done, 15 output stored,
                                       7 exit (0 where a block skips the step); SM cycle counter in 8 (entry) and 9 (exit).
-                                      Two to four tokens: 19 is "distinct experts listed", and there are 25 every block has
-                                      published, 26 / 27 first down stage landed / done; no 1, 8, 9.
+                                      Two to four tokens: 19 is "distinct experts listed", 21 / 5 this block has published the
+                                      first / second half of the experts, 22 / 25 every block has, 26 / 27 first down stage
+                                      landed / done; no 1, 8, 9.
                                       Ignored when the record (blocks * 256 bytes) does not fit the y region. */
 #define FK_FLAG_SKIP_FOREIGN 16u   /* ids outside [expert_base, expert_base+E) are skipped instead of clamped */
 #define FK_FLAG_WIDE_PASSES 128u   /* tcgen05 path: 128 tokens per pass and two weight tiles per unit instead of 64 and one */
