@@ -356,7 +356,7 @@ def run_single(args):
                                                        NCU_TRAFFIC_PER_BYTE.get("decode_few"), "profiles/decode_few_b4.md")
         dom_bytes = layer_bytes
         dom_ms = ms
-    elif B <= 96:
+    elif B < 64:
         dom_kernel, dom_bytes, traffic_ratio = ("stream_gemv_kernel<8,true,false> (gate_up GEMV + SwiGLU, "
                                                 "TMA ring, mma.sync consumers)"), gate_up_bytes, NCU_TRAFFIC_PER_BYTE["stream_gate_up"]
         traffic_file = "profiles/stream_gemv_b32.md"

@@ -87,13 +87,15 @@ static int run_experts(const fk_moe_call* c, const Workspace& w, const long long
     ep.T = d.tokens; ep.H = d.hidden; ep.E = d.experts; ep.I = d.intermediate; ep.top_k = d.top_k;
     ep.routes = pp.routes;
     ep.shared_tok0 = sh0; ep.shared_n = sh_n;
-    // Path choice.  The weight-streaming kernels win while an expert sees few tokens: with their tensor-core
-    // consumers (bf16 models, 8-token passes) up to 96 tokens per call, with the CUDA-core consumers below 64.
-    // Above that the tcgen05 grouped GEMM (64-token passes) takes over.
+    // Path choice.  The weight-streaming kernels (8-token passes with their tensor-core consumers, 4-token passes with
+    // the CUDA-core ones) win while an expert sees few tokens: below 64 tokens per call.  From 64 on the tcgen05
+    // grouped GEMM (64-token passes) takes over: at 64 evenly routed tokens the two are level (189 vs 186 us), and
+    // when a few experts draw most of the tokens the GEMM reads their weights once instead of once per 8 tokens
+    // (64 tokens, eight hot experts: 135 vs 154 us).
     const bool generic = (c->flags & FK_FLAG_FORCE_GENERIC) != 0;
     const bool stream_ok = !generic && stream_path_supported(ep, c->weight_dtype);
     const int stream_rows = stream_ok ? stream_pass_rows(ep) : 4;
-    const int stream_max_tokens = stream_rows == 8 ? 96 : 63;
+    const int stream_max_tokens = 63;
     const bool want_tc = !generic && !(c->flags & FK_FLAG_FORCE_GEMV) &&
                          ((c->flags & FK_FLAG_FORCE_TENSOR) || d.tokens > stream_max_tokens || !stream_ok);
     const bool use_tc = want_tc && (d.tokens >= 64 || (c->flags & FK_FLAG_FORCE_TENSOR)) && tc_path_supported(ep, c->weight_dtype);
