@@ -74,13 +74,8 @@ __device__ __forceinline__ void box_load(uint32_t (&a)[4][4], uint32_t box_addr,
 #pragma unroll
     for (int kk = 0; kk < 4; ++kk) d1_ldmatrix_x4(a[kk], rbase + (((2 * kk + sel) ^ sw) << 4));
 }
-// The shared-memory instructions are volatile asm statements and keep their program order, so the loads of a box are
-// written out before its MMAs: a load that waits for the MMA before it made every k-step cost a full load latency.
-__device__ __forceinline__ void box_mma(float (&c)[4], uint32_t box_addr, const uint32_t (*bfrag)[2], int lane) {
-    uint32_t a[4][4];
-    box_load(a, box_addr, lane);
-#pragma unroll
-    for (int kk = 0; kk < 4; ++kk) d1_mma(c, a[kk], bfrag[kk][0], bfrag[kk][1]);
-}
+// The shared-memory and MMA instructions are volatile asm statements and keep their program order, so callers write the
+// loads of a box (or of several) out before the MMAs: a load that waits for the MMA before it made every k-step cost
+// a full load latency.
 
 }  // namespace fk
