@@ -378,6 +378,26 @@ def test_few_token_fused_kernel_matches_staged_path_and_oracle(real_bf16_biased,
         assert torch.equal(again[1], fused[1]) and torch.equal(again[3], fused[3])      # bitwise repeatable
 
 
+@pytest.mark.parametrize("tokens,top_k", [(2, 1), (3, 2), (4, 5), (2, 8)])
+def test_few_token_fused_kernel_other_top_k_and_few_experts(tokens, top_k):
+    """Fewer than eight experts per token, and a router with fewer experts than the GPU has blocks (16: most blocks own
+    no router row): the single-launch kernel against the staged kernels and the oracle."""
+    spec = MoESpec(hidden_size=2048, num_experts=16, num_routed_experts=top_k, expert_intermediate_size=512)
+    w = make_moe_weights(60 + top_k, spec, dtype=torch.bfloat16, device="cuda", bias_std=0.5)
+    for seed in range(2):
+        hidden = make_hidden(800 + 10 * tokens + seed, tokens, spec, dtype=torch.bfloat16, device="cuda")
+        fused = triton_qwen36_batched_moe_layer_decode(hidden, *w.tuple(), top_k=top_k, router_bias=w.router_bias)
+        staged = triton_qwen36_batched_moe_layer_decode(hidden, *w.tuple(), top_k=top_k, router_bias=w.router_bias,
+                                                        flags=_lib.FLAG_NO_FUSED_DECODE)
+        assert torch.equal(fused[3], staged[3])
+        torch.testing.assert_close(fused[4], staged[4], atol=1e-6, rtol=1e-5)
+        assert O.max_abs(fused[1].cpu(), staged[1].cpu()) <= 2e-2 and O.rel_l2(fused[1].cpu(), staged[1].cpu()) <= 5e-3
+        ref = oracle_layer(hidden, w, top_k)
+        check_routing(fused[2], fused[3], fused[4], ref, torch.bfloat16)
+        check_output_where_ids_agree(fused[1], fused[3], ref.topk_ids, ref.output, torch.bfloat16,
+                                     what=f"few-token kernel, {tokens} tokens, top-{top_k}")
+
+
 def test_few_token_fused_kernel_tokens_sharing_experts():
     """Experts chosen by several tokens are streamed once and multiplied for all of them: identical tokens share all
     eight experts, hot experts are shared by most tokens, and a token's result must not depend on its neighbours."""
