@@ -42,7 +42,8 @@ static_assert(kFStages % kFConsumers == 0, "every ring slot must belong to one c
 static_assert(kFH == kFConsumers * 256 && kFI == kFConsumers * 64, "one K-slice per consumer warp");
 constexpr int kFThreads = (kFConsumers + 1 + kFMaxT) * 32;   // consumers + producer warp + one select warp per token
 constexpr int kFTile = 16;                       // MMA M: gate (or up) rows per stage, output rows per block
-constexpr int kFMaxRouterRows = 4;               // router rows of a block, the shared-expert gate vector included
+constexpr int kFMaxRouterRows = 3;               // router rows of a block, the shared-expert gate vector included
+static_assert((kFMaxRouterRows + 1) * kFMaxT == 16, "the router reduction below is written for 16 values per lane");
 constexpr int kFMaxAtoms = 6;                    // gate_up atoms per block and half (the shared expert's one included)
 constexpr int kFUnits = kFMaxT * FK_MAX_TOP_K;   // (token, routing slot) pairs = the most distinct experts
 constexpr int kFActRows = kFUnits + kFMaxT;      // activation rows of I values: (token, slot), then the shared expert per token
@@ -185,14 +186,18 @@ __device__ __forceinline__ void few_poll_and_select(const DecodeParams& p, FSmem
     __syncwarp();
 }
 
-// The distinct experts of the batch, by one warp: lane i stands for (token i / top_k, slot i % top_k).
-__device__ __forceinline__ void few_build_plan(const DecodeParams& p, FSmem& s, int lane) {
-    const int n = p.T * p.top_k;
+// "Token t does not use expert u" everywhere: done by the listing warp while it waits for the logits.
+__device__ __forceinline__ void few_clear_plan(FSmem& s, int lane) {
     for (int i = lane; i < kFUnits * kFMaxT; i += 32) {
         (&s.uw[0][0])[i] = 0.f;
         (&s.urow[0][0])[i] = -1;
     }
     __syncwarp();
+}
+
+// The distinct experts of the batch, by one warp: lane i stands for (token i / top_k, slot i % top_k).
+__device__ __forceinline__ void few_build_plan(const DecodeParams& p, FSmem& s, int lane) {
+    const int n = p.T * p.top_k;
     const bool valid = lane < n;
     const int t = valid ? lane / p.top_k : 0, sl = valid ? lane % p.top_k : 0;
     const int id = valid ? s.ids[t][sl] : -1 - lane;                 // padding lanes match nobody
@@ -382,6 +387,7 @@ decode_few_kernel(const __grid_constant__ CUtensorMap gu_map, const __grid_const
         few_barriers_ready_wait();
         if (t < T) {
             pdl_wait();
+            if (t == 0) few_clear_plan(s, lane);
             mbar_wait_spin(&s.xready, 0, kWaitCycles, &s.abort_flag);      // the tag travels with the tokens
             if (p.E <= 256) few_poll_and_select<8>(p, s, t, lane, blk == 0);
             else few_poll_and_select<32>(p, s, t, lane, blk == 0);
@@ -460,38 +466,48 @@ decode_few_kernel(const __grid_constant__ CUtensorMap gu_map, const __grid_const
                 rw[r][0] = bf16lo(w.x); rw[r][1] = bf16hi(w.x); rw[r][2] = bf16lo(w.y); rw[r][3] = bf16hi(w.y);
                 rw[r][4] = bf16lo(w.z); rw[r][5] = bf16hi(w.z); rw[r][6] = bf16lo(w.w); rw[r][7] = bf16hi(w.w);
             }
-#pragma unroll 1
-            for (int t = 0; t < T; ++t) {
-                const uint4 v = lds128(s.u.in.xraw[t] + (size_t)c0 * 2);
-                float xv[8];
-                xv[0] = bf16lo(v.x); xv[1] = bf16hi(v.x); xv[2] = bf16lo(v.y); xv[3] = bf16hi(v.y);
-                xv[4] = bf16lo(v.z); xv[5] = bf16hi(v.z); xv[6] = bf16lo(v.w); xv[7] = bf16hi(v.w);
-                float racc[kFMaxRouterRows + 1];
-                float ss = 0.f;
+            // value r * 4 + t: this lane's part of row r against token t; 12 + t: of the token's sum of squares
+            float v[16];
 #pragma unroll
-                for (int i = 0; i < 8; ++i) ss = fmaf(xv[i], xv[i], ss);
-                racc[kFMaxRouterRows] = ss;
+            for (int i = 0; i < 16; ++i) v[i] = 0.f;
 #pragma unroll
-                for (int r = 0; r < kFMaxRouterRows; ++r) {
-                    const bool gate = r == pl.gate_row;            // the gate vector meets the raw token
-                    float a0 = 0.f, a1 = 0.f;
+            for (int t = 0; t < kFMaxT; ++t) {
+                if (t < T) {
+                    const uint4 xw = lds128(s.u.in.xraw[t] + (size_t)c0 * 2);
+                    float xv[8];
+                    xv[0] = bf16lo(xw.x); xv[1] = bf16hi(xw.x); xv[2] = bf16lo(xw.y); xv[3] = bf16hi(xw.y);
+                    xv[4] = bf16lo(xw.z); xv[5] = bf16hi(xw.z); xv[6] = bf16lo(xw.w); xv[7] = bf16hi(xw.w);
+                    float ss = 0.f;
 #pragma unroll
-                    for (int i = 0; i < 8; i += 2) {
-                        a0 = fmaf(rw[r][i], gate ? xv[i] : xv[i] * gw[i], a0);
-                        a1 = fmaf(rw[r][i + 1], gate ? xv[i + 1] : xv[i + 1] * gw[i + 1], a1);
+                    for (int i = 0; i < 8; ++i) ss = fmaf(xv[i], xv[i], ss);
+                    v[kFMaxRouterRows * 4 + t] = ss;
+#pragma unroll
+                    for (int r = 0; r < kFMaxRouterRows; ++r) {
+                        const bool gate = r == pl.gate_row;            // the gate vector meets the raw token
+                        float a0 = 0.f, a1 = 0.f;
+#pragma unroll
+                        for (int i = 0; i < 8; i += 2) {
+                            a0 = fmaf(rw[r][i], gate ? xv[i] : xv[i] * gw[i], a0);
+                            a1 = fmaf(rw[r][i + 1], gate ? xv[i + 1] : xv[i + 1] * gw[i + 1], a1);
+                        }
+                        v[r * 4 + t] = a0 + a1;
                     }
-                    racc[r] = a0 + a1;
-                }
-#pragma unroll
-                for (int off = 16; off > 0; off >>= 1) {
-#pragma unroll
-                    for (int r = 0; r <= kFMaxRouterRows; ++r) racc[r] += __shfl_xor_sync(kFull, racc[r], off);
-                }
-                if (lane == 0) {
-#pragma unroll
-                    for (int r = 0; r <= kFMaxRouterRows; ++r) s.rpart[r][t][warp] = racc[r];
                 }
             }
+            // Sixteen sums over the warp in sixteen shuffles instead of eighty: at every level a lane hands over the half of
+            // its values that its partner keeps, so that lane l ends up with the total of value l & 15.
+#pragma unroll
+            for (int half = 8; half >= 1; half >>= 1) {
+                const bool up = (lane & half) != 0;
+#pragma unroll
+                for (int i = 0; i < half; ++i) {
+                    const float send = up ? v[i] : v[i + half];
+                    const float recv = __shfl_xor_sync(kFull, send, half);
+                    v[i] = (up ? v[i + half] : v[i]) + recv;
+                }
+            }
+            const float total = v[0] + __shfl_xor_sync(kFull, v[0], 16);
+            if (lane < 16) s.rpart[lane >> 2][lane & 3][warp] = total;
             __syncwarp();
             if (lane == 0) mbar_arrive(&s.rdone);
             if (warp == 0) {
