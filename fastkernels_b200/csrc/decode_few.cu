@@ -106,22 +106,24 @@ __device__ __forceinline__ FPlan few_static_plan(const DecodeParams& p, int b, i
 }
 // The distinct experts are worked off in two halves (the first one a multiple of four experts), each with its own
 // "published" counter: while the second half's gate_up streams, the first half's activations are already exchanged,
-// and while the second half's are exchanged, the first half's down tiles are multiplied.  Within a half the 32 atoms
-// per expert are dealt evenly over all blocks; the remainders of the two halves go to different blocks, and the
-// blocks that hold a shared-expert atom come last.
+// and while the second half's are exchanged, the first half's down tiles are multiplied.  Within a half the atoms are
+// dealt round-robin over all blocks (so that the 32 atoms of one expert are streamed by 32 different SMs); the
+// remainders of the two halves go to different blocks, and the blocks that hold a shared-expert atom come last.
 struct FDyn {
     int U, U0;              // distinct experts; those of the first half
-    int first0, cnt0;       // this block's atoms of the first half: [first0, first0 + cnt0) out of U0 * 32
+    int first0, cnt0;       // this block's atoms of the first half: first0 + k * G (k < cnt0) out of U0 * 32
     int first1, cnt1;       // ... of the second half, out of (U - U0) * 32, counted from atom U0 * 32
+    int G;
 };
+// Atoms rb, rb + G, rb + 2 G, ... of `total`: consecutive atoms (the 32 of one expert) go to 32 different blocks.
 __device__ __forceinline__ void few_deal(int total, int b, int G, int rot, int& first, int& count) {
     const int rb = (b + G - rot % G) % G;
-    const int q = total / G, r = total - q * G;
-    first = rb * q + min(rb, r);
-    count = q + (rb < r ? 1 : 0);
+    first = rb;
+    count = rb < total ? (total - rb + G - 1) / G : 0;
 }
 __device__ __forceinline__ FDyn few_dynamic_plan(int U, int b, int G, bool has_shared) {
     FDyn d;
+    d.G = G;
     d.U = min(max(U, 0), kFUnits);
     d.U0 = min(d.U, 4 * ((d.U + 7) / 8));
     const int rot0 = has_shared ? kFAtomsPerExpert : 0;
@@ -131,7 +133,7 @@ __device__ __forceinline__ FDyn few_dynamic_plan(int U, int b, int G, bool has_s
 }
 // global atom (expert * 32 + atom within the expert) of the block's k-th routed atom
 __device__ __forceinline__ int few_atom(const FDyn& d, int k) {
-    return k < d.cnt0 ? d.first0 + k : d.U0 * kFAtomsPerExpert + d.first1 + (k - d.cnt0);
+    return k < d.cnt0 ? d.first0 + k * d.G : d.U0 * kFAtomsPerExpert + d.first1 + (k - d.cnt0) * d.G;
 }
 
 #define FEW_TRACE(slot) do { if (p.trace) p.trace[(size_t)blockIdx.x * 32 + (slot)] = global_ns(); } while (0)
