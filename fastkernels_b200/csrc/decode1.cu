@@ -258,6 +258,7 @@ decode1_kernel(const __grid_constant__ CUtensorMap gu_map, const __grid_constant
         // on the kernel before this one (the shared expert's gate_up tiles); the token follows as soon as that
         // kernel has completed; stages whose addresses depend on the ids wait for the select warp; the down tiles
         // are issued as ring slots free up.
+        const uint64_t wpolicy = l2_evict_first_policy();      // expert weights are read once per call: first out of L2
         const int nstatic = 2 * max(0, min(pl.atoms, pl.shared_atoms - pl.atom0)) * kD1Consumers;   // stages of shared atoms
         const int total = (pl.nB + pl.nC) * kD1Consumers;
         bool token_issued = false;
@@ -336,14 +337,14 @@ decode1_kernel(const __grid_constant__ CUtensorMap gu_map, const __grid_constant
                             mbar_expect_tx(&s.full[slot], kD1StageBytes);
 #pragma unroll
                             for (int op = 0; op < 2; ++op)
-                                tma_load_3d(dst + op * 4096, map, w * 256 + (n & 1) * 128 + op * 64, y, z, &s.full[slot]);
+                                tma_load_3d_hint(dst + op * 4096, map, w * 256 + (n & 1) * 128 + op * 64, y, z, &s.full[slot], wpolicy);
                         } else {
                             // down tiles of four slots, columns [64 w, 64 w + 64) of the block's 16 output rows
                             const int c = n - pl.nB;
                             const int nu = min(4, p.top_k - c * 4);
                             mbar_expect_tx(&s.full[slot], (uint32_t)nu * 2048u);
                             for (int u = 0; u < nu; ++u)
-                                tma_load_2d(dst + u * 2048, &dn_map, w * 64, d1_id(s, c * 4 + u) * H + pl.tile * kD1Tile, &s.full[slot]);
+                                tma_load_2d_hint(dst + u * 2048, &dn_map, w * 64, d1_id(s, c * 4 + u) * H + pl.tile * kD1Tile, &s.full[slot], wpolicy);
                         }
                         if (it == nstatic) D1_TRACE(4);
                     } else if (pending) {

@@ -288,6 +288,7 @@ decode_few_kernel(const __grid_constant__ CUtensorMap gu_map, const __grid_const
         // Lane l owns ring slot l.  Stage n of consumer warp w is number it = 8 n + w of the block's queue: first the
         // gate_up stages (two per atom: the shared expert's atom, if the block has one, is known from the start), then
         // the down stages (four distinct experts each) of a block that owns output rows.
+        const uint64_t wpolicy = l2_evict_first_policy();      // expert weights are read once per call: first out of L2
         const int nstatic = pl.shared_atom >= 0 ? 2 * kFConsumers : 0;
         int total = nstatic, nB = nstatic / kFConsumers;
         FDyn dyn{};
@@ -365,7 +366,7 @@ decode_few_kernel(const __grid_constant__ CUtensorMap gu_map, const __grid_const
                             mbar_expect_tx(&s.full[slot], kFStageBytes);
 #pragma unroll
                             for (int op = 0; op < 2; ++op)
-                                tma_load_3d(dst + op * 4096, map, w * 256 + (n & 1) * 128 + op * 64, y, z, &s.full[slot]);
+                                tma_load_3d_hint(dst + op * 4096, map, w * 256 + (n & 1) * 128 + op * 64, y, z, &s.full[slot], wpolicy);
                         } else {
                             // Down tiles of a group of four distinct experts: warps 0-3 take the group's first two
                             // experts, warps 4-7 the other two, each a quarter of the columns (128) of the block's 16
@@ -375,7 +376,7 @@ decode_few_kernel(const __grid_constant__ CUtensorMap gu_map, const __grid_const
                             const int nu = min(2, max(0, dyn.U - c * 4 - 2 * (w >> 2)));
                             mbar_expect_tx(&s.full[slot], (uint32_t)nu * 4096u);       // nothing to fetch: the arrival alone completes the phase
                             for (int q = 0; q < nu; ++q)
-                                tma_load_3d(dst + q * 4096, &dn_map, 0, 2 * (w & 3), s.uexp[c * 4 + 2 * (w >> 2) + q] * H + pl.tile * kFTile, &s.full[slot]);
+                                tma_load_3d_hint(dst + q * 4096, &dn_map, 0, 2 * (w & 3), s.uexp[c * 4 + 2 * (w >> 2) + q] * H + pl.tile * kFTile, &s.full[slot], wpolicy);
                         }
                     }
                     // no pause and no suspending wait here: a lane that sleeps holds up the lanes whose slots are free

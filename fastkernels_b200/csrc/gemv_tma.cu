@@ -480,6 +480,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) stream_gemv_kernel(const __
     if (warp == kConsumerWarps) {
         // ---------------------------------------------------------------- weight producer
         {
+            const uint64_t wpolicy = l2_evict_first_policy();
             uint32_t it = 0;
             int unit = blockIdx.x;
             // __ldcg: in the down kernel this warp does not wait for the kernel before it (see launch_experts_stream), so
@@ -511,14 +512,14 @@ __global__ void __launch_bounds__(kStreamThreads, 1) stream_gemv_kernel(const __
                         // one copy per weight row (gate rows first, then the up rows of the same pairs), rows padded apart
                         for (int r = lane; r < 2 * PER_STAGE; r += 32) {
                             const size_t grow = r < PER_STAGE ? first + r : (size_t)p.I + first + (r - PER_STAGE);
-                            bulk_load(sbuf + (size_t)r * (K * 2 + kRowPad), W + grow * K, K * 2, &s.full[stage]);
+                            bulk_load_hint(sbuf + (size_t)r * (K * 2 + kRowPad), W + grow * K, K * 2, &s.full[stage], wpolicy);
                         }
                     } else if (TM) {
                         // one box of [PER_STAGE rows x 64 columns] per 128-byte column slab, 128-byte swizzle
                         const CUtensorMap* map = pass.x < 0 ? &smap : &wmap;
                         const int y = (pass.x < 0 ? 0 : pass.x * p.H) + (int)first;
                         for (int sl = lane; sl < K / 64; sl += 32)
-                            tma_load_2d(sbuf + (size_t)sl * (PER_STAGE * 128), map, sl * 64, y, &s.full[stage]);
+                            tma_load_2d_hint(sbuf + (size_t)sl * (PER_STAGE * 128), map, sl * 64, y, &s.full[stage], wpolicy);
                     } else if (lane == 0) {
                         bulk_load(sbuf, W + first * K, kStageBytes, &s.full[stage]);
                     }

@@ -80,6 +80,20 @@ __device__ __forceinline__ void bulk_load(void* dst_smem, const void* src_gmem, 
                  : "memory");
 }
 
+// The same copy with an L2 eviction hint: the weight streams are read once per call and should not push what is read
+// repeatedly (activation rows, pass lists, exchange words) out of L2.
+__device__ __forceinline__ uint64_t l2_evict_first_policy() {
+    uint64_t pol;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
+    return pol;
+}
+__device__ __forceinline__ void bulk_load_hint(void* dst_smem, const void* src_gmem, uint32_t bytes, uint64_t* bar, uint64_t policy) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;" ::"r"(
+                     smem_u32(dst_smem)),
+                 "l"(src_gmem), "r"(bytes), "r"(smem_u32(bar)), "l"(policy)
+                 : "memory");
+}
+
 // Named barrier for a subset of the block's warps.  bar.sync is an aligned instruction: every lane of a
 // warp has to execute it together, and a warp counts as arrived as soon as it is executed at all.  Code
 // that reaches the barrier after a divergent region (one lane polling a flag, say) must therefore
