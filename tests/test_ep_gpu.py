@@ -83,6 +83,19 @@ def _check_against_oracle(O, out, ids, ref, what):
     assert ma <= 2e-2 and rl <= 5e-3, (what, ma, rl, excluded)
 
 
+def _check_against_single_gpu(O, out, single, tokens, world, what):
+    """The expert-parallel result against the single-GPU layer on the rank's own tokens.  Both run the same kernels on
+    the same rows when the gathered batch takes the same path as the rank's batch: equal up to fp32 summation order.
+    From 64 tokens on a call takes the grouped GEMM, which rounds the SwiGLU activations to bf16: when only the gathered
+    batch is that large, the two agree within the bf16 output bounds."""
+    same_path = (world * tokens >= 64) == (tokens >= 64)
+    if same_path:
+        torch.testing.assert_close(out, single, atol=2e-5, rtol=1e-4)
+    else:
+        ma, rl = O.max_abs(out.cpu(), single.cpu()), O.rel_l2(out.cpu(), single.cpu())
+        assert ma <= 2e-2 and rl <= 5e-3, (what, ma, rl)
+
+
 def _worker(rank, world, port, store_port, tokens, failures):
     _init(rank, world, port)
     peers = _Peers(rank, world, store_port)
@@ -101,7 +114,7 @@ def _worker(rank, world, port, store_port, tokens, failures):
         assert torch.equal(out, out2) and torch.equal(ids, ids2), "not repeatable"
         single, _, ids1, _ = qwen36_batched_moe_decode(hidden, *full.tuple(), router_bias=full.router_bias)
         assert torch.equal(ids, ids1), "routing differs between one GPU and expert parallel"
-        torch.testing.assert_close(out, single, atol=2e-5, rtol=1e-4)
+        _check_against_single_gpu(O, out, single, tokens, world, "NCCL exchange")
         cpu = [None if t is None else t.cpu() for t in full.tuple()]
         ref = O.moe_update(hidden.cpu(), *cpu, top_k=8, router_bias=full.router_bias.cpu())
         _check_against_oracle(O, out, ids, ref, "NCCL exchange")
@@ -166,7 +179,9 @@ def _peer_worker(rank, world, port, store_port, tokens, failures):
         exchanges.append(exchange)
         for capture in (False, True):
             layer = PeerEPLayer(shard, exchange, tokens, capture=capture)
-            for step in range(4):
+            # the replayed graph runs many steps with changing inputs: a flag that overtook its rows would show as a
+            # mismatch with the collective-library exchange
+            for step in range(24 if capture else 4):
                 assert not peers.someone_failed(), "another rank failed"
                 hidden = make_hidden(70 + rank + 10 * step, tokens, spec, dtype=torch.bfloat16, device="cuda")
                 out, logits, ids, weights = layer.run(hidden)
@@ -177,7 +192,7 @@ def _peer_worker(rank, world, port, store_port, tokens, failures):
                 torch.testing.assert_close(out, ref_out, atol=2e-5, rtol=1e-4)
                 single, _, ids1, _ = qwen36_batched_moe_decode(hidden, *full.tuple(), router_bias=full.router_bias)
                 assert torch.equal(ids, ids1)
-                torch.testing.assert_close(out, single, atol=2e-5, rtol=1e-4)
+                _check_against_single_gpu(O, out, single, tokens, world, f"peer memory (capture={capture}, step {step})")
                 if step == 0:
                     ref = O.moe_update(hidden.cpu(), *cpu, top_k=8, router_bias=full.router_bias.cpu())
                     _check_against_oracle(O, out, ids, ref, f"peer memory (capture={capture})")
