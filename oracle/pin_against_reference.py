@@ -47,6 +47,12 @@ CASES = {
     # the full layer shape (H 2048, E 256, I 512, top-8); outputs come from qwen36_real_moe_update itself
     "real_full_fp32_1tok": (MoESpec(), 1, torch.float32, 31, 0.0),       # benchmark configuration 1: fp32, one token
     "real_full_bf16_4tok": (MoESpec(), 4, torch.bfloat16, 32, 0.0),
+    # one case per kernel family of the CUDA library at the full shape: single-token launch, few-token launch,
+    # streaming kernels (the default benchmark batch), grouped tensor-core GEMM
+    "real_full_bf16_1tok": (MoESpec(), 1, torch.bfloat16, 33, 0.0),
+    "real_full_bf16_2tok": (MoESpec(), 2, torch.bfloat16, 34, 0.0),
+    "real_full_bf16_32tok": (MoESpec(), 32, torch.bfloat16, 35, 0.0),
+    "real_full_bf16_64tok": (MoESpec(), 64, torch.bfloat16, 36, 0.0),
 }
 ROUTER_CASES = {
     # full-shape router (E=256, H=2048), several tokens
