@@ -492,7 +492,7 @@ def run_single(args):
 
 # DRAM bytes (read + write) per algorithmic byte of the dominant kernel, from the ncu captures summarised in
 # profiles/stream_gemv_b32.md, profiles/tc_grouped_gemm_b256.md and profiles/decode1_fused_b1.md.
-NCU_TRAFFIC_PER_BYTE = {"stream_gate_up": 1.010, "tc_gate_up": 1.015, "decode1": 1.007, "decode_few": 1.023}      # profiles/*.md
+NCU_TRAFFIC_PER_BYTE = {"stream_gate_up": 1.008, "tc_gate_up": 1.015, "decode1": 1.008, "decode_few": 1.019}      # profiles/*.md
 
 
 def main():
