@@ -13,8 +13,9 @@
 //                           expert): the home rank derives the same set from the token's ids and reads nothing else
 //
 // Dispatch: each rank stores its own rows into slot `rank` of every buffer (plain 16-byte stores to peer
-// memory), fences at system scope, and the last block to finish publishes the rank's new epoch in every
-// buffer's flag word and then waits until every rank's epoch has arrived in its own buffer.  The combine
+// memory); every block fences at device scope and takes a ticket, and the last block to finish fences at system
+// scope, publishes the rank's new epoch in every buffer's flag word (release) and then waits until every rank's
+// epoch has arrived in its own buffer (acquire).  The combine
 // does the same with the partial rows.  Epochs only grow and live in device memory, so a captured graph
 // replays correctly.  A buffer is never overwritten while a peer still reads it: rank A can only start call
 // n+1 after it has seen every rank's combine flag of call n, and a rank raises that flag after its own
