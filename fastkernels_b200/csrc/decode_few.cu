@@ -834,6 +834,9 @@ bool decode_few_supported(const DecodeParams& p, int weight_dtype) {
 }
 
 int launch_decode_few(const DecodeParams& p, cudaStream_t stream) {
+    // same switch as the single-token kernel: a cooperative launch guarantees that all blocks are resident together,
+    // at the price of the overlap with the previous kernel's tail
+    static const bool cooperative = [] { const char* e = getenv("FKMOE_D1_COOPERATIVE"); return e && e[0] == '1'; }();
     const int smem = (int)decode_few_smem_bytes();
     FK_CUDA_OK(cudaFuncSetAttribute(decode_few_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem), "decode_few attr");
     // gate_up: [2 halves x 16 rows x 64 columns] boxes; down: [16 rows x 2 x 64 columns] boxes (shared expert: [16 x 64]);
@@ -852,9 +855,15 @@ int launch_decode_few(const DecodeParams& p, cudaStream_t stream) {
     cfg.dynamicSmemBytes = (size_t)smem;
     cfg.stream = stream;
     cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
-    cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    if (cooperative) {
+        attr[0].id = cudaLaunchAttributeCooperative;
+        attr[0].val.cooperative = 1;
+        cfg.numAttrs = 1;
+    } else {
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    }
     cfg.attrs = attr;
     FK_CUDA_OK(cudaLaunchKernelEx(&cfg, decode_few_kernel, gu, sgu, dn, sdn, q), "decode_few launch");
     note_launch();

@@ -447,6 +447,45 @@ def test_few_token_fused_kernel_sees_fresh_data_every_call(real_bf16_biased):
     assert torch.equal(o, o1)
 
 
+_COOPERATIVE_CHILD = """
+import sys, torch
+from fastkernels_b200 import _lib
+from fastkernels_b200.plan import MoEDecodePlan
+from fastkernels_b200.spec import MoESpec
+from fastkernels_b200.workloads import make_hidden, make_moe_weights
+spec = MoESpec()
+w = make_moe_weights(1, spec, dtype=torch.bfloat16, device="cuda", bias_std=0.5)
+for tokens in (1, 4):
+    x = make_hidden(40 + tokens, tokens, spec, dtype=torch.bfloat16, device="cuda")
+    fused, staged = MoEDecodePlan(w, tokens), MoEDecodePlan(w, tokens, flags=_lib.FLAG_NO_FUSED_DECODE)
+    lib = _lib.load()
+    for _ in range(5):
+        before = lib.fk_launch_count()
+        out, _, ids, _ = fused.run(x)
+        assert lib.fk_launch_count() - before == 1       # the single-launch kernel took the call
+    ref, _, ref_ids, _ = staged.run(x)
+    torch.cuda.synchronize()
+    assert torch.equal(ids, ref_ids)
+    err = float((out - ref).abs().max())
+    assert err <= 2e-2, err
+    print("tokens", tokens, "max_abs", err)
+print("cooperative ok")
+"""
+
+
+def test_single_launch_kernels_as_cooperative_launches():
+    """FKMOE_D1_COOPERATIVE=1 (read once per process, hence the child): both single-launch kernels as cooperative
+    launches, which guarantee that all blocks are resident together, against the staged kernels."""
+    import os
+    import subprocess
+    import sys
+    env = dict(os.environ, FKMOE_D1_COOPERATIVE="1")
+    root = str(Path(__file__).resolve().parents[1])
+    env["PYTHONPATH"] = root + os.pathsep + env.get("PYTHONPATH", "")
+    r = subprocess.run([sys.executable, "-c", _COOPERATIVE_CHILD], env=env, cwd=root, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0 and "cooperative ok" in r.stdout, (r.stdout[-2000:], r.stderr[-2000:])
+
+
 def test_single_token_fused_kernel_fp32_hidden_and_many_calls(real_bf16):
     w = real_bf16
     hidden = make_hidden(5, 1, REAL, dtype=torch.float32, device="cuda")
